@@ -1,0 +1,147 @@
+/*
+ * moda_b200 — C ABI of the B200 (sm_100a) MoDA attention hot path.
+ *
+ * The reference (hustvl/MoDA) has no native layer: its operators are Python functions
+ * that launch Triton kernels.  Each entry point below names the reference function
+ * whose device work it replaces; the Python mirror of those functions
+ * (moda_b200/ops.py) binds this library with ctypes.
+ *
+ * Conventions
+ *   - Tensors are 4-D [B, T, H, D] with arbitrary element strides for B, T, H and a
+ *     contiguous innermost D (moda_tensor4).  Pointers are DEVICE pointers, 16-byte
+ *     aligned; strides must be multiples of 8 elements.  Inputs are never written.
+ *   - Queries are folded the reference's way (moda_v14.py:2839-2852): q is
+ *     [B, T_kv*G, H, D]; query row r belongs to base position t = r / G.
+ *   - depth_k / depth_v are [B, T_kv*L, H, D]; row t*L + l is layer l at position t
+ *     (moda_v14.py:1944-1945).  L == 0 means "no depth KV" (pass NULL tensors).
+ *   - lse is fp32 [B, T_kv*G, H] contiguous, in base-2 units (moda_v14.py:372-374).
+ *   - Every call is asynchronous on `stream` (a cudaStream_t), never synchronises,
+ *     never allocates device memory, and returns a moda_status (0 = success).
+ *     Nothing is launched when a non-zero status is returned from validation.
+ */
+#ifndef MODA_B200_H_
+#define MODA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum moda_status {
+  MODA_OK = 0,
+  MODA_ERR_NULL = 1,        /* required pointer is NULL */
+  MODA_ERR_SHAPE = 2,       /* B/T/H/G/L out of range, T_q != T_kv*G ... */
+  MODA_ERR_HEAD_DIM = 3,    /* D not in {64, 128} */
+  MODA_ERR_DTYPE = 4,       /* dtype not bf16/fp16 */
+  MODA_ERR_ALIGNMENT = 5,   /* pointer not 16-byte aligned or stride not multiple of 8 */
+  MODA_ERR_MODE = 6,        /* unknown mode / mode-argument mismatch */
+  MODA_ERR_CHUNK = 7,       /* chunk_rows not a positive multiple of G */
+  MODA_ERR_WORKSPACE = 8,   /* workspace NULL or too small */
+  MODA_ERR_CUDA = 9,        /* a CUDA runtime / driver call failed (see moda_b200_last_cuda_error) */
+  MODA_ERR_UNSUPPORTED = 10,/* requested kernel path cannot run this problem */
+  MODA_ERR_TOO_LARGE = 11   /* problem exceeds a fixed capacity of the entry point */
+} moda_status;
+
+typedef enum moda_mode {
+  MODA_CAUSAL = 0,        /* parallel_moda(is_causal=True)            moda_v14.py:2792 */
+  MODA_NONCAUSAL = 1,     /* parallel_moda(is_causal=False)           moda_v14.py:2792 */
+  MODA_CHUNK_VISIBLE = 2, /* parallel_moda_chunk_visible              moda_v16.py:3614 */
+  MODA_DEPTH_ONLY = 3     /* parallel_fda (no sequence k/v)           fda_v12.py:1346  */
+} moda_mode;
+
+typedef enum moda_dtype { MODA_BF16 = 0, MODA_FP16 = 1 } moda_dtype;
+
+/* Kernel path selector (moda_problem.path). */
+typedef enum moda_path {
+  MODA_PATH_AUTO = 0,    /* tcgen05 kernels where they apply, otherwise the mma.sync kernels */
+  MODA_PATH_SIMT_MMA = 1,/* warp-level mma.sync kernels (every shape) */
+  MODA_PATH_TCGEN05 = 2  /* tcgen05/TMEM/TMA kernels; MODA_ERR_UNSUPPORTED if they do not apply */
+} moda_path;
+
+typedef struct moda_tensor4 {
+  void *data;        /* device pointer, 16-byte aligned                       */
+  int64_t stride_b;  /* element strides; innermost (D) stride is 1            */
+  int64_t stride_t;
+  int64_t stride_h;
+} moda_tensor4;
+
+typedef struct moda_problem {
+  int32_t B;          /* batch                                                     */
+  int32_t T_kv;       /* base sequence length; T_q = T_kv * G                      */
+  int32_t H;          /* KV heads (== q heads in the folded layout)                */
+  int32_t D;          /* head dim of q/k and of v (64 or 128)                      */
+  int32_t G;          /* moda_group_num                                            */
+  int32_t L;          /* depth layers per position (0 = none)                      */
+  int32_t mode;       /* moda_mode                                                 */
+  int32_t chunk_rows; /* chunk-visible: query rows per chunk (the reference fixes
+                         64: moda_v16.py:581-585); ignored otherwise              */
+  int32_t dtype;      /* moda_dtype of q/k/v/depth/o/grads                         */
+  int32_t path;       /* moda_path                                                 */
+  float scale;        /* softmax scale (reference default D**-0.5)                 */
+  int32_t device;     /* CUDA device ordinal the pointers live on                  */
+} moda_problem;
+
+/*
+ * Forward: o, lse = attention(q, k, v, depth_k, depth_v).
+ * Replaces parallel_moda_fwd (moda_v14.py:381-522), parallel_moda_chunk_visible_fwd
+ * (moda_v16.py:498-633) and parallel_fda_fwd (fda_v12.py:261-400).
+ * k, v may be NULL only for MODA_DEPTH_ONLY; depth_k, depth_v NULL iff L == 0.
+ */
+int moda_b200_fwd(const moda_problem *prob, const moda_tensor4 *q, const moda_tensor4 *k,
+                  const moda_tensor4 *v, const moda_tensor4 *depth_k,
+                  const moda_tensor4 *depth_v, const moda_tensor4 *o, float *lse,
+                  void *stream);
+
+/*
+ * Bytes of scratch moda_b200_bwd needs (delta [B,T_q,H] fp32, plus per-path extras).
+ * Replaces the reference's internal torch.empty/torch.zeros scratch
+ * (moda_v14.py:1609,1715-1716).
+ */
+int moda_b200_bwd_workspace_bytes(const moda_problem *prob, size_t *bytes);
+
+/*
+ * Backward: dq, dk, dv, d_depth_k, d_depth_v from (inputs, o, lse, dout).
+ * Replaces parallel_moda_bwd (moda_v14.py:1470-1842), parallel_moda_chunk_visible_bwd
+ * (moda_v16.py:2099-2343) and parallel_fda_bwd (fda_v12.py:881-1135).
+ * `workspace` is caller-owned device scratch of at least
+ * moda_b200_bwd_workspace_bytes() bytes, 256-byte aligned; contents are undefined
+ * on entry and exit.  Gradients are fully overwritten (no pre-zeroing needed) and are
+ * computed without atomics: two runs on the same inputs are bit-identical.
+ */
+int moda_b200_bwd(const moda_problem *prob, const moda_tensor4 *q, const moda_tensor4 *k,
+                  const moda_tensor4 *v, const moda_tensor4 *depth_k,
+                  const moda_tensor4 *depth_v, const moda_tensor4 *o, const float *lse,
+                  const moda_tensor4 *dout, const moda_tensor4 *dq, const moda_tensor4 *dk,
+                  const moda_tensor4 *dv, const moda_tensor4 *d_depth_k,
+                  const moda_tensor4 *d_depth_v, void *workspace, size_t workspace_bytes,
+                  void *stream);
+
+/*
+ * Validation only (no launch): the status moda_b200_fwd / moda_b200_bwd would return
+ * for this problem's shape fields.  Mirrors the reference's shape assertions
+ * (moda_v14.py:404-408,476-478,487,2839-2862).
+ */
+int moda_b200_check_problem(const moda_problem *prob);
+
+/* Which kernel path MODA_PATH_AUTO resolves to for this problem's forward (is_bwd=0)
+ * or backward (is_bwd=1): MODA_PATH_SIMT_MMA or MODA_PATH_TCGEN05; <0 on bad input. */
+int moda_b200_resolve_path(const moda_problem *prob, int is_bwd);
+
+/* Number of kernel launches the last successful call on this host thread issued. */
+int moda_b200_last_launch_count(void);
+
+/* cudaError_t value recorded by the last MODA_ERR_CUDA on this host thread. */
+int moda_b200_last_cuda_error(void);
+
+/* Static, human-readable name of a moda_status. */
+const char *moda_b200_status_string(int status);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int moda_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MODA_B200_H_ */

@@ -1,0 +1,110 @@
+"""ctypes binding of ``libmoda_b200.so`` (declarations: ``include/moda_b200.h``).
+
+The library is the only compute path of this package: there is no eager / CPU
+fallback.  Loading fails loudly when the shared object has not been built
+(``python -m moda_b200.build``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmoda_b200.so")
+
+MODE_CAUSAL, MODE_NONCAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY = 0, 1, 2, 3
+DTYPE_BF16, DTYPE_FP16 = 0, 1
+PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05 = 0, 1, 2
+
+# every symbol include/moda_b200.h declares
+EXPORTED_SYMBOLS = (
+    "moda_b200_fwd",
+    "moda_b200_bwd_workspace_bytes",
+    "moda_b200_bwd",
+    "moda_b200_check_problem",
+    "moda_b200_resolve_path",
+    "moda_b200_last_launch_count",
+    "moda_b200_last_cuda_error",
+    "moda_b200_status_string",
+    "moda_b200_version",
+)
+
+
+class Tensor4(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("stride_b", ctypes.c_int64),
+        ("stride_t", ctypes.c_int64),
+        ("stride_h", ctypes.c_int64),
+    ]
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [
+        ("B", ctypes.c_int32),
+        ("T_kv", ctypes.c_int32),
+        ("H", ctypes.c_int32),
+        ("D", ctypes.c_int32),
+        ("G", ctypes.c_int32),
+        ("L", ctypes.c_int32),
+        ("mode", ctypes.c_int32),
+        ("chunk_rows", ctypes.c_int32),
+        ("dtype", ctypes.c_int32),
+        ("path", ctypes.c_int32),
+        ("scale", ctypes.c_float),
+        ("device", ctypes.c_int32),
+    ]
+
+
+class ModaLibraryError(RuntimeError):
+    """The shared library is missing or returned a non-zero status."""
+
+    def __init__(self, message: str, status: int = -1, cuda_error: int = 0):
+        super().__init__(message)
+        self.status = status
+        self.cuda_error = cuda_error
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ModaLibraryError(
+            f"{LIB_PATH} not found: build it with `python -m moda_b200.build` "
+            "(there is no fallback path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    P, T, V = ctypes.POINTER(Problem), ctypes.POINTER(Tensor4), ctypes.c_void_p
+    lib.moda_b200_fwd.argtypes = [P, T, T, T, T, T, T, V, V]
+    lib.moda_b200_fwd.restype = ctypes.c_int
+    lib.moda_b200_bwd_workspace_bytes.argtypes = [P, ctypes.POINTER(ctypes.c_size_t)]
+    lib.moda_b200_bwd_workspace_bytes.restype = ctypes.c_int
+    lib.moda_b200_bwd.argtypes = [P] + [T] * 6 + [V] + [T] * 6 + [V, ctypes.c_size_t, V]
+    lib.moda_b200_bwd.restype = ctypes.c_int
+    lib.moda_b200_check_problem.argtypes = [P]
+    lib.moda_b200_check_problem.restype = ctypes.c_int
+    lib.moda_b200_resolve_path.argtypes = [P, ctypes.c_int]
+    lib.moda_b200_resolve_path.restype = ctypes.c_int
+    lib.moda_b200_last_launch_count.restype = ctypes.c_int
+    lib.moda_b200_last_cuda_error.restype = ctypes.c_int
+    lib.moda_b200_status_string.argtypes = [ctypes.c_int]
+    lib.moda_b200_status_string.restype = ctypes.c_char_p
+    lib.moda_b200_version.restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+def status_string(status: int) -> str:
+    return load().moda_b200_status_string(int(status)).decode()
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        lib = load()
+        cuda_err = lib.moda_b200_last_cuda_error() if status == 9 else 0
+        extra = f" (cudaError {cuda_err})" if cuda_err else ""
+        raise ModaLibraryError(f"{what}: {status_string(status)}{extra}", status, cuda_err)

@@ -1,0 +1,92 @@
+// Shared definitions of the MoDA kernels: the launch parameter block, the visibility
+// rule (one place for every mask in the library), and small device primitives.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace moda {
+
+enum Mode : int { kCausal = 0, kNonCausal = 1, kChunkVisible = 2, kDepthOnly = 3 };
+
+// Element strides of a [B, T, H, D] tensor (innermost stride 1).
+struct View {
+  void* ptr;
+  int64_t sb, st, sh;
+  __host__ __device__ __forceinline__ int64_t off(int b, int64_t t, int h) const {
+    return (int64_t)b * sb + t * st + (int64_t)h * sh;
+  }
+};
+
+struct Params {
+  View q, k, v, kd, vd, o;          // forward
+  View dout, dq, dk, dv, dkd, dvd;  // backward
+  float* lse;                       // [B, T_q, H] fp32 (base-2)
+  float* delta;                     // [B, T_q, H] fp32 rowsum(o * dout)
+  int B, H, T_kv, T_q, G, L;
+  int mode;
+  int Cb;                           // chunk-visible: base positions per chunk (chunk_rows / G)
+  float scale;                      // softmax scale
+  float scale_log2;                 // scale * log2(e); reference constant 1.4426950216 (moda_v14.py:109)
+};
+
+// ---------------------------------------------------------------------------
+// Visibility.  A query row r (base position t = r / G) sees
+//   sequence key j     iff  seq_lo <= j < seq_hi
+//   depth row c=t'*L+l iff  dep_lo <= c < dep_hi
+// Both intervals are monotone non-decreasing in r, which the kernels rely on to
+// derive tile ranges from a tile's first and last row.
+//   causal / chunk-visible: seq [0, t+1)            moda_v14.py:250, moda_v16.py:2553
+//   non-causal:             seq [0, T_kv)           moda_v14.py:259-300
+//   own-position depth:     dep [t*L, (t+1)*L)      moda_v14.py:352-356
+//   chunk-visible depth:    dep [chunk_start(t)*L, (t+1)*L)   moda_v16.py:325-328
+// Rows r >= T_q see nothing.
+// ---------------------------------------------------------------------------
+__host__ __device__ __forceinline__ void seq_interval(const Params& p, int r, int& lo, int& hi) {
+  lo = 0;
+  if (r >= p.T_q || p.mode == kDepthOnly) { hi = 0; return; }
+  hi = (p.mode == kNonCausal) ? p.T_kv : (r / p.G + 1);
+}
+__host__ __device__ __forceinline__ void dep_interval(const Params& p, int r, int& lo, int& hi) {
+  if (r >= p.T_q || p.L == 0) { lo = 0; hi = 0; return; }
+  const int t = r / p.G;
+  const int t0 = (p.mode == kChunkVisible) ? (t / p.Cb) * p.Cb : t;
+  lo = t0 * p.L;
+  hi = (t + 1) * p.L;
+}
+
+// ---------------------------------------------------------------------------
+// dtype traits
+// ---------------------------------------------------------------------------
+template <typename T> struct Pack;
+template <> struct Pack<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  }
+};
+template <> struct Pack<__half> {
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+}  // namespace moda

@@ -1,0 +1,289 @@
+// C ABI of libmoda_b200.so: argument validation, parameter-block set-up and kernel
+// dispatch.  Declarations and the reference functions each entry point replaces are
+// in include/moda_b200.h.  No torch headers; pure CUDA runtime.
+#include "../../include/moda_b200.h"
+
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "simt_mma_kernels.cuh"
+#ifndef MODA_NO_TCGEN05
+#include "tc_kernels.cuh"
+#endif
+
+namespace {
+
+using namespace moda;
+
+thread_local int g_last_launches = 0;
+thread_local int g_last_cuda_error = 0;
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_tensor(const moda_tensor4* t, bool required) {
+  if (t == nullptr || t->data == nullptr) return required ? MODA_ERR_NULL : MODA_OK;
+  if (!aligned16(t->data)) return MODA_ERR_ALIGNMENT;
+  if ((t->stride_b % 8) || (t->stride_t % 8) || (t->stride_h % 8)) return MODA_ERR_ALIGNMENT;
+  return MODA_OK;
+}
+
+View to_view(const moda_tensor4* t) {
+  View v{nullptr, 0, 0, 0};
+  if (t != nullptr) { v.ptr = t->data; v.sb = t->stride_b; v.st = t->stride_t; v.sh = t->stride_h; }
+  return v;
+}
+
+int check_problem(const moda_problem* pr) {
+  if (pr == nullptr) return MODA_ERR_NULL;
+  if (pr->B < 1 || pr->T_kv < 1 || pr->H < 1 || pr->G < 1 || pr->L < 0) return MODA_ERR_SHAPE;
+  if (pr->B > 65535 || pr->H > 65535) return MODA_ERR_SHAPE;
+  if ((int64_t)pr->T_kv * pr->G > (int64_t)1 << 30) return MODA_ERR_SHAPE;
+  if ((int64_t)pr->T_kv * pr->L > (int64_t)1 << 30) return MODA_ERR_SHAPE;
+  if (pr->D != 64 && pr->D != 128) return MODA_ERR_HEAD_DIM;
+  if (pr->dtype != MODA_BF16 && pr->dtype != MODA_FP16) return MODA_ERR_DTYPE;
+  if (pr->mode < MODA_CAUSAL || pr->mode > MODA_DEPTH_ONLY) return MODA_ERR_MODE;
+  if (pr->mode == MODA_DEPTH_ONLY && pr->L < 1) return MODA_ERR_MODE;
+  if (pr->mode == MODA_CHUNK_VISIBLE) {
+    if (pr->chunk_rows < 1 || pr->chunk_rows % pr->G != 0) return MODA_ERR_CHUNK;
+  }
+  if (pr->path < MODA_PATH_AUTO || pr->path > MODA_PATH_TCGEN05) return MODA_ERR_MODE;
+  if (!(pr->scale == pr->scale)) return MODA_ERR_SHAPE;  // NaN scale
+  return MODA_OK;
+}
+
+void fill_common(Params& p, const moda_problem* pr) {
+  p.B = pr->B; p.H = pr->H; p.T_kv = pr->T_kv; p.T_q = pr->T_kv * pr->G; p.G = pr->G; p.L = pr->L;
+  p.mode = pr->mode;
+  p.Cb = (pr->mode == MODA_CHUNK_VISIBLE) ? pr->chunk_rows / pr->G : 1;
+  p.scale = pr->scale;
+  p.scale_log2 = pr->scale * 1.4426950216f;
+}
+
+int cuda_fail(cudaError_t e) { g_last_cuda_error = (int)e; return MODA_ERR_CUDA; }
+
+#define MODA_CUDA(x) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) return cuda_fail(e__); } while (0)
+
+template <typename K> int opt_in_smem(K kernel, size_t bytes) {
+  MODA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return MODA_OK;
+}
+
+// ----------------------------------------------------------------- mma.sync path
+template <typename T, int D>
+int simt_fwd(const Params& p, cudaStream_t st) {
+  auto kern = simt::fwd_kernel<T, D>;
+  constexpr size_t smem = simt::fwd_smem<T, D>();
+  if (int rc = opt_in_smem(kern, smem)) return rc;
+  dim3 grid((p.T_q + 63) / 64, p.H, p.B);
+  kern<<<grid, 128, smem, st>>>(p);
+  MODA_CUDA(cudaGetLastError());
+  g_last_launches += 1;
+  return MODA_OK;
+}
+
+template <typename T, int D>
+int simt_delta(const Params& p, cudaStream_t st) {
+  const int64_t rows = (int64_t)p.B * p.T_q * p.H;
+  int blocks = (int)((rows + 7) / 8);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  simt::delta_kernel<T, D><<<blocks, 256, 0, st>>>(p);
+  MODA_CUDA(cudaGetLastError());
+  g_last_launches += 1;
+  return MODA_OK;
+}
+
+template <typename T, int D>
+int simt_bwd(const Params& p, cudaStream_t st) {
+  if (int rc = simt_delta<T, D>(p, st)) return rc;
+  {
+    auto kern = simt::dq_kernel<T, D>;
+    constexpr size_t smem = simt::dq_smem<T, D>();
+    if (int rc = opt_in_smem(kern, smem)) return rc;
+    dim3 grid((p.T_q + 63) / 64, p.H, p.B);
+    kern<<<grid, 128, smem, st>>>(p);
+    MODA_CUDA(cudaGetLastError());
+    g_last_launches += 1;
+  }
+  {
+    auto kern = simt::dkv_kernel<T, D>;
+    constexpr size_t smem = simt::dkv_smem<T, D>();
+    if (int rc = opt_in_smem(kern, smem)) return rc;
+    const int n_seq = (p.mode == kDepthOnly) ? 0 : (p.T_kv + 63) / 64;
+    const int n_dep = (int)(((int64_t)p.T_kv * p.L + 63) / 64);
+    if (n_seq + n_dep > 0) {
+      dim3 grid(n_seq + n_dep, p.H, p.B);
+      kern<<<grid, 128, smem, st>>>(p, n_seq);
+      MODA_CUDA(cudaGetLastError());
+      g_last_launches += 1;
+    }
+  }
+  return MODA_OK;
+}
+
+template <typename T>
+int simt_fwd_d(const Params& p, int D, cudaStream_t st) {
+  return D == 64 ? simt_fwd<T, 64>(p, st) : simt_fwd<T, 128>(p, st);
+}
+template <typename T>
+int simt_bwd_d(const Params& p, int D, cudaStream_t st) {
+  return D == 64 ? simt_bwd<T, 64>(p, st) : simt_bwd<T, 128>(p, st);
+}
+
+int resolve_path(const moda_problem* pr, bool is_bwd) {
+#ifndef MODA_NO_TCGEN05
+  const bool ok = is_bwd ? tc::bwd_supported(pr) : tc::fwd_supported(pr);
+#else
+  const bool ok = false;
+#endif
+  if (pr->path == MODA_PATH_SIMT_MMA) return MODA_PATH_SIMT_MMA;
+  if (pr->path == MODA_PATH_TCGEN05) return ok ? MODA_PATH_TCGEN05 : -MODA_ERR_UNSUPPORTED;
+  return ok ? MODA_PATH_TCGEN05 : MODA_PATH_SIMT_MMA;
+}
+
+size_t delta_bytes(const moda_problem* pr) {
+  const size_t n = (size_t)pr->B * pr->T_kv * pr->G * pr->H * sizeof(float);
+  return (n + 255) & ~(size_t)255;
+}
+
+struct DeviceGuard {
+  int prev = -1; bool ok = true; cudaError_t err = cudaSuccess;
+  explicit DeviceGuard(int dev) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != dev) err = cudaSetDevice(dev);
+    ok = (err == cudaSuccess);
+  }
+  ~DeviceGuard() { int cur = -1; if (cudaGetDevice(&cur) == cudaSuccess && cur != prev && prev >= 0) cudaSetDevice(prev); }
+};
+
+}  // namespace
+
+extern "C" {
+
+int moda_b200_check_problem(const moda_problem* prob) { return check_problem(prob); }
+
+int moda_b200_resolve_path(const moda_problem* prob, int is_bwd) {
+  if (int rc = check_problem(prob)) return -rc;
+  return resolve_path(prob, is_bwd != 0);
+}
+
+int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_tensor4* k,
+                  const moda_tensor4* v, const moda_tensor4* depth_k, const moda_tensor4* depth_v,
+                  const moda_tensor4* o, float* lse, void* stream) {
+  if (int rc = check_problem(prob)) return rc;
+  const bool need_seq = prob->mode != MODA_DEPTH_ONLY;
+  const bool need_dep = prob->L > 0;
+  if (int rc = check_tensor(q, true)) return rc;
+  if (int rc = check_tensor(k, need_seq)) return rc;
+  if (int rc = check_tensor(v, need_seq)) return rc;
+  if (int rc = check_tensor(depth_k, need_dep)) return rc;
+  if (int rc = check_tensor(depth_v, need_dep)) return rc;
+  if (int rc = check_tensor(o, true)) return rc;
+  if (lse == nullptr) return MODA_ERR_NULL;
+  const int path = resolve_path(prob, false);
+  if (path < 0) return -path;
+
+  Params p{};
+  fill_common(p, prob);
+  p.q = to_view(q); p.k = to_view(need_seq ? k : nullptr); p.v = to_view(need_seq ? v : nullptr);
+  p.kd = to_view(need_dep ? depth_k : nullptr); p.vd = to_view(need_dep ? depth_v : nullptr);
+  p.o = to_view(o); p.lse = lse;
+
+  DeviceGuard guard(prob->device);
+  if (!guard.ok) return cuda_fail(guard.err);
+  g_last_launches = 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#ifndef MODA_NO_TCGEN05
+  if (path == MODA_PATH_TCGEN05) return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+#endif
+  return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)
+                                  : simt_fwd_d<__half>(p, prob->D, st);
+}
+
+int moda_b200_bwd_workspace_bytes(const moda_problem* prob, size_t* bytes) {
+  if (bytes == nullptr) return MODA_ERR_NULL;
+  if (int rc = check_problem(prob)) return rc;
+  size_t n = delta_bytes(prob);
+#ifndef MODA_NO_TCGEN05
+  n += tc::bwd_extra_workspace_bytes(prob);
+#endif
+  *bytes = n;
+  return MODA_OK;
+}
+
+int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_tensor4* k,
+                  const moda_tensor4* v, const moda_tensor4* depth_k, const moda_tensor4* depth_v,
+                  const moda_tensor4* o, const float* lse, const moda_tensor4* dout,
+                  const moda_tensor4* dq, const moda_tensor4* dk, const moda_tensor4* dv,
+                  const moda_tensor4* d_depth_k, const moda_tensor4* d_depth_v, void* workspace,
+                  size_t workspace_bytes, void* stream) {
+  if (int rc = check_problem(prob)) return rc;
+  const bool need_seq = prob->mode != MODA_DEPTH_ONLY;
+  const bool need_dep = prob->L > 0;
+  if (int rc = check_tensor(q, true)) return rc;
+  if (int rc = check_tensor(k, need_seq)) return rc;
+  if (int rc = check_tensor(v, need_seq)) return rc;
+  if (int rc = check_tensor(depth_k, need_dep)) return rc;
+  if (int rc = check_tensor(depth_v, need_dep)) return rc;
+  if (int rc = check_tensor(o, true)) return rc;
+  if (int rc = check_tensor(dout, true)) return rc;
+  if (int rc = check_tensor(dq, true)) return rc;
+  if (int rc = check_tensor(dk, need_seq)) return rc;
+  if (int rc = check_tensor(dv, need_seq)) return rc;
+  if (int rc = check_tensor(d_depth_k, need_dep)) return rc;
+  if (int rc = check_tensor(d_depth_v, need_dep)) return rc;
+  if (lse == nullptr) return MODA_ERR_NULL;
+  size_t need = 0;
+  if (int rc = moda_b200_bwd_workspace_bytes(prob, &need)) return rc;
+  if (workspace == nullptr || workspace_bytes < need) return MODA_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return MODA_ERR_ALIGNMENT;
+  const int path = resolve_path(prob, true);
+  if (path < 0) return -path;
+
+  Params p{};
+  fill_common(p, prob);
+  p.q = to_view(q); p.k = to_view(need_seq ? k : nullptr); p.v = to_view(need_seq ? v : nullptr);
+  p.kd = to_view(need_dep ? depth_k : nullptr); p.vd = to_view(need_dep ? depth_v : nullptr);
+  p.o = to_view(o); p.lse = const_cast<float*>(lse);
+  p.dout = to_view(dout); p.dq = to_view(dq);
+  p.dk = to_view(need_seq ? dk : nullptr); p.dv = to_view(need_seq ? dv : nullptr);
+  p.dkd = to_view(need_dep ? d_depth_k : nullptr); p.dvd = to_view(need_dep ? d_depth_v : nullptr);
+  p.delta = reinterpret_cast<float*>(workspace);
+
+  DeviceGuard guard(prob->device);
+  if (!guard.ok) return cuda_fail(guard.err);
+  g_last_launches = 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#ifndef MODA_NO_TCGEN05
+  if (path == MODA_PATH_TCGEN05) {
+    void* extra = reinterpret_cast<unsigned char*>(workspace) + delta_bytes(prob);
+    return tc::bwd(p, prob, extra, st, &g_last_launches, &g_last_cuda_error);
+  }
+#endif
+  return prob->dtype == MODA_BF16 ? simt_bwd_d<__nv_bfloat16>(p, prob->D, st)
+                                  : simt_bwd_d<__half>(p, prob->D, st);
+}
+
+int moda_b200_last_launch_count(void) { return g_last_launches; }
+int moda_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+const char* moda_b200_status_string(int status) {
+  switch (status) {
+    case MODA_OK: return "ok";
+    case MODA_ERR_NULL: return "required pointer is NULL";
+    case MODA_ERR_SHAPE: return "invalid shape";
+    case MODA_ERR_HEAD_DIM: return "head dim must be 64 or 128";
+    case MODA_ERR_DTYPE: return "dtype must be bf16 or fp16";
+    case MODA_ERR_ALIGNMENT: return "pointer or stride alignment";
+    case MODA_ERR_MODE: return "invalid mode";
+    case MODA_ERR_CHUNK: return "chunk_rows must be a positive multiple of G";
+    case MODA_ERR_WORKSPACE: return "workspace missing or too small";
+    case MODA_ERR_CUDA: return "CUDA call failed";
+    case MODA_ERR_UNSUPPORTED: return "kernel path does not support this problem";
+    case MODA_ERR_TOO_LARGE: return "problem exceeds the entry point's fixed capacity";
+    default: return "unknown status";
+  }
+}
+
+int moda_b200_version(void) { return 100; }
+
+}  // extern "C"

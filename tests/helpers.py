@@ -1,0 +1,41 @@
+"""Shared helpers of the test-suite: golden fixture loading and error metrics."""
+import glob
+import os
+
+import numpy as np
+import torch
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# Tolerances for bf16/fp16 kernels against the fp32 oracle on the same (rounded) inputs.
+TOL_O_MAX_ABS = 2e-2
+TOL_LSE_MAX_ABS = 1e-3
+TOL_GRAD_REL_L2 = 5e-2
+
+
+def golden_names():
+    return sorted(os.path.splitext(os.path.basename(p))[0]
+                  for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+
+
+def load_golden(name):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    rec = {k: z[k] for k in z.files}
+    seed, mode, B, T, H, D, L, G, cp = [int(x) for x in rec["meta"]]
+    scale = float(rec["scale"][0])
+    rec["cfg"] = dict(seed=seed, mode=mode, B=B, T_kv=T, H=H, D=D, L=L, G=G,
+                      chunk_positions=cp, scale=None if scale < 0 else scale)
+    return rec
+
+
+def max_abs(a, b):
+    return (a.double() - b.double()).abs().max().item()
+
+
+def rel_l2(a, b):
+    a, b = a.double(), b.double()
+    return ((a - b).pow(2).sum().sqrt() / (b.pow(2).sum().sqrt() + 1e-12)).item()
+
+
+def t(x):
+    return None if x is None else torch.from_numpy(np.asarray(x))

@@ -1,0 +1,128 @@
+"""CPU: the C-ABI library loads, exports every symbol the header declares, and its
+validation returns the documented status codes without touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib(built_library):
+    from moda_b200 import _cabi
+    return _cabi.load()
+
+
+def _declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for fn in os.listdir(inc):
+        if fn.endswith(".h"):
+            text = open(os.path.join(inc, fn)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(moda_b200_\w+)\s*\(", text))
+    return sorted(names)
+
+
+def test_every_declared_symbol_is_exported(lib):
+    from moda_b200 import _cabi
+    declared = _declared_symbols()
+    assert set(_cabi.EXPORTED_SYMBOLS) <= set(declared)
+    assert len(declared) >= 9
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def _prob(**kw):
+    from moda_b200._cabi import Problem
+    base = dict(B=1, T_kv=64, H=2, D=64, G=1, L=2, mode=0, chunk_rows=64, dtype=0, path=0,
+                scale=0.125, device=0)
+    base.update(kw)
+    return Problem(**base)
+
+
+@pytest.mark.parametrize("kw,code", [
+    ({}, 0),
+    ({"B": 0}, 2), ({"T_kv": 0}, 2), ({"L": -1}, 2), ({"G": 0}, 2),
+    ({"D": 96}, 3), ({"D": 256}, 3),
+    ({"dtype": 2}, 4),
+    ({"mode": 7}, 6), ({"mode": 3, "L": 0}, 6), ({"path": 5}, 6),
+    ({"mode": 2, "chunk_rows": 0}, 7), ({"mode": 2, "chunk_rows": 64, "G": 3}, 7),
+    ({"mode": 2, "chunk_rows": 64, "G": 4}, 0),
+])
+def test_check_problem_codes(lib, kw, code):
+    p = _prob(**kw)
+    assert lib.moda_b200_check_problem(ctypes.byref(p)) == code
+
+
+def test_null_and_alignment_are_rejected_before_any_launch(lib):
+    from moda_b200._cabi import Tensor4
+    p = _prob()
+    good = Tensor4(0x1000, 64 * 2 * 64, 2 * 64, 64)
+    null = Tensor4(0, 0, 0, 0)
+    odd = Tensor4(0x1008, 64 * 2 * 64, 2 * 64, 64)
+    bad_stride = Tensor4(0x1000, 64 * 2 * 64, 2 * 64 + 4, 64)
+    r = ctypes.byref
+    f = lib.moda_b200_fwd
+    assert f(r(p), r(null), r(good), r(good), r(good), r(good), r(good), 0x2000, None) == 1
+    assert f(r(p), r(good), r(good), r(good), None, r(good), r(good), 0x2000, None) == 1      # L>0 needs depth
+    assert f(r(p), r(good), r(good), r(good), r(good), r(good), r(good), None, None) == 1     # lse NULL
+    assert f(r(p), r(odd), r(good), r(good), r(good), r(good), r(good), 0x2000, None) == 5
+    assert f(r(p), r(good), r(bad_stride), r(good), r(good), r(good), r(good), 0x2000, None) == 5
+    pt = _prob(path=2, D=64)     # tcgen05 path forced on a problem it may not take -> unsupported or ok
+    assert lib.moda_b200_resolve_path(r(pt), 0) in (2, -10)
+
+
+def test_workspace_size_and_bwd_rejects_small_workspace(lib):
+    from moda_b200._cabi import Tensor4
+    p = _prob(B=2, T_kv=100, H=3, G=2)
+    n = ctypes.c_size_t(0)
+    assert lib.moda_b200_bwd_workspace_bytes(ctypes.byref(p), ctypes.byref(n)) == 0
+    assert n.value >= 2 * 200 * 3 * 4 and n.value % 256 == 0
+    g = Tensor4(0x1000, 8192, 64, 64)
+    r = ctypes.byref
+    rc = lib.moda_b200_bwd(r(p), r(g), r(g), r(g), r(g), r(g), r(g), 0x2000, r(g), r(g), r(g), r(g),
+                           r(g), r(g), 0x4000, 16, None)
+    assert rc == 8
+
+
+def test_status_strings(lib):
+    assert lib.moda_b200_status_string(0) == b"ok"
+    assert b"head dim" in lib.moda_b200_status_string(3)
+    assert lib.moda_b200_version() >= 100
+
+
+def test_python_wrappers_mirror_reference_assertions(built_library):
+    import moda_b200 as M
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16)
+    k = torch.zeros(1, 8, 3, 64, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="head-dimension GQA"):
+        M.parallel_moda(q, k, k, warn_shape=False)
+    k = torch.zeros(1, 4, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="T_q must equal T_kv"):
+        M.parallel_moda(q, k, k, warn_shape=False)
+    with pytest.raises(AssertionError, match="legacy k/v"):
+        M.parallel_fda(q, k, k)
+    with pytest.raises(AssertionError):
+        M.parallel_moda(q, q, q, g=torch.zeros(1, 8, 2), warn_shape=False)
+    # no CPU path: a CPU tensor is refused loudly, never computed some other way
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        M.parallel_moda(q, q, q, warn_shape=False)
+    with pytest.warns(UserWarning, match="head_first"):
+        with pytest.raises(RuntimeError):
+            M.parallel_moda(torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16),
+                            torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16),
+                            torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16))
+
+
+def test_product_package_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "moda_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for fn in files:
+            if fn.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, fn)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), fn
+                assert "moda_oracle" not in text, fn

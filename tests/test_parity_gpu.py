@@ -1,0 +1,199 @@
+"""GPU parity: the CUDA path (called through the Python mirror, i.e. through the
+C-ABI) against the CPU oracle on the same seeded inputs.
+
+Tolerances (bf16/fp16 inputs, fp32 oracle on the same rounded inputs):
+  max|o - o_ref| <= 2e-2, max|lse - lse_ref| <= 1e-3 (base-2 units),
+  every gradient rel-L2 <= 5e-2.
+The case grid covers the ranges of the reference's operator test
+(tests/ops/test_moda.py:95-198: T_kv 1..256 incl. odd, H 1..8, L 0..16,
+G in {1,2,4,8}, fp16/bf16, scales 0.0156..2.0) and adds what that test lacks:
+non-causal, chunk-visible, depth-only, lse, D=128, strided inputs.
+"""
+import itertools
+
+import pytest
+import torch
+
+from oracle import moda_oracle as mo
+from tests.helpers import (TOL_GRAD_REL_L2, TOL_LSE_MAX_ABS, TOL_O_MAX_ABS, golden_names,
+                           load_golden, max_abs, rel_l2, t)
+
+pytestmark = pytest.mark.gpu
+
+DT = {"bf16": torch.bfloat16, "fp16": torch.float16}
+
+
+def _run_case(M, mode, B, T, H, D, L, G, dtype, scale, seed, path=None, check_bwd=True, inputs=None):
+    dev = torch.device("cuda", 0)
+    if inputs is None:
+        inputs = mo.make_inputs(seed, B, T, H, D, L, G, dtype=dtype, with_seq=(mode != mo.MODE_DEPTH_ONLY))
+    q, k, v, kd, vd, dout = inputs
+    cp = max(64 // G, 1)
+    ref = mo.moda_attention_ref_grads(q, k, v, kd, vd, dout, scale, G, mode, cp)
+    leaves = [None if x is None else x.to(dev).requires_grad_(True) for x in (q, k, v, kd, vd)]
+    old = M.set_kernel_path(path if path is not None else M.PATH_AUTO)
+    try:
+        if mode == mo.MODE_DEPTH_ONLY:
+            o, lse = M.parallel_fda(leaves[0], cached_k=leaves[3], cached_v=leaves[4], scale=scale,
+                                    moda_group_num=G, need_lse=True, warn_shape=False)
+        elif mode == mo.MODE_CHUNK_VISIBLE:
+            o, lse = M.parallel_moda_chunk_visible(leaves[0], leaves[1], leaves[2], cached_k=leaves[3],
+                                                   cached_v=leaves[4], scale=scale, moda_group_num=G,
+                                                   need_lse=True, warn_shape=False)
+        else:
+            o, lse = M.parallel_moda(leaves[0], leaves[1], leaves[2], cached_k=leaves[3], cached_v=leaves[4],
+                                     scale=scale, moda_group_num=G, is_causal=(mode == mo.MODE_CAUSAL),
+                                     need_lse=True, warn_shape=False)
+        assert M.last_launch_count() >= 1
+        assert o.dtype == dtype and lse.dtype == torch.float32
+        eo, el = max_abs(o.float().cpu(), ref[0]), max_abs(lse.cpu(), ref[1])
+        assert eo <= TOL_O_MAX_ABS, f"o max-abs {eo}"
+        assert el <= TOL_LSE_MAX_ABS, f"lse max-abs {el}"
+        if check_bwd:
+            (o.float() * dout.to(dev).float()).sum().backward()
+            for name, leaf, g_ref in zip(("dq", "dk", "dv", "d_depth_k", "d_depth_v"), leaves, ref[2:]):
+                if leaf is None:
+                    continue
+                assert leaf.grad is not None and leaf.grad.dtype == dtype, name
+                e = rel_l2(leaf.grad.float().cpu(), g_ref)
+                assert e <= TOL_GRAD_REL_L2, f"{name} rel-L2 {e}"
+    finally:
+        M.set_kernel_path(old)
+    return o, lse
+
+
+@pytest.fixture(scope="module")
+def M(built_library):
+    import moda_b200
+    assert torch.cuda.is_available()
+    return moda_b200
+
+
+# (B, T_kv, H, L, G, dtype, scale) — causal own-position MoDA, D = 64
+CAUSAL_CASES = [
+    (1, 1, 1, 0, 1, "fp16", None), (1, 2, 2, 0, 2, "fp16", None), (2, 3, 2, 1, 2, "fp16", 1.0),
+    (1, 63, 1, 0, 1, "fp16", 1.0), (1, 64, 2, 1, 1, "fp16", None), (1, 65, 2, 0, 4, "fp16", None),
+    (2, 47, 3, 2, 2, "fp16", 0.5), (2, 95, 4, 4, 1, "fp16", None), (3, 80, 3, 0, 2, "fp16", None),
+    (2, 111, 5, 4, 1, "fp16", 1.0), (1, 32, 2, 8, 2, "fp16", None), (1, 40, 2, 8, 4, "fp16", 0.25),
+    (1, 129, 6, 3, 2, "fp16", 0.0156), (1, 191, 7, 5, 1, "fp16", 2.0), (1, 193, 2, 16, 1, "fp16", None),
+    (2, 256, 4, 4, 2, "fp16", 1.0), (1, 128, 8, 12, 8, "fp16", None), (2, 192, 4, 0, 4, "fp16", 0.1),
+    (1, 160, 2, 8, 2, "bf16", 0.1), (1, 128, 2, 8, 4, "bf16", 0.1), (1, 63, 2, 4, 2, "bf16", None),
+    (2, 80, 3, 4, 4, "bf16", 0.1), (1, 255, 1, 7, 8, "bf16", None), (1, 64, 2, 0, 2, "bf16", None),
+    (1, 33, 2, 1, 8, "bf16", 0.5), (1, 200, 3, 16, 1, "bf16", None),
+]
+
+
+@pytest.mark.parametrize("B,T,H,L,G,dt,scale", CAUSAL_CASES)
+def test_causal_moda_d64(M, B, T, H, L, G, dt, scale):
+    _run_case(M, mo.MODE_CAUSAL, B, T, H, 64, L, G, DT[dt], scale, seed=2025 + T + L)
+
+
+@pytest.mark.parametrize("mode", [mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE, mo.MODE_DEPTH_ONLY])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T,L,G", [(1, 1, 1), (70, 3, 1), (197, 11, 1), (128, 4, 4), (130, 2, 2), (96, 5, 8)])
+def test_all_modes(M, mode, D, T, L, G):
+    _run_case(M, mode, 2, T, 2, D, L, G, torch.bfloat16, None, seed=7 + T + D)
+
+
+@pytest.mark.parametrize("mode", [mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE])
+def test_no_depth(M, mode):
+    _run_case(M, mode, 1, 150, 2, 128, 0, 2, torch.bfloat16, None, seed=3)
+
+
+@pytest.mark.parametrize("mode,T,L,G", [
+    (mo.MODE_CAUSAL, 1024, 24, 4),          # BASELINE config 2 shape at reduced T, B, H
+    (mo.MODE_CHUNK_VISIBLE, 1024, 32, 4),   # BASELINE config 4 shape at reduced T, H
+    (mo.MODE_CHUNK_VISIBLE, 512, 8, 1),
+    (mo.MODE_DEPTH_ONLY, 512, 32, 1),       # BASELINE config 3 shape at reduced B, T, H
+    (mo.MODE_CAUSAL, 640, 0, 1),
+])
+def test_config_shapes_reduced_d128(M, mode, T, L, G):
+    _run_case(M, mode, 1, T, 2, 128, L, G, torch.bfloat16, None, seed=11 + T)
+
+
+def test_deit_shape_noncausal(M):
+    # BASELINE config 5 at reduced batch: T=197, H=6, D=64, L=11, non-causal
+    _run_case(M, mo.MODE_NONCAUSAL, 3, 197, 6, 64, 11, 1, torch.bfloat16, None, seed=4)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_against_reference_golden_fixtures(M, name):
+    """Kernel vs outputs of the reference's own torch oracle (fp32 inputs rounded to
+    bf16 for the kernel, so the fixture is compared at bf16-input tolerance)."""
+    rec = load_golden(name)
+    c = rec["cfg"]
+    dev = torch.device("cuda", 0)
+    q, k, v, kd, vd, dout = mo.make_inputs(c["seed"], c["B"], c["T_kv"], c["H"], c["D"], c["L"], c["G"],
+                                           with_seq=(c["mode"] != mo.MODE_DEPTH_ONLY))
+    if c["mode"] == mo.MODE_CHUNK_VISIBLE and c["chunk_positions"] * c["G"] != 64:
+        pytest.skip("operator defines 64 query rows per chunk")
+    xs = [None if x is None else x.to(dev).to(torch.bfloat16) for x in (q, k, v, kd, vd)]
+    if c["mode"] == mo.MODE_DEPTH_ONLY:
+        o, lse = M.parallel_fda_fwd(xs[0], scale=c["scale"], cached_k=xs[3], cached_v=xs[4],
+                                    moda_group_num=c["G"])
+    elif c["mode"] == mo.MODE_CHUNK_VISIBLE:
+        o, lse = M.parallel_moda_chunk_visible_fwd(xs[0], xs[1], xs[2], scale=c["scale"], cached_k=xs[3],
+                                                   cached_v=xs[4], moda_group_num=c["G"])
+    else:
+        o, lse = M.parallel_moda_fwd(xs[0], xs[1], xs[2], scale=c["scale"], cached_k=xs[3], cached_v=xs[4],
+                                     moda_group_num=c["G"], is_causal=(c["mode"] == mo.MODE_CAUSAL))
+    # inputs were rounded to bf16 (rel 2^-9) before the kernel: allow that on top
+    assert max_abs(o.float().cpu(), t(rec["o"])) <= 6e-2
+    assert max_abs(lse.cpu(), t(rec["lse"])) <= 6e-2
+    # and exactly at kernel tolerance against the oracle on the rounded inputs
+    ro, rl = mo.moda_attention_ref(*[None if x is None else x.cpu() for x in xs], c["scale"], c["G"],
+                                   c["mode"], max(c["chunk_positions"], 1))
+    assert max_abs(o.float().cpu(), ro) <= TOL_O_MAX_ABS
+    assert max_abs(lse.cpu(), rl) <= TOL_LSE_MAX_ABS
+
+
+def test_bitwise_reproducible(M):
+    dev = torch.device("cuda", 0)
+    q, k, v, kd, vd, dout = [x.to(dev) for x in mo.make_inputs(21, 2, 300, 2, 128, 6, 4, dtype=torch.bfloat16)]
+    outs = []
+    for _ in range(2):
+        o, lse = M.parallel_moda_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=4)
+        grads = M.parallel_moda_bwd(q, k, v, o, None, lse, dout, cached_k=kd, cached_v=vd, moda_group_num=4)
+        outs.append([o, lse] + [g for g in grads if g is not None])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+def test_strided_head_slice_inputs_are_consumed_in_place(M):
+    """A KV-head shard of a [B,T,H,D] tensor is a non-contiguous view; the library takes
+    element strides, so no copy is needed and the result equals the contiguous call."""
+    dev = torch.device("cuda", 0)
+    q, k, v, kd, vd, _ = [x.to(dev) for x in mo.make_inputs(31, 2, 100, 4, 64, 3, 2, dtype=torch.bfloat16)]
+    o_full, lse_full = M.parallel_moda_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=2)
+    sl = slice(1, 3)
+    o_s, lse_s = M.parallel_moda_fwd(q[:, :, sl], k[:, :, sl], v[:, :, sl], cached_k=kd[:, :, sl],
+                                     cached_v=vd[:, :, sl], moda_group_num=2)
+    assert torch.equal(o_s, o_full[:, :, sl]) and torch.equal(lse_s, lse_full[:, :, sl])
+
+
+def test_unfolded_convenience_form(M):
+    dev = torch.device("cuda", 0)
+    B, T, Hkv, G, D, L = 2, 90, 2, 4, 64, 3
+    gen = torch.Generator().manual_seed(5)
+    q = torch.randn(B, T, G * Hkv, D, generator=gen).to(torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, generator=gen).to(torch.bfloat16)
+    dk_ = torch.randn(B, T, L, Hkv, D, generator=gen).to(torch.bfloat16)
+    dv_ = torch.randn(B, T, L, Hkv, D, generator=gen).to(torch.bfloat16)
+    o, lse = M.moda_attention(q.to(dev), k.to(dev), v.to(dev), dk_.to(dev), dv_.to(dev), is_causal=True)
+    assert o.shape == (B, T, G * Hkv, D) and lse.shape == (B, T, G * Hkv)
+    # direct per-head formulation: query head hq = g*Hkv + h uses KV head h
+    for hq in (0, 3, 5):
+        h = hq % Hkv
+        ro, rl = mo.moda_attention_ref(q[:, :, hq:hq + 1], k[:, :, h:h + 1], v[:, :, h:h + 1],
+                                       dk_[:, :, :, h:h + 1].reshape(B, T * L, 1, D),
+                                       dv_[:, :, :, h:h + 1].reshape(B, T * L, 1, D), None, 1, mo.MODE_CAUSAL)
+        assert max_abs(o[:, :, hq:hq + 1].float().cpu(), ro) <= TOL_O_MAX_ABS
+        assert max_abs(lse[:, :, hq:hq + 1].cpu(), rl) <= TOL_LSE_MAX_ABS
+
+
+def test_errors_surface_as_exceptions(M):
+    dev = torch.device("cuda", 0)
+    q = torch.zeros(1, 8, 1, 96, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(M.ModaLibraryError, match="head dim"):
+        M.parallel_moda(q, q, q, warn_shape=False)
