@@ -11,6 +11,7 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TOL_O_MAX_ABS = 2e-2
 TOL_LSE_MAX_ABS = 1e-3
 TOL_GRAD_REL_L2 = 5e-2
+TOL_GRAD_MAX_ABS = 1e-2   # only for gradients whose oracle value is ~0
 
 
 def golden_names():

@@ -15,7 +15,7 @@ import pytest
 import torch
 
 from oracle import moda_oracle as mo
-from tests.helpers import (TOL_GRAD_REL_L2, TOL_LSE_MAX_ABS, TOL_O_MAX_ABS, golden_names,
+from tests.helpers import (TOL_GRAD_MAX_ABS, TOL_GRAD_REL_L2, TOL_LSE_MAX_ABS, TOL_O_MAX_ABS, golden_names,
                            load_golden, max_abs, rel_l2, t)
 
 pytestmark = pytest.mark.gpu
@@ -56,7 +56,11 @@ def _run_case(M, mode, B, T, H, D, L, G, dtype, scale, seed, path=None, check_bw
                     continue
                 assert leaf.grad is not None and leaf.grad.dtype == dtype, name
                 e = rel_l2(leaf.grad.float().cpu(), g_ref)
-                assert e <= TOL_GRAD_REL_L2, f"{name} rel-L2 {e}"
+                ea = max_abs(leaf.grad.float().cpu(), g_ref)
+                # a gradient that is (near) zero in the oracle has no meaningful relative
+                # error; the reference's own rule accepts max-abs <= 1e-2 there
+                # (tests/ops/test_moda.py:84-92,298-299)
+                assert e <= TOL_GRAD_REL_L2 or ea <= TOL_GRAD_MAX_ABS, f"{name} rel-L2 {e} max-abs {ea}"
     finally:
         M.set_kernel_path(old)
     return o, lse
