@@ -1,0 +1,457 @@
+#!/usr/bin/env python
+"""Benchmark of the MoDA hot path: fwd+bwd TFLOP/s on BASELINE config 4.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+One "step" is one forward + backward pass of chunk-visible MoDA
+(``parallel_moda_chunk_visible``) over the whole workload: B=1, T=65536, Hq=32,
+Hkv=8 (G=4), D=128, L=32, chunk of 64 query rows, bf16, seeded N(0,1) synthetic
+inputs.  With N GPUs the 8 KV heads are split contiguously over the ranks (strong
+scaling: total work is fixed), no collective in the timed region; per-head checksums
+are all-gathered afterwards for validation only.
+
+Prints ONE JSON line (rank 0).  ``value`` is algorithmic TFLOP/s (14*D*pairs per
+step; masked, padded and recomputed work is never counted) with inputs resident in
+HBM; ``e2e`` is the same metric through the public autograd operator with HOST
+buffers (pinned), host->device copies of all inputs and device->host copies of all
+results inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (mode, B, T_kv, Hkv, G, D, L)
+    "config4_chunk_visible_T65536": ("chunk", 1, 65536, 8, 4, 128, 32),
+    "config2_causal_T4096": ("causal", 2, 4096, 4, 4, 128, 24),
+    "config3_fda_T8192": ("fda", 8, 8192, 16, 1, 128, 32),
+    "config5_deit_noncausal_T197": ("noncausal", 256, 197, 6, 1, 64, 11),
+    "small_chunk_visible_T8192": ("chunk", 1, 8192, 8, 4, 128, 32),
+}
+DEFAULT_WORKLOAD = "config4_chunk_visible_T65536"
+CHUNK_ROWS = 64
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel on the default
+# workload, from the ncu captures summarised under profiles/ (None = not captured).
+NCU_TRAFFIC_BYTES = {}
+
+# share of the backward's 10*D*pairs algorithmic FLOPs attributed to each backward
+# kernel (dq kernel runs 3 of the 7 executed matmuls, dk/dv kernel 4 of 7)
+BWD_SHARE = {"simt_dq": 3.0 / 7.0, "simt_dkv": 4.0 / 7.0, "tc_dq": 3.0 / 7.0, "tc_dkv": 4.0 / 7.0}
+
+
+def pairs(mode, B, T, Hkv, G, L):
+    """Visible (query, key) pairs; the unit of algorithmic work."""
+    Hq = Hkv * G
+    if mode == "fda":
+        seq = 0
+    elif mode == "noncausal":
+        seq = T * T
+    else:
+        seq = T * (T + 1) // 2
+    if mode == "chunk":
+        cb = CHUNK_ROWS // G
+        # positions p of a chunk see p - chunk_start + 1 positions' depth rows
+        full, rem = divmod(T, cb)
+        dep = L * (full * cb * (cb + 1) // 2 + rem * (rem + 1) // 2)
+    else:
+        dep = T * L
+    return B * Hq * (seq + dep)
+
+
+def flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=True):
+    p = pairs(mode, B, T, Hkv, G, L)
+    return (4 * D * p if fwd else 0) + (10 * D * p if bwd else 0)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        return {"tflops": float(m.get("bf16_tflops_sustained", m.get("bf16_tflops"))),
+                "tflops_burst": float(m.get("bf16_tflops")), "hbm_gbs": float(m["hbm_gbs"]),
+                "source": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_shard(mode, T, G, D, L, units, H, seed, device, dtype=torch.bfloat16):
+    """Per-rank contiguous tensors [1, T*, n_units, D]; each (tensor, b, h) unit has its own
+    seeded stream so the data do not depend on the number of ranks.  A rank's units may
+    span batch rows; they are stored along the head axis of a batch-1 tensor (units are
+    independent, so this is only a layout of the shard)."""
+    from moda_b200.sharding import unit_seed
+    n = len(units)
+    shapes = {"q": T * G, "k": T, "v": T, "kd": T * L, "vd": T * L, "dout": T * G}
+    out = {}
+    for tid, (name, rows) in enumerate(shapes.items()):
+        if mode == "fda" and name in ("k", "v"):
+            out[name] = None
+            continue
+        if rows == 0:
+            out[name] = None
+            continue
+        x = torch.empty(1, rows, n, D, dtype=dtype, device=device)
+        for i, u in enumerate(range(units.start, units.stop)):
+            g = torch.Generator(device=device).manual_seed(unit_seed(seed, tid, u))
+            x[0, :, i] = torch.randn(rows, D, generator=g, device=device, dtype=torch.float32).to(dtype)
+        out[name] = x
+    return out
+
+
+def op_fwd_bwd(M, mode, t, G):
+    if mode == "chunk":
+        o, lse = M.parallel_moda_chunk_visible_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+        n = M.last_launch_count()
+        g = M.parallel_moda_chunk_visible_bwd(t["q"], t["k"], t["v"], o, None, lse, t["dout"], cached_k=t["kd"],
+                                              cached_v=t["vd"], moda_group_num=G)
+    elif mode == "fda":
+        o, lse = M.parallel_fda_fwd(t["q"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+        n = M.last_launch_count()
+        g = M.parallel_fda_bwd(t["q"], o, None, lse, t["dout"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+    else:
+        causal = mode == "causal"
+        o, lse = M.parallel_moda_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G, is_causal=causal)
+        n = M.last_launch_count()
+        g = M.parallel_moda_bwd(t["q"], t["k"], t["v"], o, None, lse, t["dout"], cached_k=t["kd"], cached_v=t["vd"],
+                                moda_group_num=G, is_causal=causal)
+    n += M.last_launch_count()
+    return o, lse, [x for x in g if x is not None], n
+
+
+def op_autograd(M, mode, leaves, dout, G):
+    q, k, v, kd, vd = leaves
+    if mode == "chunk":
+        o, lse = M.parallel_moda_chunk_visible(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=G, need_lse=True, warn_shape=False)
+    elif mode == "fda":
+        o, lse = M.parallel_fda(q, cached_k=kd, cached_v=vd, moda_group_num=G, need_lse=True, warn_shape=False)
+    else:
+        o, lse = M.parallel_moda(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=G, is_causal=(mode == "causal"),
+                                 need_lse=True, warn_shape=False)
+    o.backward(dout)
+    return o, lse
+
+
+def cpu_reference_sample(mode, G, D, L, T_sample, threads=None):
+    """Times the CPU oracle (the reference's torch algorithm, fp32) forward+backward on ONE
+    (batch, KV-head) unit at sequence length T_sample; returns (seconds, flops, description)."""
+    from oracle import moda_oracle as mo
+    if threads:
+        torch.set_num_threads(threads)
+    omode = {"chunk": mo.MODE_CHUNK_VISIBLE, "causal": mo.MODE_CAUSAL, "noncausal": mo.MODE_NONCAUSAL,
+             "fda": mo.MODE_DEPTH_ONLY}[mode]
+    q, k, v, kd, vd, dout = mo.make_inputs(3, 1, T_sample, 1, D, L, G, with_seq=(mode != "fda"))
+    t0 = time.perf_counter()
+    mo.moda_attention_ref_grads(q, k, v, kd, vd, dout, None, G, omode, max(CHUNK_ROWS // G, 1))
+    dt = time.perf_counter() - t0
+    fl = flops(mode, 1, T_sample, 1, G, D, L)
+    desc = (f"oracle fwd+bwd (autograd), fp32, one (batch, KV-head) unit, T={T_sample}, G={G}, D={D}, L={L}, "
+            f"{mode}; {torch.get_num_threads()} torch threads of {os.cpu_count()} host CPUs")
+    return dt, fl, desc
+
+
+def run_reference_arm(args, wl):
+    """--impl reference: the reference's own CPU implementation of the path.  The reference
+    is Python/torch and cannot travel to the GPU box, so the timed code is the oracle port
+    of its torch functions, on all host threads, on a bounded sample of the workload."""
+    mode, B, T, Hkv, G, D, L = wl
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T_s = min(T, args.cpu_sample_T)
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_sample(mode, G, D, L, max(256, T_s // 8))
+    times = []
+    fl = desc = None
+    for _ in range(args.steps):
+        dt, fl, desc = cpu_reference_sample(mode, G, D, L, T_s)
+        times.append(dt)
+    total = sum(times)
+    val = fl * len(times) / total / 1e12
+    line = {
+        "impl": "reference", "metric": "MoDA fwd+bwd TFLOP/s (bf16, T=64K, L=32)", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "mode": mode, "B": B, "T": T, "Hkv": Hkv, "G": G, "D": D, "L": L,
+                   "note": "CPU oracle port of the reference torch path, bounded sample"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": desc},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--cpu-sample-T", type=int, default=4096)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fwd-only", action="store_true", help="time forward only (exploration; not the headline)")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    mode, B, T, Hkv, G, D, L = wl
+
+    if args.impl == "reference":
+        run_reference_arm(args, wl)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit("launch multi-GPU runs with torch.distributed.run --nproc-per-node N (one rank per GPU)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from moda_b200 import build
+    build.build()
+    import moda_b200 as M
+    from moda_b200 import _cabi
+    from moda_b200.sharding import gather_units, partition_units
+    M.set_kernel_path({"auto": M.PATH_AUTO, "simt": M.PATH_SIMT_MMA, "tcgen05": M.PATH_TCGEN05}[args.path])
+
+    n_units = B * Hkv
+    units = partition_units(n_units, world, rank)
+    t = make_shard(mode, T, G, D, L, units, Hkv, seed=3, device=device)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step_flops_total = flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=not args.fwd_only)
+
+    def one_step():
+        if args.fwd_only:
+            if mode == "chunk":
+                o, lse = M.parallel_moda_chunk_visible_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+            elif mode == "fda":
+                o, lse = M.parallel_fda_fwd(t["q"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+            else:
+                o, lse = M.parallel_moda_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G,
+                                             is_causal=(mode == "causal"))
+            return o, lse, [], M.last_launch_count()
+        return op_fwd_bwd(M, mode, t, G)
+
+    launches = 0
+    if len(units) > 0:
+        for _ in range(args.warmup):
+            one_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    _cabi.profile_begin()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    o = lse = None
+    for _ in range(args.steps):
+        if len(units) > 0:
+            o, lse, grads, n = one_step()
+            launches += n
+    ev1.record()
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    prof = _cabi.profile_end()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        tt = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(tt.item())
+        lt = torch.tensor([launches], device=device, dtype=torch.int64)
+        dist.all_reduce(lt, op=dist.ReduceOp.SUM)
+        launches = int(lt.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = step_flops_total / (ms_per_step * 1e-3) / 1e12
+
+    # validation gather (untimed): per-unit checksums, identical for every N
+    if len(units) > 0 and o is not None:
+        cs = torch.stack([o.float().sum(dim=(0, 1, 3)), lse.sum(dim=(0, 1))], dim=1).double()
+    else:
+        cs = torch.zeros(0, 2, dtype=torch.float64, device=device)
+    cs_all = gather_units(cs, n_units, world, rank)
+
+    # ---- roofline of the dominant kernel (rank 0's shard) -------------------------------
+    pk = peaks()
+    roofline = None
+    if prof:
+        name, (cnt, tot_ms) = max(prof.items(), key=lambda kv: kv[1][1])
+        shard_frac = len(units) / n_units
+        p_sh = pairs(mode, B, T, Hkv, G, L) * shard_frac
+        if name in ("simt_fwd", "tc_fwd", "fda_fwd"):
+            alg = 4 * D * p_sh
+        elif name in BWD_SHARE:
+            alg = 10 * D * p_sh * BWD_SHARE[name]
+        else:
+            alg = 10 * D * p_sh
+        avg_ms = tot_ms / cnt
+        if mode in ("fda",):
+            e = 2
+            by = (2 * T * G * D * e + 2 * T * L * D * e) * B * Hkv * shard_frac
+            ach = by / (avg_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                        "frac": ach / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": pk["source"]}
+        else:
+            ach = alg / (avg_ms * 1e-3) / 1e12
+            roofline = {"bound": "tensor", "kernel": name, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
+                        "frac": ach / pk["tflops"], "traffic": NCU_TRAFFIC_BYTES.get(name),
+                        "peak_source": pk["source"] + " (sustained cuBLAS bf16)", "avg_launch_ms": avg_ms,
+                        "kernels": {k: {"launches": c, "total_ms": round(m, 3)} for k, (c, m) in prof.items()}}
+
+    # ---- end-to-end through the public autograd operator with host buffers -------------
+    e2e = None
+    if not args.no_e2e and not args.fwd_only and len(units) > 0:
+        try:
+            names = ["q", "k", "v", "kd", "vd"]
+            host = {n: (t[n].cpu().pin_memory() if t[n] is not None else None) for n in names + ["dout"]}
+            leaves = [None if t[n] is None else torch.empty_like(t[n]).requires_grad_(True) for n in names]
+            dout_d = torch.empty_like(t["dout"])
+            res_host = None
+            h2d = sum(x.numel() * x.element_size() for x in host.values() if x is not None)
+
+            def e2e_step():
+                nonlocal res_host
+                with torch.no_grad():
+                    for n, leaf in zip(names, leaves):
+                        if leaf is not None:
+                            leaf.copy_(host[n], non_blocking=True)
+                            leaf.grad = None
+                    dout_d.copy_(host["dout"], non_blocking=True)
+                o2, lse2 = op_autograd(M, mode, leaves, dout_d, G)
+                outs = [o2.detach(), lse2] + [l.grad for l in leaves if l is not None]
+                if res_host is None:
+                    res_host = [torch.empty(x.shape, dtype=x.dtype, pin_memory=True) for x in outs]
+                for d, s in zip(res_host, outs):
+                    d.copy_(s, non_blocking=True)
+                return sum(x.numel() * x.element_size() for x in outs)
+
+            d2h = e2e_step()
+            barrier()
+            n_e2e = max(1, min(args.steps, 2))
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n_e2e):
+                e2e_step()
+            b.record()
+            barrier()
+            ems = a.elapsed_time(b)
+            if world > 1:
+                tt = torch.tensor([ems], device=device, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                ems = float(tt.item())
+            e2e = {"value": step_flops_total / (ems / n_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                   "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": n_e2e,
+                   "ms_per_step": ems / n_e2e, "note": "per-rank bytes; pinned host buffers"}
+            del host, leaves, res_host
+        except RuntimeError as exc:  # e.g. host cannot pin this much memory
+            e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                   "error": str(exc)[:200]}
+    elif world > 1:
+        barrier()
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        dt, fl, desc = cpu_reference_sample(mode, G, D, L, min(T, args.cpu_sample_T))
+        cpu_baseline = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                        "sample": desc, "seconds": dt}
+
+    if rank == 0:
+        line = {
+            "metric": "MoDA fwd+bwd TFLOP/s (bf16, T=64K, L=32)" if not args.fwd_only else "MoDA fwd TFLOP/s",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "mode": mode, "B": B, "T": T, "Hq": Hkv * G, "Hkv": Hkv, "G": G,
+                       "D": D, "L": L, "chunk_rows": CHUNK_ROWS, "sharding": f"kv-head x{world}",
+                       "l2": "inputs larger than L2 (no flush needed)", "kernel_path": args.path,
+                       "flops_per_step": step_flops_total},
+            "tokens_per_s": B * T / (ms_per_step * 1e-3),
+            "frac_of_nominal_bf16_peak": value / (2250.0 * world),
+            "frac_of_measured_bf16_peak": value / (pk["tflops"] * world),
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks,
+            "validation": {"per_unit_checksum_o_lse": [[round(float(a), 3), round(float(b), 3)] for a, b in cs_all.tolist()]},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -129,6 +129,18 @@ int moda_b200_check_problem(const moda_problem *prob);
  * or backward (is_bwd=1): MODA_PATH_SIMT_MMA or MODA_PATH_TCGEN05; <0 on bad input. */
 int moda_b200_resolve_path(const moda_problem *prob, int is_bwd);
 
+/*
+ * Per-kernel device timing.  Between profile_begin and profile_end every kernel this
+ * library launches is bracketed by cudaEvents on its launch stream; profile_end waits
+ * for them and returns, per kernel id that ran, its launch count and summed duration.
+ * Replaces the reference's torch.cuda.Event timing loops (moda_v14.py:3054-3078), at
+ * kernel granularity.  Not for use inside stream capture.
+ */
+int moda_b200_profile_begin(void);
+int moda_b200_profile_end(int max_entries, int *n_entries, int *kernel_ids, int *launches,
+                          float *total_ms);
+const char *moda_b200_kernel_name(int kernel_id);
+
 /* Number of kernel launches the last successful call on this host thread issued. */
 int moda_b200_last_launch_count(void);
 

@@ -24,6 +24,9 @@ EXPORTED_SYMBOLS = (
     "moda_b200_bwd",
     "moda_b200_check_problem",
     "moda_b200_resolve_path",
+    "moda_b200_profile_begin",
+    "moda_b200_profile_end",
+    "moda_b200_kernel_name",
     "moda_b200_last_launch_count",
     "moda_b200_last_cuda_error",
     "moda_b200_status_string",
@@ -89,6 +92,12 @@ def load() -> ctypes.CDLL:
     lib.moda_b200_check_problem.restype = ctypes.c_int
     lib.moda_b200_resolve_path.argtypes = [P, ctypes.c_int]
     lib.moda_b200_resolve_path.restype = ctypes.c_int
+    IP, FP = ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_float)
+    lib.moda_b200_profile_begin.restype = ctypes.c_int
+    lib.moda_b200_profile_end.argtypes = [ctypes.c_int, IP, IP, IP, FP]
+    lib.moda_b200_profile_end.restype = ctypes.c_int
+    lib.moda_b200_kernel_name.argtypes = [ctypes.c_int]
+    lib.moda_b200_kernel_name.restype = ctypes.c_char_p
     lib.moda_b200_last_launch_count.restype = ctypes.c_int
     lib.moda_b200_last_cuda_error.restype = ctypes.c_int
     lib.moda_b200_status_string.argtypes = [ctypes.c_int]
@@ -108,3 +117,18 @@ def check(status: int, what: str) -> None:
         cuda_err = lib.moda_b200_last_cuda_error() if status == 9 else 0
         extra = f" (cudaError {cuda_err})" if cuda_err else ""
         raise ModaLibraryError(f"{what}: {status_string(status)}{extra}", status, cuda_err)
+
+
+def profile_begin() -> None:
+    check(load().moda_b200_profile_begin(), "moda_b200_profile_begin")
+
+
+def profile_end() -> dict:
+    """{kernel name: (launches, total_ms)} for the kernels launched since profile_begin."""
+    lib = load()
+    n = ctypes.c_int(0)
+    ids = (ctypes.c_int * 16)()
+    cnt = (ctypes.c_int * 16)()
+    ms = (ctypes.c_float * 16)()
+    check(lib.moda_b200_profile_end(16, ctypes.byref(n), ids, cnt, ms), "moda_b200_profile_end")
+    return {lib.moda_b200_kernel_name(ids[i]).decode(): (int(cnt[i]), float(ms[i])) for i in range(n.value)}
