@@ -252,7 +252,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05"])
-    ap.add_argument("--cpu-sample-T", type=int, default=4096)
+    ap.add_argument("--cpu-sample-T", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fwd-only", action="store_true", help="time forward only (exploration; not the headline)")

@@ -141,6 +141,16 @@ int moda_b200_profile_end(int max_entries, int *n_entries, int *kernel_ids, int 
                           float *total_ms);
 const char *moda_b200_kernel_name(int kernel_id);
 
+/*
+ * Device-side status of the tcgen05 kernels.  Every wait inside those kernels (on an
+ * mbarrier fed by TMA, by the tensor core or by other warps) is bounded; a wait that
+ * expires records (1 << 8 | barrier id) here, the CTA releases its TMEM and returns,
+ * and the remaining CTAs of the launch return at once.  0 means no wait has expired
+ * since the last launch began.  SYNCHRONISES the device.  The reference has no
+ * counterpart (Triton kernels do not spin on barriers they could miss).
+ */
+int moda_b200_device_status(int *status);
+
 /* Number of kernel launches the last successful call on this host thread issued. */
 int moda_b200_last_launch_count(void);
 

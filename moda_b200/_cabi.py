@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "moda_b200_profile_begin",
     "moda_b200_profile_end",
     "moda_b200_kernel_name",
+    "moda_b200_device_status",
     "moda_b200_last_launch_count",
     "moda_b200_last_cuda_error",
     "moda_b200_status_string",
@@ -98,6 +99,8 @@ def load() -> ctypes.CDLL:
     lib.moda_b200_profile_end.restype = ctypes.c_int
     lib.moda_b200_kernel_name.argtypes = [ctypes.c_int]
     lib.moda_b200_kernel_name.restype = ctypes.c_char_p
+    lib.moda_b200_device_status.argtypes = [IP]
+    lib.moda_b200_device_status.restype = ctypes.c_int
     lib.moda_b200_last_launch_count.restype = ctypes.c_int
     lib.moda_b200_last_cuda_error.restype = ctypes.c_int
     lib.moda_b200_status_string.argtypes = [ctypes.c_int]
@@ -132,3 +135,10 @@ def profile_end() -> dict:
     ms = (ctypes.c_float * 16)()
     check(lib.moda_b200_profile_end(16, ctypes.byref(n), ids, cnt, ms), "moda_b200_profile_end")
     return {lib.moda_b200_kernel_name(ids[i]).decode(): (int(cnt[i]), float(ms[i])) for i in range(n.value)}
+
+
+def device_status() -> int:
+    """Status word of the tcgen05 kernels' bounded waits (0 = none expired); synchronises."""
+    v = ctypes.c_int(0)
+    check(load().moda_b200_device_status(ctypes.byref(v)), "moda_b200_device_status")
+    return int(v.value)

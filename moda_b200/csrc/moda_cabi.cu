@@ -340,6 +340,30 @@ const char* moda_b200_kernel_name(int kernel_id) {
   return (kernel_id >= 0 && kernel_id < kKernCount) ? kKernelNames[kernel_id] : "unknown";
 }
 
+int moda_b200_device_status(int* status) {
+  if (status == nullptr) return MODA_ERR_NULL;
+#ifndef MODA_NO_TCGEN05
+  int v = 0;
+  const int e = tc::read_status(&v);
+  if (e != 0) { g_last_cuda_error = e; return MODA_ERR_CUDA; }
+  *status = v;
+#else
+  *status = 0;
+#endif
+  return MODA_OK;
+}
+
+// Bring-up aid, not part of the public header: `dump` (device, 128*128 floats, may be NULL)
+// receives the raw S tile of the first key tile of CTA (0,0,0) of the tcgen05 forward;
+// variant 1 routes P through shared memory instead of TMEM.
+int moda_b200_debug_set(void* dump, int variant) {
+#ifndef MODA_NO_TCGEN05
+  tc::debug_state().dump = reinterpret_cast<float*>(dump);
+  tc::debug_state().variant = variant;
+#endif
+  return MODA_OK;
+}
+
 int moda_b200_last_launch_count(void) { return g_last_launches; }
 int moda_b200_last_cuda_error(void) { return g_last_cuda_error; }
 

@@ -1,11 +1,537 @@
-// tcgen05 / TMEM / TMA kernels (placeholder interface; filled in next).
+// tcgen05 / TMEM / TMA MoDA kernels for sm_100a (D = 128, bf16 or fp16).
+//
+// Forward.  One CTA owns 128 folded query rows of one (batch, KV head) and walks the
+// key tiles they can see: sequence K/V first, then the depth K/V window of the tile
+// (the same walk and the same visibility intervals as the mma.sync kernels).  Two CTAs
+// are resident per SM so that one CTA's softmax overlaps the other's MMAs.
+//
+//   warp 4, one lane : producer.  TMA loads (128B-swizzled [128 x 64] boxes) of Q once
+//                      and of each K and V tile into single-stage buffers; issues
+//                      S = Q K^T and O += P V as tcgen05.mma (M=128, N=128, K=16 steps)
+//                      with fp32 accumulators in TMEM.
+//   warps 0-3        : softmax.  Thread = query row = TMEM lane.  tcgen05.ld of the S
+//                      row, visibility mask on masked tiles only, online softmax in
+//                      base 2 with lazy rescaling of O (O is touched only when a row
+//                      maximum grows by more than 2^8), P written back to TMEM over S
+//                      as packed 16-bit pairs and consumed by the PV MMA straight from
+//                      TMEM.
+//
+// TMEM (256 columns per CTA): [0,128) S (fp32) / P (16-bit, first 64 columns),
+// [128,256) O (fp32).  Shared memory: Q, K, V tiles of 32 KB each.
+//
+// Every mbarrier wait is bounded: on expiry the CTA records an error in a device
+// status word, drains its outstanding TMA loads (bounded again), frees its TMEM and
+// returns; later CTAs of the launch see the status word and return at once.
 #pragma once
+#include <cuda.h>
+
+#include <cstring>
+#include <type_traits>
+
 #include "../../include/moda_b200.h"
 #include "common.cuh"
-namespace moda { namespace tc {
-inline bool fwd_supported(const moda_problem*) { return false; }
+
+namespace moda {
+namespace tc {
+
+constexpr int kBM = 128;
+constexpr int kBN = 128;
+constexpr uint32_t kSpinLimit = 1u << 22;      // polls per wait before giving up
+constexpr uint32_t kTileBytes = 128 * 128 * 2; // one [128 x 128] 16-bit tile
+constexpr uint32_t kHalfBytes = kTileBytes / 2;
+
+// 0 = ok; otherwise (code << 8) | barrier id of the first wait that expired.
+__device__ int g_tc_status;
+
+struct FwdMaps { CUtensorMap q, k, v, kd, vd; };
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit expired or another thread of the CTA
+// already gave up (abort flag); the caller must then leave through the teardown path.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int bar_id) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test(bar, parity)) return true;
+    if ((i & 63u) == 63u && *abort_flag != 0) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_tc_status, 0, (1 << 8) | bar_id);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(slot_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :: "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 columns of 32 bits: thread (lane i of warp w) <-> TMEM lane 32w+i; register k <->
+// column k.  OFF selects which 32 registers of a larger per-thread array take part, so that
+// the array stays in registers (all indices are compile-time constants).
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[N]) {
+  static_assert(OFF + 32 <= N, "register window out of range");
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),
+        "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]), "=r"(r[OFF + 11]),
+        "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]), "=r"(r[OFF + 17]),
+        "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]), "=r"(r[OFF + 22]), "=r"(r[OFF + 23]),
+        "=r"(r[OFF + 24]), "=r"(r[OFF + 25]), "=r"(r[OFF + 26]), "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]),
+        "=r"(r[OFF + 30]), "=r"(r[OFF + 31])
+      : "r"(taddr) : "memory");
+}
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(OFF + 32 <= N, "register window out of range");
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      :: "r"(taddr),
+         "r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]), "r"(r[OFF + 4]), "r"(r[OFF + 5]),
+         "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]), "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]),
+         "r"(r[OFF + 12]), "r"(r[OFF + 13]), "r"(r[OFF + 14]), "r"(r[OFF + 15]), "r"(r[OFF + 16]), "r"(r[OFF + 17]),
+         "r"(r[OFF + 18]), "r"(r[OFF + 19]), "r"(r[OFF + 20]), "r"(r[OFF + 21]), "r"(r[OFF + 22]), "r"(r[OFF + 23]),
+         "r"(r[OFF + 24]), "r"(r[OFF + 25]), "r"(r[OFF + 26]), "r"(r[OFF + 27]), "r"(r[OFF + 28]), "r"(r[OFF + 29]),
+         "r"(r[OFF + 30]), "r"(r[OFF + 31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+//   K-major operand  ([rows][64 elem] boxes, 128 B per row):   lbo = 16,   sbo = 1024
+//   MN-major operand ([k rows][64 elem] boxes, second 64-wide
+//   block of the MN extent in the next box):                    lbo = box bytes, sbo = 1024
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16, fp32 accumulate, M = 128.
+//   fmt: 0 = f16, 1 = bf16.  b_mn_major: B operand is MN-major (V tile) instead of K-major.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t n, bool b_mn_major) {
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+enum BarId : int { kBarQ = 0, kBarK, kBarV, kBarS, kBarP, kBarO, kBarCount };
+
+// Tile walk of a 128-row query tile (same construction as simt::make_walk).
+struct Walk { int n_seq, n_dep, dep_c0, seq_full_hi; };
+__device__ __forceinline__ Walk make_walk(const Params& p, int r0) {
+  Walk w;
+  const int r_last = min(r0 + kBM, p.T_q) - 1;
+  int lo, hi, lo2, hi2;
+  seq_interval(p, r_last, lo, hi);
+  w.n_seq = (hi + kBN - 1) / kBN;
+  seq_interval(p, r0, lo2, hi2);
+  w.seq_full_hi = hi2;
+  dep_interval(p, r0, lo, hi);
+  dep_interval(p, r_last, lo2, hi2);
+  w.dep_c0 = lo;
+  w.n_dep = (hi2 - lo + kBN - 1) / kBN;
+  return w;
+}
+
+// ======================================================================= forward
+// grid (ceil(T_q/128), H, B); 160 threads.  kPTmem: P is handed to the PV MMA through
+// TMEM (production).  kPTmem = false stages P through a swizzled shared-memory tile
+// instead (one CTA per SM; kept as a cross-check of the TMEM operand layout).
+template <typename T, bool kPTmem>
+__global__ void __launch_bounds__(160, kPTmem ? 2 : 1)
+fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps maps, float* dbg) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw_u32);
+  const uint32_t sQ = base, sK = base + kTileBytes, sV = base + 2 * kTileBytes, sP = base + 3 * kTileBytes;
+  const uint32_t ctl = base + (kPTmem ? 3 : 4) * kTileBytes;
+  unsigned char* gctl = gbase + (kPTmem ? 3 : 4) * kTileBytes;
+  const uint32_t bars = ctl;                                    // kBarCount x 8 bytes
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 64);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 72);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 76);   // never set: lets the drain waits run
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;   // an earlier CTA failed: do nothing
+
+  const int n_qt = (p.T_q + kBM - 1) / kBM;
+  const int qt = n_qt - 1 - (int)blockIdx.x;     // heaviest causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int r0 = qt * kBM;
+  const Walk walk = make_walk(p, r0);
+  const int n_tiles = walk.n_seq + walk.n_dep;
+
+  if (tid == 0) {
+    mbar_init(bars + 8 * kBarQ, 1);
+    mbar_init(bars + 8 * kBarK, 1);
+    mbar_init(bars + 8 * kBarV, 1);
+    mbar_init(bars + 8 * kBarS, 1);
+    mbar_init(bars + 8 * kBarP, 128);
+    mbar_init(bars + 8 * kBarO, 1);
+    *abort_flag = 0;
+    *drain_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(ctl + 64, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_S = tmem, tmem_O = tmem + 128;
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------- producer lane
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
+      constexpr uint32_t idesc_pv = instr_desc(fmt, 128, true);
+      bool pend_k = false, pend_v = false;
+      uint32_t pend_k_par = 0, pend_v_par = 0;
+      auto load_kv = [&](int i, bool is_k) {
+        const bool dep = i >= walk.n_seq;
+        const int row = dep ? walk.dep_c0 + (i - walk.n_seq) * kBN : i * kBN;
+        const CUtensorMap* m = is_k ? (dep ? &maps.kd : &maps.k) : (dep ? &maps.vd : &maps.v);
+        const uint32_t dst = is_k ? sK : sV;
+        const uint32_t bar = bars + 8 * (is_k ? kBarK : kBarV);
+        mbar_expect_tx(bar, kTileBytes);
+        tma_load_4d(dst, m, bar, 0, h, row, b);
+        tma_load_4d(dst + kHalfBytes, m, bar, 64, h, row, b);
+        if (is_k) { pend_k = true; pend_k_par = i & 1; } else { pend_v = true; pend_v_par = i & 1; }
+      };
+      prefetch_map(&maps.q); prefetch_map(&maps.k); prefetch_map(&maps.v);
+      mbar_expect_tx(bars + 8 * kBarQ, kTileBytes);
+      tma_load_4d(sQ, &maps.q, bars + 8 * kBarQ, 0, h, r0, b);
+      tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * kBarQ, 64, h, r0, b);
+      load_kv(0, true);
+      load_kv(0, false);
+      bool ok = mbar_wait(bars + 8 * kBarQ, 0, abort_flag, kBarQ);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const uint32_t par = j & 1;
+        if (!(ok = mbar_wait(bars + 8 * kBarK, par, abort_flag, kBarK))) break;
+        pend_k = false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+          mma_ss(tmem_S, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
+        }
+        tc_commit(bars + 8 * kBarS);
+        if (j > 0) {   // PV(j-1) done => V buffer free
+          if (!(ok = mbar_wait(bars + 8 * kBarO, (j - 1) & 1, abort_flag, kBarO))) break;
+          load_kv(j, false);
+        }
+        if (!(ok = mbar_wait(bars + 8 * kBarS, par, abort_flag, kBarS))) break;
+        if (j + 1 < n_tiles) load_kv(j + 1, true);   // QK(j) done => K buffer free
+        if (!(ok = mbar_wait(bars + 8 * kBarP, par, abort_flag, kBarP))) break;
+        if (!(ok = mbar_wait(bars + 8 * kBarV, par, abort_flag, kBarV))) break;
+        pend_v = false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t bdesc = smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024);
+          const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+          if (kPTmem) {
+            mma_ts(tmem_O, tmem_S + kk * 8, bdesc, idesc_pv, acc);
+          } else {
+            const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+            mma_ss(tmem_O, smem_desc_sw128(sP + off, 16, 1024), bdesc, idesc_pv, acc);
+          }
+        }
+        tc_commit(bars + 8 * kBarO);
+      }
+      if (!ok) {   // give up: let loads in flight land before the CTA's shared memory is released
+        if (pend_k) mbar_wait(bars + 8 * kBarK, pend_k_par, drain_flag, kBarK);
+        if (pend_v) mbar_wait(bars + 8 * kBarV, pend_v_par, drain_flag, kBarV);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- softmax warps
+    const int row = warp * 32 + lane;          // row of the tile == TMEM lane
+    const int r = r0 + row;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    int slo, shi, dlo, dhi;
+    seq_interval(p, r, slo, shi);
+    dep_interval(p, r, dlo, dhi);
+    float m_used = -INFINITY;   // maximum the accumulators are currently scaled by
+    float l = 0.f;
+    bool ok = true;
+    const float c = p.scale_log2;
+
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kBarS, j & 1, abort_flag, kBarS));
+      if (!ok) break;   // warp-uniform: the tcgen05 loads/stores below are warp-collective
+      tc_fence_after();
+      const bool is_dep = j >= walk.n_seq;
+      const int c0 = is_dep ? walk.dep_c0 + (j - walk.n_seq) * kBN : j * kBN;
+      const bool masked = is_dep || (c0 + kBN > walk.seq_full_hi);
+      const int lo = is_dep ? dlo : slo, hi = is_dep ? dhi : shi;
+
+      uint32_t su[128];
+      tmem_ld32<0>(tmem_S + lane_addr + 0, su);
+      tmem_ld32<32>(tmem_S + lane_addr + 32, su);
+      tmem_ld32<64>(tmem_S + lane_addr + 64, su);
+      tmem_ld32<96>(tmem_S + lane_addr + 96, su);
+      tmem_wait_ld();
+      float s[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
+      if (dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = s[i];
+      }
+      float mx = -INFINITY;
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const int col = c0 + i;
+          if (col < lo || col >= hi) s[i] = -INFINITY;
+          mx = fmaxf(mx, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      }
+      const float m_new = fmaxf(m_used, mx * c);   // scale > 0 is required by this path
+      // lazy rescale: keep the old reference maximum unless it is more than 2^8 too small
+      float alpha = 1.f;
+      bool grow = false;
+      if (m_new > m_used + 8.f) {        // also true for the first finite maximum (m_used = -inf)
+        alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+        grow = (m_used != -INFINITY);    // nothing accumulated yet => nothing to rescale
+        m_used = m_new;
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      l *= alpha;
+      float sum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float p0 = fast_exp2(fmaf(s[2 * i], c, -m_sub));
+        const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, -m_sub));
+        sum += p0 + p1;
+        pk[i] = Pack<T>::pack(p0, p1);
+      }
+      l += sum;
+      if (kPTmem) {
+        tmem_st32<0>(tmem_S + lane_addr + 0, pk);
+        tmem_st32<32>(tmem_S + lane_addr + 32, pk);
+      } else {
+        // K-major, 128B-swizzled [128 rows][64 keys] x 2 blocks: 16-byte chunk cidx of a row
+        // lives at chunk (cidx ^ (row & 7))
+        unsigned char* prow = gbase + 3 * kTileBytes + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 16; ++ch) {
+          const int blk = ch >> 3, cidx = ch & 7;
+          uint4 v4 = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+          *reinterpret_cast<uint4*>(prow + blk * kHalfBytes + ((cidx ^ (row & 7)) << 4)) = v4;
+        }
+      }
+      // rescale O (TMEM round trip) only when some row of this warp moved its maximum
+      if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t ov[32];
+          tmem_ld32<0>(tmem_O + lane_addr + q4 * 32, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st32<0>(tmem_O + lane_addr + q4 * 32, ov);
+        }
+      }
+      if (kPTmem) {
+        tmem_wait_st();
+      } else {
+        tmem_wait_st();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      tc_fence_before();
+      mbar_arrive(bars + 8 * kBarP);
+    }
+
+    if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kBarO, (n_tiles - 1) & 1, abort_flag, kBarO));
+    if (ok && n_tiles > 0) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* go = reinterpret_cast<T*>(p.o.ptr) + p.o.off(b, r, h);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t ov[32];
+        tmem_ld32<0>(tmem_O + lane_addr + q4 * 32, ov);
+        tmem_wait_ld();
+        if (r < p.T_q) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v4;
+            v4.x = Pack<T>::pack(__uint_as_float(ov[i * 8 + 0]) * inv, __uint_as_float(ov[i * 8 + 1]) * inv);
+            v4.y = Pack<T>::pack(__uint_as_float(ov[i * 8 + 2]) * inv, __uint_as_float(ov[i * 8 + 3]) * inv);
+            v4.z = Pack<T>::pack(__uint_as_float(ov[i * 8 + 4]) * inv, __uint_as_float(ov[i * 8 + 5]) * inv);
+            v4.w = Pack<T>::pack(__uint_as_float(ov[i * 8 + 6]) * inv, __uint_as_float(ov[i * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(go + q4 * 32 + i * 8) = v4;
+          }
+        }
+      }
+      if (r < p.T_q) p.lse[((int64_t)b * p.T_q + r) * p.H + h] = m_used + log2f(l);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// [B, T, H, D] view -> 4-D tensor map (D, H, T, B), box [64, 1, 128, 1], 128B swizzle, zero fill.
+inline bool make_map(CUtensorMap* m, const View& v, int dtype, int B, int64_t T, int H, int D) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || v.ptr == nullptr) return false;
+  // a size-1 dimension may carry any stride; TMA still wants a positive multiple of 16 bytes
+  auto fix = [](int64_t s) { return (cuuint64_t)((s > 0 ? s : 8) * 2); };
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[3] = {fix(v.sh), fix(v.st), fix(v.sb)};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult rc = fn(m, dtype == MODA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+inline bool strides_ok(const moda_problem* pr) {
+  (void)pr;
+  return true;
+}
+
+inline bool fwd_supported(const moda_problem* pr) {
+  return pr->D == 128 && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && pr->T_kv * (int64_t)pr->G >= 1;
+}
 inline bool bwd_supported(const moda_problem*) { return false; }
 inline size_t bwd_extra_workspace_bytes(const moda_problem*) { return 0; }
-inline int fwd(const Params&, const moda_problem*, cudaStream_t, int*, int*) { return MODA_ERR_UNSUPPORTED; }
+
+// debugging aids (set through moda_b200_debug_set): variant 1 routes P through shared memory
+struct DebugState { float* dump = nullptr; int variant = 0; };
+inline DebugState& debug_state() { static DebugState s; return s; }
+
+inline int fwd(const Params& p, const moda_problem* pr, cudaStream_t st, int* launches, int* cuda_err) {
+  FwdMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const int64_t TL = (int64_t)p.T_kv * p.L;
+  bool ok = make_map(&maps.q, p.q, pr->dtype, p.B, p.T_q, p.H, 128) &&
+            make_map(&maps.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 128) &&
+            make_map(&maps.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 128);
+  if (ok && p.L > 0) {
+    ok = make_map(&maps.kd, p.kd, pr->dtype, p.B, TL, p.H, 128) && make_map(&maps.vd, p.vd, pr->dtype, p.B, TL, p.H, 128);
+  } else if (ok) {
+    maps.kd = maps.k; maps.vd = maps.v;   // never dereferenced (no depth tiles)
+  }
+  if (!ok) return MODA_ERR_UNSUPPORTED;
+
+  void* status_addr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&status_addr, g_tc_status);
+  if (e == cudaSuccess) e = cudaMemsetAsync(status_addr, 0, sizeof(int), st);
+  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+
+  const bool p_tmem = debug_state().variant != 1;
+  const size_t smem = (p_tmem ? 3 : 4) * (size_t)kTileBytes + 1024 + 128;
+  dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (er != cudaSuccess) return er;
+    kern<<<grid, 160, smem, st>>>(p, maps, debug_state().dump);
+    return cudaGetLastError();
+  };
+  if (pr->dtype == MODA_BF16) e = p_tmem ? launch(fwd_kernel<__nv_bfloat16, true>) : launch(fwd_kernel<__nv_bfloat16, false>);
+  else e = p_tmem ? launch(fwd_kernel<__half, true>) : launch(fwd_kernel<__half, false>);
+  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+  *launches += 1;
+  return MODA_OK;
+}
+
 inline int bwd(const Params&, const moda_problem*, void*, cudaStream_t, int*, int*) { return MODA_ERR_UNSUPPORTED; }
-}}
+
+// Reads (and synchronises on) the device status word of the tcgen05 kernels.
+inline int read_status(int* out) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+  if (e != cudaSuccess) return (int)e;
+  *out = v;
+  return 0;
+}
+
+}  // namespace tc
+}  // namespace moda

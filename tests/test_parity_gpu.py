@@ -201,3 +201,42 @@ def test_errors_surface_as_exceptions(M):
     q = torch.zeros(1, 8, 1, 96, dtype=torch.bfloat16, device=dev)
     with pytest.raises(M.ModaLibraryError, match="head dim"):
         M.parallel_moda(q, q, q, warn_shape=False)
+
+
+# ------------------------------------------------------------------ tcgen05 kernels
+@pytest.mark.parametrize("mode", [mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE])
+@pytest.mark.parametrize("T,L,G,dt", [
+    (1, 1, 1, "bf16"), (127, 0, 1, "bf16"), (128, 2, 1, "fp16"), (129, 3, 2, "bf16"), (300, 5, 4, "bf16"),
+    (1000, 3, 4, "fp16"), (513, 16, 8, "bf16"), (2048, 24, 4, "bf16"),
+])
+def test_tcgen05_forward(M, mode, T, L, G, dt):
+    """The tcgen05/TMEM/TMA forward, forced, D=128; its bounded waits must not have expired."""
+    from moda_b200 import _cabi
+    _run_case(M, mode, 1, T, 2, 128, L, G, DT[dt], None, seed=100 + T, path=M.PATH_TCGEN05, check_bwd=False)
+    assert _cabi.device_status() == 0
+
+
+def test_tcgen05_forward_matches_mma_sync_path(M):
+    """Two independent implementations of the same forward agree closely (both round P to bf16)."""
+    dev = torch.device("cuda", 0)
+    q, k, v, kd, vd, _ = [x.to(dev) for x in mo.make_inputs(77, 2, 777, 3, 128, 7, 2, dtype=torch.bfloat16)]
+    res = {}
+    for path in (M.PATH_SIMT_MMA, M.PATH_TCGEN05):
+        old = M.set_kernel_path(path)
+        try:
+            res[path] = M.parallel_moda_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=2)
+        finally:
+            M.set_kernel_path(old)
+    (o1, l1), (o2, l2) = res[M.PATH_SIMT_MMA], res[M.PATH_TCGEN05]
+    assert max_abs(o1.float(), o2.float()) <= 1e-2 and max_abs(l1, l2) <= 1e-4
+
+
+def test_tcgen05_path_refuses_what_it_cannot_run(M):
+    dev = torch.device("cuda", 0)
+    q = torch.zeros(1, 64, 1, 64, dtype=torch.bfloat16, device=dev)
+    old = M.set_kernel_path(M.PATH_TCGEN05)
+    try:
+        with pytest.raises(M.ModaLibraryError, match="does not support"):
+            M.parallel_moda_fwd(q, q, q)
+    finally:
+        M.set_kernel_path(old)
