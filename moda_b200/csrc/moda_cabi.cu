@@ -5,13 +5,12 @@
 
 #include <cuda_runtime.h>
 
-#include <mutex>
-#include <vector>
-
 #include "common.cuh"
+#include "profiler.cuh"
 #include "simt_mma_kernels.cuh"
 #ifndef MODA_NO_TCGEN05
 #include "tc_kernels.cuh"
+#include "tc_bwd_kernels.cuh"
 #endif
 
 namespace {
@@ -20,33 +19,6 @@ using namespace moda;
 
 thread_local int g_last_launches = 0;
 thread_local int g_last_cuda_error = 0;
-
-// ---- optional per-kernel timing (cudaEvents on the launch stream) -------------------
-enum KernelId : int { kKernFwdSimt = 0, kKernDelta, kKernDqSimt, kKernDkvSimt, kKernFwdTc, kKernDqTc,
-                      kKernDkvTc, kKernFdaFwd, kKernFdaBwd, kKernCount };
-const char* const kKernelNames[kKernCount] = {
-    "simt_fwd", "delta", "simt_dq", "simt_dkv", "tc_fwd", "tc_dq", "tc_dkv", "fda_fwd", "fda_bwd"};
-struct ProfEntry { int id; cudaEvent_t a, b; };
-std::mutex g_prof_mu;
-bool g_prof_on = false;
-std::vector<ProfEntry> g_prof;
-
-struct ProfScope {
-  cudaStream_t st; cudaEvent_t a = nullptr, b = nullptr; int id; bool on;
-  ProfScope(int id_, cudaStream_t st_) : st(st_), id(id_), on(g_prof_on) {
-    if (on) {
-      if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) { on = false; return; }
-      cudaEventRecord(a, st);
-    }
-  }
-  ~ProfScope() {
-    if (on) {
-      cudaEventRecord(b, st);
-      std::lock_guard<std::mutex> lk(g_prof_mu);
-      g_prof.push_back({id, a, b});
-    }
-  }
-};
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -106,7 +78,7 @@ int simt_fwd(const Params& p, cudaStream_t st) {
   if (int rc = opt_in_smem(kern, smem)) return rc;
   dim3 grid((p.T_q + 63) / 64, p.H, p.B);
   {
-    ProfScope ps(kKernFwdSimt, st);
+    prof::Scope ps(prof::kFwdSimt, st);
     kern<<<grid, 128, smem, st>>>(p);
   }
   MODA_CUDA(cudaGetLastError());
@@ -120,7 +92,7 @@ int simt_delta(const Params& p, cudaStream_t st) {
   int blocks = (int)((rows + 7) / 8);
   if (blocks > 148 * 16) blocks = 148 * 16;
   {
-    ProfScope ps(kKernDelta, st);
+    prof::Scope ps(prof::kDelta, st);
     simt::delta_kernel<T, D><<<blocks, 256, 0, st>>>(p);
   }
   MODA_CUDA(cudaGetLastError());
@@ -137,7 +109,7 @@ int simt_bwd(const Params& p, cudaStream_t st) {
     if (int rc = opt_in_smem(kern, smem)) return rc;
     dim3 grid((p.T_q + 63) / 64, p.H, p.B);
     {
-      ProfScope ps(kKernDqSimt, st);
+      prof::Scope ps(prof::kDqSimt, st);
       kern<<<grid, 128, smem, st>>>(p);
     }
     MODA_CUDA(cudaGetLastError());
@@ -151,7 +123,7 @@ int simt_bwd(const Params& p, cudaStream_t st) {
     const int n_dep = (int)(((int64_t)p.T_kv * p.L + 63) / 64);
     if (n_seq + n_dep > 0) {
       dim3 grid(n_seq + n_dep, p.H, p.B);
-      ProfScope ps(kKernDkvSimt, st);
+      prof::Scope ps(prof::kDkvSimt, st);
       kern<<<grid, 128, smem, st>>>(p, n_seq);
       MODA_CUDA(cudaGetLastError());
       g_last_launches += 1;
@@ -304,21 +276,23 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
 }
 
 int moda_b200_profile_begin(void) {
-  std::lock_guard<std::mutex> lk(g_prof_mu);
-  for (auto& e : g_prof) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
-  g_prof.clear();
-  g_prof_on = true;
+  prof::State& ps = prof::state();
+  std::lock_guard<std::mutex> lk(ps.mu);
+  for (auto& e : ps.entries) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
+  ps.entries.clear();
+  ps.on = true;
   return MODA_OK;
 }
 
 int moda_b200_profile_end(int max_entries, int* n_entries, int* kernel_ids, int* launches, float* total_ms) {
   if (n_entries == nullptr || kernel_ids == nullptr || launches == nullptr || total_ms == nullptr) return MODA_ERR_NULL;
-  std::lock_guard<std::mutex> lk(g_prof_mu);
-  g_prof_on = false;
-  int cnt[kKernCount] = {0};
-  float ms[kKernCount] = {0.f};
+  prof::State& ps = prof::state();
+  std::lock_guard<std::mutex> lk(ps.mu);
+  ps.on = false;
+  int cnt[prof::kCount] = {0};
+  float ms[prof::kCount] = {0.f};
   int rc = MODA_OK;
-  for (auto& e : g_prof) {
+  for (auto& e : ps.entries) {
     float t = 0.f;
     cudaError_t err = cudaEventSynchronize(e.b);
     if (err == cudaSuccess) err = cudaEventElapsedTime(&t, e.a, e.b);
@@ -326,9 +300,9 @@ int moda_b200_profile_end(int max_entries, int* n_entries, int* kernel_ids, int*
     cnt[e.id] += 1; ms[e.id] += t;
     cudaEventDestroy(e.a); cudaEventDestroy(e.b);
   }
-  g_prof.clear();
+  ps.entries.clear();
   int n = 0;
-  for (int i = 0; i < kKernCount && n < max_entries; ++i) {
+  for (int i = 0; i < prof::kCount && n < max_entries; ++i) {
     if (cnt[i] == 0) continue;
     kernel_ids[n] = i; launches[n] = cnt[i]; total_ms[n] = ms[i]; ++n;
   }
@@ -336,9 +310,7 @@ int moda_b200_profile_end(int max_entries, int* n_entries, int* kernel_ids, int*
   return rc;
 }
 
-const char* moda_b200_kernel_name(int kernel_id) {
-  return (kernel_id >= 0 && kernel_id < kKernCount) ? kKernelNames[kernel_id] : "unknown";
-}
+const char* moda_b200_kernel_name(int kernel_id) { return prof::kernel_name(kernel_id); }
 
 int moda_b200_device_status(int* status) {
   if (status == nullptr) return MODA_ERR_NULL;

@@ -1,0 +1,663 @@
+// tcgen05 / TMEM / TMA backward kernels of MoDA for sm_100a (D = 128, bf16 or fp16).
+//
+// Like the reference (moda_v14.py:1470-1842) the backward is a row-statistics pass, a
+// query-parallel dq kernel and a key-parallel dk/dv kernel; every output row has one
+// owning CTA, so there are no atomics and results are bit-reproducible.
+//
+//   pre_kernel : delta = rowsum(o * dout) (stored o, fp32 accumulate: moda_v14.py:525-539)
+//                written, with a copy of lse, as [B, H, T_q rounded up to 64] so that a
+//                (b, h) slice of 64 rows is one contiguous 256-byte bulk copy.
+//   dq_kernel  : CTA = 128 query rows; walks the visible key tiles in steps of 64 keys.
+//                S = Q K^T, dP = dO V^T (SS MMAs, N = 64) -> softmax warps form
+//                dS = P (dP - delta) in the input dtype in TMEM -> dQ += dS K (TS MMA,
+//                K tile read MN-major).  dq = scale * dQ (moda_v14.py:860).
+//   dkv_kernel : CTA = 128 keys of the sequence K/V or of the depth K/V; walks the query
+//                rows that can see them in steps of 64 rows.  S^T = K Q^T, dP^T = V dO^T
+//                (SS, N = 64) -> P^T and dS^T in TMEM -> dV += P^T dO, dK += dS^T Q (TS
+//                MMAs, Q/dO tiles read MN-major).  dk = scale * dK (moda_v14.py:1019).
+//                The G heads of a KV head are rows of the same folded query tile, so the
+//                GQA sum happens inside the MMA.
+//
+// Both MMA kernels run one CTA per SM with a software pipeline: two TMEM stages for the
+// score tiles (the tensor core computes step i+1 while the softmax warps work on step i)
+// and a four-deep TMA ring for the per-step operand tiles.  The tensor pipe executes the
+// MMAs of one issuing thread in order, which is what allows step i+2's scores to reuse the
+// TMEM stage the step-i update reads from without a wait in between.
+#pragma once
+#include "tc_kernels.cuh"
+
+namespace moda {
+namespace tc {
+
+constexpr int kStep = 64;            // keys (dq) or query rows (dkv) per pipeline step
+constexpr int kRing = 4;             // operand ring depth
+constexpr uint32_t kStepTile = 64 * 128 * 2;   // one [64 x 128] 16-bit tile (two 8 KB boxes)
+constexpr uint32_t kStepHalf = kStepTile / 2;
+
+struct DqMaps { CUtensorMap q, dout, k, v, kd, vd; };      // q, dout: 128-row boxes; others 64-row
+struct DkvMaps { CUtensorMap k, v, kd, vd, q, dout; };     // k, v, kd, vd: 128-row boxes; q, dout 64-row
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// ------------------------------------------------------------------ statistics pass
+// One warp per (b, h, r); a block of 8 warps covers 8 consecutive rows of one (b, h).
+template <typename T>
+__global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params p, float* delta_t, float* lse_t, int T_qp) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int64_t groups_per_bh = T_qp / 8;
+  const int64_t n_groups = (int64_t)p.B * p.H * groups_per_bh;
+  for (int64_t gidx = blockIdx.x; gidx < n_groups; gidx += gridDim.x) {
+    const int64_t bh = gidx / groups_per_bh;
+    const int r = (int)(gidx % groups_per_bh) * 8 + w;
+    const int b = (int)(bh / p.H), h = (int)(bh % p.H);
+    float s = 0.f, l = 0.f;
+    if (r < p.T_q) {
+      const T* po = reinterpret_cast<const T*>(p.o.ptr) + p.o.off(b, r, h);
+      const T* pd = reinterpret_cast<const T*>(p.dout.ptr) + p.dout.off(b, r, h);
+      const uint2 a = *reinterpret_cast<const uint2*>(po + lane * 4);
+      const uint2 d = *reinterpret_cast<const uint2*>(pd + lane * 4);
+      const float2 a0 = Pack<T>::unpack(a.x), a1 = Pack<T>::unpack(a.y);
+      const float2 d0 = Pack<T>::unpack(d.x), d1 = Pack<T>::unpack(d.y);
+      s = a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      l = p.lse[((int64_t)b * p.T_q + r) * p.H + h];
+    }
+    if (lane == 0) {
+      delta_t[bh * T_qp + r] = s;     // rows in [T_q, T_qp) are written as zeros
+      lse_t[bh * T_qp + r] = l;
+    }
+  }
+}
+
+enum BwdBar : int { kBRes = 0, kBIn0 = 1, kBS0 = 5, kBP0 = 7, kBT0 = 9, kBwdBarCount = 11 };
+
+// ============================================================================ dq
+// grid (ceil(T_q/128), H, B), 160 threads.  TMEM (512 columns allocated):
+//   stage s in {0,1}: [s*128, s*128+64) S (fp32) / dS (16-bit, first 32 columns),
+//                     [s*128+64, s*128+128) dP (fp32);   [256, 384) dQ (fp32).
+// Shared memory: Q, dO (32 KB each, resident), ring of kRing x {K step tile, V step tile}.
+template <typename T>
+__global__ void __launch_bounds__(160, 1)
+dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
+          const float* lse_t, int T_qp) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw_u32);
+  const uint32_t sQ = base, sDO = base + kTileBytes, sRing = base + 2 * kTileBytes;   // ring slot: K then V
+  const uint32_t ctl_off = 2 * kTileBytes + kRing * 2 * kStepTile;
+  const uint32_t bars = base + ctl_off;
+  unsigned char* gctl = gbase + ctl_off;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 104);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 108);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
+
+  const int n_qt = (p.T_q + kBM - 1) / kBM;
+  const int qt = n_qt - 1 - (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int r0 = qt * kBM;
+  // key walk in steps of 64
+  int n_seq, n_dep, dep_c0, seq_full_hi;
+  {
+    const int r_last = min(r0 + kBM, p.T_q) - 1;
+    int lo, hi, lo2, hi2;
+    seq_interval(p, r_last, lo, hi);
+    n_seq = (hi + kStep - 1) / kStep;
+    seq_interval(p, r0, lo2, hi2);
+    seq_full_hi = hi2;
+    dep_interval(p, r0, lo, hi);
+    dep_interval(p, r_last, lo2, hi2);
+    dep_c0 = lo;
+    n_dep = (hi2 - lo + kStep - 1) / kStep;
+  }
+  const int n = n_seq + n_dep;
+
+  if (tid == 0) {
+    mbar_init(bars + 8 * kBRes, 1);
+    for (int i = 0; i < kRing; ++i) mbar_init(bars + 8 * (kBIn0 + i), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (kBS0 + i), 1);
+      mbar_init(bars + 8 * (kBP0 + i), 128);
+      mbar_init(bars + 8 * (kBT0 + i), 1);
+    }
+    *abort_flag = 0;
+    *drain_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(bars + 96, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_dQ = tmem + 256;
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+
+  if (warp == 4) {
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      uint32_t pending = 0;   // ring slots with a load in flight
+      uint32_t pend_par[kRing] = {0, 0, 0, 0};
+      auto load_step = [&](int i) {
+        const bool dep = i >= n_seq;
+        const int row = dep ? dep_c0 + (i - n_seq) * kStep : i * kStep;
+        const uint32_t slot = i % kRing, dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (kBIn0 + slot);
+        const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
+        const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
+        mbar_expect_tx(bar, 2 * kStepTile);
+        tma_load_4d(dst, mk, bar, 0, h, row, b);
+        tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
+        tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
+        tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
+        pending |= 1u << slot; pend_par[slot] = (i / kRing) & 1;
+      };
+      auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T, dP(i) = dO V(i)^T into TMEM stage i&1
+        const uint32_t slot = i % kRing, sK = sRing + slot * 2 * kStepTile, sV = sK + kStepTile;
+        const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
+          mma_ss(tS, smem_desc_sw128(sQ + offA, 16, 1024), smem_desc_sw128(sK + offB, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
+          mma_ss(tP, smem_desc_sw128(sDO + offA, 16, 1024), smem_desc_sw128(sV + offB, 16, 1024), idesc_s, kk > 0);
+        }
+        tc_commit(bars + 8 * (kBS0 + (i & 1)));
+      };
+      prefetch_map(&maps.q); prefetch_map(&maps.dout); prefetch_map(&maps.k); prefetch_map(&maps.v);
+      mbar_expect_tx(bars + 8 * kBRes, 2 * kTileBytes);
+      tma_load_4d(sQ, &maps.q, bars + 8 * kBRes, 0, h, r0, b);
+      tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * kBRes, 64, h, r0, b);
+      tma_load_4d(sDO, &maps.dout, bars + 8 * kBRes, 0, h, r0, b);
+      tma_load_4d(sDO + kHalfBytes, &maps.dout, bars + 8 * kBRes, 64, h, r0, b);
+      for (int i = 0; i < 3 && i < n; ++i) load_step(i);
+      bool ok = mbar_wait(bars + 8 * kBRes, 0, abort_flag, kBRes);
+      for (int i = 0; ok && i < 2 && i < n; ++i) {
+        if (!(ok = mbar_wait(bars + 8 * (kBIn0 + i), 0, abort_flag, kBIn0 + i))) break;
+        pending &= ~(1u << i);
+        tc_fence_after();
+        issue_scores(i);
+      }
+      for (int j = 0; ok && j < n; ++j) {
+        // dQ += dS(j) K(j)
+        if (!(ok = mbar_wait(bars + 8 * (kBP0 + (j & 1)), (j >> 1) & 1, abort_flag, kBP0 + (j & 1)))) break;
+        tc_fence_after();
+        {
+          const uint32_t slot = j % kRing, sK = sRing + slot * 2 * kStepTile;
+          const uint32_t tA = tmem + (j & 1) * 128;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ts(tmem_dQ, tA + kk * 8, smem_desc_sw128(sK + kk * 2048, kStepHalf, 1024), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bars + 8 * (kBT0 + (j & 1)));
+        }
+        if (j + 2 < n) {
+          const int i = j + 2;
+          const uint32_t slot = i % kRing;
+          if (!(ok = mbar_wait(bars + 8 * (kBIn0 + slot), (i / kRing) & 1, abort_flag, kBIn0 + slot))) break;
+          pending &= ~(1u << slot);
+          tc_fence_after();
+          issue_scores(i);
+        }
+        if (j + 3 < n) {   // ring slot of step j+3 was last read by the update of step j-1
+          if (j >= 1) {
+            if (!(ok = mbar_wait(bars + 8 * (kBT0 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, kBT0 + ((j - 1) & 1)))) break;
+          }
+          load_step(j + 3);
+        }
+      }
+      if (!ok) {   // let loads in flight land before the CTA's shared memory is released
+        for (int s = 0; s < kRing; ++s)
+          if (pending & (1u << s)) mbar_wait(bars + 8 * (kBIn0 + s), pend_par[s], drain_flag, kBIn0 + s);
+      }
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const int r = r0 + row;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    int slo, shi, dlo, dhi;
+    seq_interval(p, r, slo, shi);
+    dep_interval(p, r, dlo, dhi);
+    float lse_r = 0.f, dl_r = 0.f;
+    if (r < p.T_q) {
+      const int64_t idx = ((int64_t)b * p.H + h) * T_qp + r;
+      lse_r = lse_t[idx]; dl_r = delta_t[idx];
+    }
+    const float c = p.scale_log2;
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBS0 + (i & 1)), (i >> 1) & 1, abort_flag, kBS0 + (i & 1)));
+      if (!ok) break;
+      tc_fence_after();
+      const bool is_dep = i >= n_seq;
+      const int c0 = is_dep ? dep_c0 + (i - n_seq) * kStep : i * kStep;
+      const bool masked = is_dep || (c0 + kStep > seq_full_hi);
+      const int lo = is_dep ? dlo : slo, hi = is_dep ? dhi : shi;
+      const uint32_t tS = tmem + (i & 1) * 128 + lane_addr;
+      uint32_t su[64], du[64];
+      tmem_ld32<0>(tS, su);
+      tmem_ld32<32>(tS + 32, su);
+      tmem_ld32<0>(tS + 64, du);
+      tmem_ld32<32>(tS + 96, du);
+      tmem_wait_ld();
+      uint32_t pk[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        float p0 = fast_exp2(fmaf(__uint_as_float(su[2 * jj]), c, -lse_r));
+        float p1 = fast_exp2(fmaf(__uint_as_float(su[2 * jj + 1]), c, -lse_r));
+        if (masked) {
+          const int col = c0 + 2 * jj;
+          if (col < lo || col >= hi) p0 = 0.f;
+          if (col + 1 < lo || col + 1 >= hi) p1 = 0.f;
+        }
+        pk[jj] = Pack<T>::pack(p0 * (__uint_as_float(du[2 * jj]) - dl_r), p1 * (__uint_as_float(du[2 * jj + 1]) - dl_r));
+      }
+      tmem_st32<0>(tS, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * (kBP0 + (i & 1)));
+    }
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBT0 + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, kBT0 + ((n - 1) & 1)));
+    if (ok && n > 0) {
+      tc_fence_after();
+      T* gdq = reinterpret_cast<T*>(p.dq.ptr) + p.dq.off(b, r, h);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t ov[32];
+        tmem_ld32<0>(tmem_dQ + lane_addr + q4 * 32, ov);
+        tmem_wait_ld();
+        if (r < p.T_q) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v4;
+            v4.x = Pack<T>::pack(__uint_as_float(ov[i * 8 + 0]) * p.scale, __uint_as_float(ov[i * 8 + 1]) * p.scale);
+            v4.y = Pack<T>::pack(__uint_as_float(ov[i * 8 + 2]) * p.scale, __uint_as_float(ov[i * 8 + 3]) * p.scale);
+            v4.z = Pack<T>::pack(__uint_as_float(ov[i * 8 + 4]) * p.scale, __uint_as_float(ov[i * 8 + 5]) * p.scale);
+            v4.w = Pack<T>::pack(__uint_as_float(ov[i * 8 + 6]) * p.scale, __uint_as_float(ov[i * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(gdq + q4 * 32 + i * 8) = v4;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =========================================================================== dk / dv
+// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 160 threads; key tiles of 128.
+// TMEM (512 columns): stage s: [s*128, +64) S^T / P^T (16-bit, 32 columns),
+//   [s*128+64, +64) dP^T / dS^T (16-bit, 32 columns); [256,384) dV; [384,512) dK.
+// Shared memory: K, V tile (32 KB each, resident), ring of kRing x {Q step tile, dO step
+// tile, 64 lse, 64 delta}.
+constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
+
+template <typename T>
+__global__ void __launch_bounds__(160, 1)
+dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
+           const float* lse_t, int T_qp, int n_seq_key_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw_u32);
+  const uint32_t sK = base, sV = base + kTileBytes, sRing = base + 2 * kTileBytes;
+  // ring slot layout: [Q 16 KB][dO 16 KB] for all slots first (keeps tiles 1024-aligned), stats after
+  const uint32_t sStat = sRing + kRing * 2 * kStepTile;
+  const uint32_t ctl_off = 2 * kTileBytes + kRing * kDkvSlot;
+  const uint32_t bars = base + ctl_off;
+  unsigned char* gctl = gbase + ctl_off;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 104);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 108);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
+
+  const int h = blockIdx.y, b = blockIdx.z;
+  const bool is_dep = (int)blockIdx.x >= n_seq_key_tiles;
+  const int c0 = (is_dep ? (int)blockIdx.x - n_seq_key_tiles : (int)blockIdx.x) * kBN;
+  const int n_keys = is_dep ? p.T_kv * p.L : p.T_kv;
+  const int c_last = min(c0 + kBN, n_keys) - 1;
+
+  // query rows that can see a key of this tile: [q_begin, q_end), walked in steps of 64
+  int q_begin, q_end;
+  if (!is_dep) {
+    q_begin = (p.mode == kNonCausal) ? 0 : c0 * p.G;
+    q_end = p.T_q;
+  } else {
+    const int p_lo = c0 / p.L, p_hi = c_last / p.L;
+    q_begin = p_lo * p.G;
+    const int t_end = (p.mode == kChunkVisible) ? min((p_hi / p.Cb + 1) * p.Cb, p.T_kv) : p_hi + 1;
+    q_end = t_end * p.G;
+  }
+  q_begin = (q_begin / kStep) * kStep;
+  const int n = (q_end - q_begin + kStep - 1) / kStep;
+
+  if (tid == 0) {
+    mbar_init(bars + 8 * kBRes, 1);
+    for (int i = 0; i < kRing; ++i) mbar_init(bars + 8 * (kBIn0 + i), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (kBS0 + i), 1);
+      mbar_init(bars + 8 * (kBP0 + i), 128);
+      mbar_init(bars + 8 * (kBT0 + i), 1);
+    }
+    *abort_flag = 0;
+    *drain_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(bars + 96, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_dV = tmem + 256, tmem_dK = tmem + 384;
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  const int64_t stat_base = ((int64_t)b * p.H + h) * T_qp;
+
+  if (warp == 4) {
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      uint32_t pending = 0;
+      uint32_t pend_par[kRing] = {0, 0, 0, 0};
+      auto load_step = [&](int i) {
+        const int row = q_begin + i * kStep;
+        const uint32_t slot = i % kRing, dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (kBIn0 + slot);
+        const uint32_t st = sStat + slot * 512;
+        mbar_expect_tx(bar, 2 * kStepTile + 512);
+        tma_load_4d(dst, &maps.q, bar, 0, h, row, b);
+        tma_load_4d(dst + kStepHalf, &maps.q, bar, 64, h, row, b);
+        tma_load_4d(dst + kStepTile, &maps.dout, bar, 0, h, row, b);
+        tma_load_4d(dst + kStepTile + kStepHalf, &maps.dout, bar, 64, h, row, b);
+        bulk_load(st, lse_t + stat_base + row, 256, bar);
+        bulk_load(st + 256, delta_t + stat_base + row, 256, bar);
+        pending |= 1u << slot; pend_par[slot] = (i / kRing) & 1;
+      };
+      auto issue_scores = [&](int i) {   // S^T(i) = K Q(i)^T, dP^T(i) = V dO(i)^T
+        const uint32_t slot = i % kRing, sQ = sRing + slot * 2 * kStepTile, sDO = sQ + kStepTile;
+        const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
+          mma_ss(tS, smem_desc_sw128(sK + offA, 16, 1024), smem_desc_sw128(sQ + offB, 16, 1024), idesc_s, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
+          mma_ss(tP, smem_desc_sw128(sV + offA, 16, 1024), smem_desc_sw128(sDO + offB, 16, 1024), idesc_s, kk > 0);
+        }
+        tc_commit(bars + 8 * (kBS0 + (i & 1)));
+      };
+      const CUtensorMap* mk = is_dep ? &maps.kd : &maps.k;
+      const CUtensorMap* mv = is_dep ? &maps.vd : &maps.v;
+      prefetch_map(mk); prefetch_map(mv); prefetch_map(&maps.q); prefetch_map(&maps.dout);
+      mbar_expect_tx(bars + 8 * kBRes, 2 * kTileBytes);
+      tma_load_4d(sK, mk, bars + 8 * kBRes, 0, h, c0, b);
+      tma_load_4d(sK + kHalfBytes, mk, bars + 8 * kBRes, 64, h, c0, b);
+      tma_load_4d(sV, mv, bars + 8 * kBRes, 0, h, c0, b);
+      tma_load_4d(sV + kHalfBytes, mv, bars + 8 * kBRes, 64, h, c0, b);
+      for (int i = 0; i < 3 && i < n; ++i) load_step(i);
+      bool ok = mbar_wait(bars + 8 * kBRes, 0, abort_flag, kBRes);
+      for (int i = 0; ok && i < 2 && i < n; ++i) {
+        if (!(ok = mbar_wait(bars + 8 * (kBIn0 + i), 0, abort_flag, kBIn0 + i))) break;
+        pending &= ~(1u << i);
+        tc_fence_after();
+        issue_scores(i);
+      }
+      for (int j = 0; ok && j < n; ++j) {
+        if (!(ok = mbar_wait(bars + 8 * (kBP0 + (j & 1)), (j >> 1) & 1, abort_flag, kBP0 + (j & 1)))) break;
+        tc_fence_after();
+        {
+          const uint32_t slot = j % kRing, sQ = sRing + slot * 2 * kStepTile, sDO = sQ + kStepTile;
+          const uint32_t tPt = tmem + (j & 1) * 128, tDSt = tPt + 64;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO
+            mma_ts(tmem_dV, tPt + kk * 8, smem_desc_sw128(sDO + kk * 2048, kStepHalf, 1024), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
+            mma_ts(tmem_dK, tDSt + kk * 8, smem_desc_sw128(sQ + kk * 2048, kStepHalf, 1024), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bars + 8 * (kBT0 + (j & 1)));
+        }
+        if (j + 2 < n) {
+          const int i = j + 2;
+          const uint32_t slot = i % kRing;
+          if (!(ok = mbar_wait(bars + 8 * (kBIn0 + slot), (i / kRing) & 1, abort_flag, kBIn0 + slot))) break;
+          pending &= ~(1u << slot);
+          tc_fence_after();
+          issue_scores(i);
+        }
+        if (j + 3 < n) {
+          if (j >= 1) {
+            if (!(ok = mbar_wait(bars + 8 * (kBT0 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, kBT0 + ((j - 1) & 1)))) break;
+          }
+          load_step(j + 3);
+        }
+      }
+      if (!ok) {   // let loads in flight land before the CTA's shared memory is released
+        for (int s = 0; s < kRing; ++s)
+          if (pending & (1u << s)) mbar_wait(bars + 8 * (kBIn0 + s), pend_par[s], drain_flag, kBIn0 + s);
+      }
+    }
+  } else {
+    const int row = warp * 32 + lane;       // key row of the tile == TMEM lane
+    const int key = c0 + row;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // query rows [rlo, rhi) that see this key (see the visibility rule in common.cuh, inverted)
+    int rlo, rhi;
+    if (key >= n_keys) { rlo = 0; rhi = 0; }
+    else if (!is_dep) { rlo = (p.mode == kNonCausal) ? 0 : key * p.G; rhi = p.T_q; }
+    else {
+      const int tp = key / p.L;
+      rlo = tp * p.G;
+      rhi = ((p.mode == kChunkVisible) ? min((tp / p.Cb + 1) * p.Cb, p.T_kv) : tp + 1) * p.G;
+    }
+    // a step [q0, q0+64) needs no mask iff every valid key of the tile sees all 64 rows
+    const int tile_rlo_max = is_dep ? 0x7fffffff : ((p.mode == kNonCausal) ? 0 : c_last * p.G);
+    const bool tail_keys = (c0 + kBN > n_keys);
+    const float c = p.scale_log2;
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
+      const uint32_t slot = i % kRing;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBIn0 + slot), (i / kRing) & 1, abort_flag, kBIn0 + slot));
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBS0 + (i & 1)), (i >> 1) & 1, abort_flag, kBS0 + (i & 1)));
+      if (!ok) break;
+      tc_fence_after();
+      const int q0 = q_begin + i * kStep;
+      const bool masked = is_dep || tail_keys || q0 < tile_rlo_max || q0 + kStep > p.T_q;
+      const uint32_t tS = tmem + (i & 1) * 128 + lane_addr;
+      const float4* st4 = reinterpret_cast<const float4*>(gbase + (sStat - base) + slot * 512);
+      uint32_t su[64], du[64];
+      tmem_ld32<0>(tS, su);
+      tmem_ld32<32>(tS + 32, su);
+      tmem_ld32<0>(tS + 64, du);
+      tmem_ld32<32>(tS + 96, du);
+      tmem_wait_ld();
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int j4 = 0; j4 < 16; ++j4) {
+        const float4 l4 = st4[j4], d4 = st4[16 + j4];
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pv[4], dv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int jj = j4 * 4 + e;
+          float pe = fast_exp2(fmaf(__uint_as_float(su[jj]), c, -ls[e]));
+          if (masked) {
+            const int rr = q0 + jj;
+            if (rr < rlo || rr >= rhi) pe = 0.f;
+          }
+          pv[e] = pe;
+          dv[e] = pe * (__uint_as_float(du[jj]) - ds[e]);
+        }
+        pp[j4 * 2] = Pack<T>::pack(pv[0], pv[1]); pp[j4 * 2 + 1] = Pack<T>::pack(pv[2], pv[3]);
+        pd[j4 * 2] = Pack<T>::pack(dv[0], dv[1]); pd[j4 * 2 + 1] = Pack<T>::pack(dv[2], dv[3]);
+      }
+      tmem_st32<0>(tS, pp);
+      tmem_st32<0>(tS + 64, pd);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * (kBP0 + (i & 1)));
+    }
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBT0 + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, kBT0 + ((n - 1) & 1)));
+    if (ok && n > 0) {
+      tc_fence_after();
+      const View& okv = is_dep ? p.dkd : p.dk;
+      const View& ovv = is_dep ? p.dvd : p.dv;
+      T* gdk = reinterpret_cast<T*>(okv.ptr) + okv.off(b, key, h);
+      T* gdv = reinterpret_cast<T*>(ovv.ptr) + ovv.off(b, key, h);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t ov[32], ok2[32];
+        tmem_ld32<0>(tmem_dV + lane_addr + q4 * 32, ov);
+        tmem_ld32<0>(tmem_dK + lane_addr + q4 * 32, ok2);
+        tmem_wait_ld();
+        if (key < n_keys) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v4, k4;
+            v4.x = Pack<T>::pack(__uint_as_float(ov[i * 8 + 0]), __uint_as_float(ov[i * 8 + 1]));
+            v4.y = Pack<T>::pack(__uint_as_float(ov[i * 8 + 2]), __uint_as_float(ov[i * 8 + 3]));
+            v4.z = Pack<T>::pack(__uint_as_float(ov[i * 8 + 4]), __uint_as_float(ov[i * 8 + 5]));
+            v4.w = Pack<T>::pack(__uint_as_float(ov[i * 8 + 6]), __uint_as_float(ov[i * 8 + 7]));
+            k4.x = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 0]) * p.scale, __uint_as_float(ok2[i * 8 + 1]) * p.scale);
+            k4.y = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 2]) * p.scale, __uint_as_float(ok2[i * 8 + 3]) * p.scale);
+            k4.z = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 4]) * p.scale, __uint_as_float(ok2[i * 8 + 5]) * p.scale);
+            k4.w = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 6]) * p.scale, __uint_as_float(ok2[i * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(gdv + q4 * 32 + i * 8) = v4;
+            *reinterpret_cast<uint4*>(gdk + q4 * 32 + i * 8) = k4;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+inline bool make_map_rows(CUtensorMap* m, const View& v, int dtype, int B, int64_t T, int H, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || v.ptr == nullptr) return false;
+  auto fix = [](int64_t s) { return (cuuint64_t)((s > 0 ? s : 8) * 2); };
+  cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[3] = {fix(v.sh), fix(v.st), fix(v.sb)};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(m, dtype == MODA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, v.ptr,
+            dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline int padded_rows(int T_q) { return (T_q + 63) / 64 * 64 + 64; }   // +64: a step may start in the last block
+
+inline bool bwd_supported(const moda_problem* pr) {
+  return pr->D == 128 && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
+}
+
+inline size_t bwd_extra_workspace_bytes(const moda_problem* pr) {
+  if (!bwd_supported(pr)) return 0;
+  const size_t n = (size_t)pr->B * pr->H * padded_rows(pr->T_kv * pr->G) * sizeof(float);
+  return 2 * ((n + 255) & ~(size_t)255);
+}
+
+inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_t st, int* launches, int* cuda_err) {
+  const int T_qp = padded_rows(p.T_q);
+  const size_t n = (((size_t)p.B * p.H * T_qp * sizeof(float)) + 255) & ~(size_t)255;
+  float* delta_t = reinterpret_cast<float*>(extra);
+  float* lse_t = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(extra) + n);
+  const int64_t TL = (int64_t)p.T_kv * p.L;
+  const bool dep = p.L > 0;
+
+  DqMaps dqm; DkvMaps dkm;
+  memset(&dqm, 0, sizeof(dqm)); memset(&dkm, 0, sizeof(dkm));
+  bool ok = make_map_rows(&dqm.q, p.q, pr->dtype, p.B, p.T_q, p.H, 128) &&
+            make_map_rows(&dqm.dout, p.dout, pr->dtype, p.B, p.T_q, p.H, 128) &&
+            make_map_rows(&dqm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 64) &&
+            make_map_rows(&dqm.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 64) &&
+            make_map_rows(&dkm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 128) &&
+            make_map_rows(&dkm.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 128) &&
+            make_map_rows(&dkm.q, p.q, pr->dtype, p.B, p.T_q, p.H, 64) &&
+            make_map_rows(&dkm.dout, p.dout, pr->dtype, p.B, p.T_q, p.H, 64);
+  if (ok && dep) {
+    ok = make_map_rows(&dqm.kd, p.kd, pr->dtype, p.B, TL, p.H, 64) && make_map_rows(&dqm.vd, p.vd, pr->dtype, p.B, TL, p.H, 64) &&
+         make_map_rows(&dkm.kd, p.kd, pr->dtype, p.B, TL, p.H, 128) && make_map_rows(&dkm.vd, p.vd, pr->dtype, p.B, TL, p.H, 128);
+  } else if (ok) {
+    dqm.kd = dqm.k; dqm.vd = dqm.v; dkm.kd = dkm.k; dkm.vd = dkm.v;
+  }
+  if (!ok) return MODA_ERR_UNSUPPORTED;
+
+  void* status_addr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&status_addr, g_tc_status);
+  if (e == cudaSuccess) e = cudaMemsetAsync(status_addr, 0, sizeof(int), st);
+  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+
+  const bool bf = pr->dtype == MODA_BF16;
+  {
+    const int64_t groups = (int64_t)p.B * p.H * (T_qp / 8);
+    const int blocks = (int)(groups < 148 * 32 ? groups : 148 * 32);
+    prof::Scope ps(prof::kPreTc, st);
+    if (bf) pre_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
+    else pre_kernel<__half><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
+  }
+  if ((e = cudaGetLastError()) != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+  *launches += 1;
+  {
+    const size_t smem = 2 * (size_t)kTileBytes + kRing * 2 * (size_t)kStepTile + 128 + 1024;
+    dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
+    auto launch = [&](auto kern) -> cudaError_t {
+      cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (er != cudaSuccess) return er;
+      prof::Scope ps(prof::kDqTc, st);
+      kern<<<grid, 160, smem, st>>>(p, dqm, delta_t, lse_t, T_qp);
+      return cudaGetLastError();
+    };
+    e = bf ? launch(dq_kernel<__nv_bfloat16>) : launch(dq_kernel<__half>);
+    if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+    *launches += 1;
+  }
+  {
+    const size_t smem = 2 * (size_t)kTileBytes + kRing * (size_t)kDkvSlot + 128 + 1024;
+    const int n_seq = (p.T_kv + kBN - 1) / kBN;
+    const int n_dep = (int)((TL + kBN - 1) / kBN);
+    dim3 grid(n_seq + n_dep, p.H, p.B);
+    auto launch = [&](auto kern) -> cudaError_t {
+      cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (er != cudaSuccess) return er;
+      prof::Scope ps(prof::kDkvTc, st);
+      kern<<<grid, 160, smem, st>>>(p, dkm, delta_t, lse_t, T_qp, n_seq);
+      return cudaGetLastError();
+    };
+    e = bf ? launch(dkv_kernel<__nv_bfloat16>) : launch(dkv_kernel<__half>);
+    if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+    *launches += 1;
+  }
+  return MODA_OK;
+}
+
+}  // namespace tc
+}  // namespace moda

@@ -30,6 +30,7 @@
 
 #include "../../include/moda_b200.h"
 #include "common.cuh"
+#include "profiler.cuh"
 
 namespace moda {
 namespace tc {
@@ -472,16 +473,9 @@ inline bool make_map(CUtensorMap* m, const View& v, int dtype, int B, int64_t T,
   return rc == CUDA_SUCCESS;
 }
 
-inline bool strides_ok(const moda_problem* pr) {
-  (void)pr;
-  return true;
-}
-
 inline bool fwd_supported(const moda_problem* pr) {
   return pr->D == 128 && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && pr->T_kv * (int64_t)pr->G >= 1;
 }
-inline bool bwd_supported(const moda_problem*) { return false; }
-inline size_t bwd_extra_workspace_bytes(const moda_problem*) { return 0; }
 
 // debugging aids (set through moda_b200_debug_set): variant 1 routes P through shared memory
 struct DebugState { float* dump = nullptr; int variant = 0; };
@@ -512,6 +506,7 @@ inline int fwd(const Params& p, const moda_problem* pr, cudaStream_t st, int* la
   auto launch = [&](auto kern) -> cudaError_t {
     cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (er != cudaSuccess) return er;
+    prof::Scope ps(prof::kFwdTc, st);
     kern<<<grid, 160, smem, st>>>(p, maps, debug_state().dump);
     return cudaGetLastError();
   };
@@ -521,8 +516,6 @@ inline int fwd(const Params& p, const moda_problem* pr, cudaStream_t st, int* la
   *launches += 1;
   return MODA_OK;
 }
-
-inline int bwd(const Params&, const moda_problem*, void*, cudaStream_t, int*, int*) { return MODA_ERR_UNSUPPORTED; }
 
 // Reads (and synchronises on) the device status word of the tcgen05 kernels.
 inline int read_status(int* out) {

@@ -240,3 +240,32 @@ def test_tcgen05_path_refuses_what_it_cannot_run(M):
             M.parallel_moda_fwd(q, q, q)
     finally:
         M.set_kernel_path(old)
+
+
+@pytest.mark.parametrize("mode", [mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE])
+@pytest.mark.parametrize("T,L,G,dt", [
+    (1, 1, 1, "bf16"), (64, 0, 1, "bf16"), (127, 2, 1, "fp16"), (129, 3, 2, "bf16"), (300, 5, 4, "bf16"),
+    (1000, 3, 4, "fp16"), (513, 16, 8, "bf16"), (1536, 24, 4, "bf16"),
+])
+def test_tcgen05_forward_and_backward(M, mode, T, L, G, dt):
+    """tcgen05 forward + backward (statistics pass, dq kernel, dk/dv kernel), forced, D=128."""
+    from moda_b200 import _cabi
+    _run_case(M, mode, 1, T, 2, 128, L, G, DT[dt], None, seed=200 + T, path=M.PATH_TCGEN05, check_bwd=True)
+    assert _cabi.device_status() == 0
+
+
+def test_tcgen05_backward_bitwise_reproducible_and_batched(M):
+    dev = torch.device("cuda", 0)
+    q, k, v, kd, vd, dout = [x.to(dev) for x in mo.make_inputs(23, 3, 333, 2, 128, 4, 4, dtype=torch.bfloat16)]
+    old = M.set_kernel_path(M.PATH_TCGEN05)
+    try:
+        outs = []
+        for _ in range(2):
+            o, lse = M.parallel_moda_chunk_visible_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=4)
+            grads = M.parallel_moda_chunk_visible_bwd(q, k, v, o, None, lse, dout, cached_k=kd, cached_v=vd,
+                                                      moda_group_num=4)
+            outs.append([o, lse] + [g for g in grads if g is not None])
+        for a, b in zip(*outs):
+            assert torch.equal(a, b)
+    finally:
+        M.set_kernel_path(old)
