@@ -119,6 +119,45 @@ int moda_b200_bwd(const moda_problem *prob, const moda_tensor4 *q, const moda_te
                   void *stream);
 
 /*
+ * Backward for callers that cannot hand the library a scratch buffer.
+ *
+ * Some hosts of this operator have no way to allocate device memory at the point where
+ * the backward runs: code replaying inside a region where cudaMalloc is forbidden or
+ * would synchronise the device (a latency-critical serving loop, a plugin callback
+ * that is only given its input and output buffers, a framework whose allocator is
+ * locked while gradients are produced).  For them this entry point does exactly what
+ * moda_b200_bwd does, but takes no workspace: the scratch (the per-row delta and, on
+ * the tcgen05 path, the transposed lse/delta copies) lives in a fixed device array of
+ * MODA_B200_STATIC_SCRATCH_BYTES that is part of the library image.  It calls no
+ * cudaMalloc/cudaFree and no allocating library routine.
+ *
+ *  - Limit: problems whose moda_b200_bwd_workspace_bytes() exceeds
+ *    MODA_B200_STATIC_SCRATCH_BYTES are refused with MODA_ERR_TOO_LARGE and nothing is
+ *    launched.  Every GPU that loads the library holds the array until the process
+ *    exits, which is why it is kept modest.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device made current) and caches it; make that
+ *    first call outside any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's
+ *    contents.  The backward writes every scratch word before reading it, so nothing
+ *    needs clearing between calls; but two calls whose kernels overlap on the GPU
+ *    (different streams, no ordering between them) race on it.  Order such calls, or
+ *    use moda_b200_bwd with separate workspaces.
+ *
+ * It has no counterpart in the reference, whose backward allocates its scratch with
+ * torch (moda_v14.py:1609-1652,1715-1716).
+ */
+#define MODA_B200_STATIC_SCRATCH_BYTES (8u << 20)
+int moda_b200_bwd_static_scratch(const moda_problem *prob, const moda_tensor4 *q,
+                                 const moda_tensor4 *k, const moda_tensor4 *v,
+                                 const moda_tensor4 *depth_k, const moda_tensor4 *depth_v,
+                                 const moda_tensor4 *o, const float *lse,
+                                 const moda_tensor4 *dout, const moda_tensor4 *dq,
+                                 const moda_tensor4 *dk, const moda_tensor4 *dv,
+                                 const moda_tensor4 *d_depth_k, const moda_tensor4 *d_depth_v,
+                                 void *stream);
+
+/*
  * Validation only (no launch): the status moda_b200_fwd / moda_b200_bwd would return
  * for this problem's shape fields.  Mirrors the reference's shape assertions
  * (moda_v14.py:404-408,476-478,487,2839-2862).

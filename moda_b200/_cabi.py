@@ -16,12 +16,14 @@ LIB_PATH = os.path.join(_HERE, "libmoda_b200.so")
 MODE_CAUSAL, MODE_NONCAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY = 0, 1, 2, 3
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05 = 0, 1, 2
+STATIC_SCRATCH_BYTES = 8 << 20   # MODA_B200_STATIC_SCRATCH_BYTES
 
 # every symbol include/moda_b200.h declares
 EXPORTED_SYMBOLS = (
     "moda_b200_fwd",
     "moda_b200_bwd_workspace_bytes",
     "moda_b200_bwd",
+    "moda_b200_bwd_static_scratch",
     "moda_b200_check_problem",
     "moda_b200_resolve_path",
     "moda_b200_profile_begin",
@@ -89,6 +91,8 @@ def load() -> ctypes.CDLL:
     lib.moda_b200_bwd_workspace_bytes.restype = ctypes.c_int
     lib.moda_b200_bwd.argtypes = [P] + [T] * 6 + [V] + [T] * 6 + [V, ctypes.c_size_t, V]
     lib.moda_b200_bwd.restype = ctypes.c_int
+    lib.moda_b200_bwd_static_scratch.argtypes = [P] + [T] * 6 + [V] + [T] * 6 + [V]
+    lib.moda_b200_bwd_static_scratch.restype = ctypes.c_int
     lib.moda_b200_check_problem.argtypes = [P]
     lib.moda_b200_check_problem.restype = ctypes.c_int
     lib.moda_b200_resolve_path.argtypes = [P, ctypes.c_int]

@@ -336,6 +336,49 @@ int moda_b200_debug_set(void* dump, int variant) {
   return MODA_OK;
 }
 
+// ---- backward without any caller-provided or library-allocated scratch ---------------
+// The scratch of the backward lives in this file-scope device array.  In host code the
+// name g_static_scratch is only a handle for the runtime; the address kernels can use is
+// obtained per device with cudaGetSymbolAddress and cached below.
+static __device__ __align__(256) unsigned char g_static_scratch[MODA_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mu;
+void* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the CURRENT device (resolved once per device).
+int static_scratch_address(int device, void** out) {
+  if (device < 0 || device >= kMaxDevices) return MODA_ERR_SHAPE;
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  if (g_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return cuda_fail(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+    g_scratch_ptr[device] = ptr;
+  }
+  *out = g_scratch_ptr[device];
+  return MODA_OK;
+}
+}  // namespace
+
+int moda_b200_bwd_static_scratch(const moda_problem* prob, const moda_tensor4* q, const moda_tensor4* k,
+                                 const moda_tensor4* v, const moda_tensor4* depth_k,
+                                 const moda_tensor4* depth_v, const moda_tensor4* o, const float* lse,
+                                 const moda_tensor4* dout, const moda_tensor4* dq, const moda_tensor4* dk,
+                                 const moda_tensor4* dv, const moda_tensor4* d_depth_k,
+                                 const moda_tensor4* d_depth_v, void* stream) {
+  size_t need = 0;
+  if (int rc = moda_b200_bwd_workspace_bytes(prob, &need)) return rc;
+  if (need > (size_t)MODA_B200_STATIC_SCRATCH_BYTES) return MODA_ERR_TOO_LARGE;
+  DeviceGuard guard(prob->device);          // the symbol address is per device: resolve it with
+  if (!guard.ok) return cuda_fail(guard.err);  // the problem's device current
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(prob->device, &scratch)) return rc;
+  return moda_b200_bwd(prob, q, k, v, depth_k, depth_v, o, lse, dout, dq, dk, dv, d_depth_k, d_depth_v,
+                       scratch, (size_t)MODA_B200_STATIC_SCRATCH_BYTES, stream);
+}
+
 int moda_b200_last_launch_count(void) { return g_last_launches; }
 int moda_b200_last_cuda_error(void) { return g_last_cuda_error; }
 

@@ -350,3 +350,40 @@ def moda_attention(q, k, v, depth_k=None, depth_v=None, is_causal=True, chunk_si
         o, lse = parallel_moda(qf, k, v, cached_k=ck, cached_v=cv, scale=scale, moda_group_num=G,
                                is_causal=is_causal, need_lse=True, warn_shape=False)
     return o.reshape(B, T, G * Hkv, D), lse.reshape(B, T, G * Hkv)
+
+
+# ---- backward for callers that may not allocate -----------------------------------
+def backward_into_static_scratch(q, k, v, cached_k, cached_v, o, lse, do, dq, dk, dv, d_cached_k,
+                                 d_cached_v, scale, moda_group_num, mode,
+                                 chunk_rows=CHUNK_VISIBLE_QUERY_ROWS) -> None:
+    """Backward into gradient tensors the caller already owns, with the kernels' scratch
+    taken from the fixed device array inside the library (``moda_b200_bwd_static_scratch``).
+
+    Nothing is allocated here, neither by torch nor by CUDA: this is the form for callers
+    that run where allocation is off limits (inside a region that must not call
+    ``cudaMalloc``, or a callback that only receives its buffers).  All tensors must
+    already be in a layout the library consumes in place (innermost stride 1, other
+    strides multiples of 8 elements, 16-byte aligned) — they are not copied.  Raises
+    ``ModaLibraryError`` (status ``MODA_ERR_TOO_LARGE``) when the problem needs more than
+    ``_cabi.STATIC_SCRATCH_BYTES`` of scratch.  The array is shared by all calls on a
+    device: do not let two such calls overlap on the GPU, and make the first call on a
+    device outside stream capture (it resolves the array's address).
+    """
+    B, T_q, H, D = q.shape
+    T_kv = T_q // moda_group_num
+    use_depth = cached_k is not None and cached_v is not None
+    L = cached_k.shape[1] // T_kv if use_depth else 0
+    for x in (q, k, v, cached_k, cached_v, o, do, dq, dk, dv, d_cached_k, d_cached_v):
+        if x is not None and _usable(x) is not x:
+            raise ValueError("backward_into_static_scratch does not copy: pass tensors with innermost "
+                             "stride 1, other strides multiples of 8, 16-byte aligned")
+    assert lse.dtype == torch.float32 and lse.is_contiguous()
+    prob = _problem(q, T_kv, L, moda_group_num, mode, scale, chunk_rows)
+    lib = _cabi.load()
+    ts = list(map(_t4, (q, k, v, cached_k, cached_v, o)))
+    gs = list(map(_t4, (do, dq, dk, dv, d_cached_k, d_cached_v)))
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = lib.moda_b200_bwd_static_scratch(ctypes.byref(prob), *[_ref(t) for t in ts], lse.data_ptr(),
+                                              *[_ref(t) for t in gs], stream)
+    _cabi.check(rc, "moda_b200_bwd_static_scratch")
