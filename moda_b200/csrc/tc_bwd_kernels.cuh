@@ -5,36 +5,41 @@
 // owning CTA, so there are no atomics and results are bit-reproducible.
 //
 //   pre_kernel : delta = rowsum(o * dout) (stored o, fp32 accumulate: moda_v14.py:525-539)
-//                written, with a copy of lse, as [B, H, T_q rounded up to 64] so that a
-//                (b, h) slice of 64 rows is one contiguous 256-byte bulk copy.
+//                written, with a copy of lse, as [B, H, T_q rounded up to 64 (+64)] so that
+//                a (b, h) slice of 64 rows is one contiguous 256-byte bulk copy.
 //   dq_kernel  : CTA = 128 query rows; walks the visible key tiles in steps of 64 keys.
-//                S = Q K^T, dP = dO V^T (SS MMAs, N = 64) -> softmax warps form
-//                dS = P (dP - delta) in the input dtype in TMEM -> dQ += dS K (TS MMA,
-//                K tile read MN-major).  dq = scale * dQ (moda_v14.py:860).
+//                Q and dO rows sit in TMEM as 16-bit A operands for the whole CTA, so the
+//                score MMAs S = Q K^T, dP = dO V^T (N = 64) read only the K / V step tile
+//                from shared memory; softmax warps form dS = P (dP - delta) in TMEM;
+//                dQ += dS K (A from TMEM, K tile read MN-major).  dq = scale * dQ.
 //   dkv_kernel : CTA = 128 keys of the sequence K/V or of the depth K/V; walks the query
 //                rows that can see them in steps of 64 rows.  S^T = K Q^T, dP^T = V dO^T
-//                (SS, N = 64) -> P^T and dS^T in TMEM -> dV += P^T dO, dK += dS^T Q (TS
-//                MMAs, Q/dO tiles read MN-major).  dk = scale * dK (moda_v14.py:1019).
+//                (both operands in shared memory, N = 64) -> P^T and dS^T in TMEM ->
+//                dV += P^T dO, dK += dS^T Q (A from TMEM, Q/dO tiles read MN-major).
 //                The G heads of a KV head are rows of the same folded query tile, so the
-//                GQA sum happens inside the MMA.
+//                GQA sum happens inside the MMA.  dk = scale * dK.
 //
-// Both MMA kernels run one CTA per SM with a software pipeline: two TMEM stages for the
-// score tiles (the tensor core computes step i+1 while the softmax warps work on step i)
-// and a four-deep TMA ring for the per-step operand tiles.  The tensor pipe executes the
-// MMAs of one issuing thread in order, which is what allows step i+2's scores to reuse the
-// TMEM stage the step-i update reads from without a wait in between.
+// Both MMA kernels run one CTA per SM with four roles: a TMA warp that keeps a ring of
+// step tiles full, an MMA warp, and two softmax warpgroups that take alternate steps (each
+// owns one of the two TMEM score stages).  The tensor pipe executes the MMAs of one issuing
+// thread in order, which is what allows step i+2's scores to reuse the TMEM stage the step-i
+// update reads from without a wait in between; ring slots are handed back to the TMA warp by
+// a tcgen05.commit on the slot's "empty" barrier after the update that last read them.
 #pragma once
 #include "tc_kernels.cuh"
 
 namespace moda {
 namespace tc {
 
-constexpr int kStep = 64;            // keys (dq) or query rows (dkv) per pipeline step
-constexpr int kRing = 4;             // operand ring depth
+constexpr int kStep = 64;                      // keys (dq) or query rows (dkv) per pipeline step
+constexpr int kDqRing = 6;                     // dq: ring of {K, V} step tiles
+constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delta} step tiles
 constexpr uint32_t kStepTile = 64 * 128 * 2;   // one [64 x 128] 16-bit tile (two 8 KB boxes)
 constexpr uint32_t kStepHalf = kStepTile / 2;
+constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
+constexpr int kBwdThreads = 320;               // 8 softmax warps + MMA warp + TMA warp
 
-struct DqMaps { CUtensorMap q, dout, k, v, kd, vd; };      // q, dout: 128-row boxes; others 64-row
+struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
 struct DkvMaps { CUtensorMap k, v, kd, vd, q, dout; };     // k, v, kd, vd: 128-row boxes; q, dout 64-row
 
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -73,28 +78,49 @@ __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params
   }
 }
 
-enum BwdBar : int { kBRes = 0, kBIn0 = 1, kBS0 = 5, kBP0 = 7, kBT0 = 9, kBwdBarCount = 11 };
+// Control block shared by both kernels (placed after the tiles):
+//   [0, 8*kMaxBars) mbarriers; then the TMEM base slot, the abort flag and the drain flag.
+constexpr int kMaxBars = 20;
+constexpr uint32_t kCtlBytes = 8 * kMaxBars + 32;
+struct BwdBars {          // barrier indices for a ring of R slots
+  int res, full0, empty0, s0, p0, done;
+  __host__ __device__ constexpr explicit BwdBars(int R)
+      : res(0), full0(1), empty0(1 + R), s0(1 + 2 * R), p0(3 + 2 * R), done(5 + 2 * R) {}
+};
+static_assert(5 + 2 * kDqRing < kMaxBars && 5 + 2 * kDkvRing < kMaxBars, "control block too small");
+
+// Base of a 128-byte-swizzle descriptor for a tile at `addr`; per-MMA offsets (multiples of
+// 16 bytes, staying inside the tile) are added to the low word.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) { return smem_desc_sw128(addr, 16, 1024); }
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_stride) {
+  return smem_desc_sw128(addr, block_stride, 1024);
+}
+__device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { return d + (uint64_t)(byte_off >> 4); }
 
 // ============================================================================ dq
-// grid (ceil(T_q/128), H, B), 160 threads.  TMEM (512 columns allocated):
-//   stage s in {0,1}: [s*128, s*128+64) S (fp32) / dS (16-bit, first 32 columns),
-//                     [s*128+64, s*128+128) dP (fp32);   [256, 384) dQ (fp32).
-// Shared memory: Q, dO (32 KB each, resident), ring of kRing x {K step tile, V step tile}.
+// grid (ceil(T_q/128), H, B), 320 threads.  TMEM (512 columns):
+//   stage s in {0,1}: [s*128, +64) S (fp32) / dS (16-bit, first 32 columns), [s*128+64, +64) dP;
+//   [256, 384) dQ (fp32);  [384, 448) Q (16-bit A operand);  [448, 512) dO (16-bit A operand).
+// Shared memory: ring of kDqRing x {K step tile, V step tile} (32 KB per slot).
 template <typename T>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
           const float* lse_t, int T_qp) {
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t raw_u32 = smem_u32(smem_raw);
-  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
-  unsigned char* gbase = smem_raw + (base - raw_u32);
-  const uint32_t sQ = base, sDO = base + kTileBytes, sRing = base + 2 * kTileBytes;   // ring slot: K then V
-  const uint32_t ctl_off = 2 * kTileBytes + kRing * 2 * kStepTile;
+  constexpr int R = kDqRing;
+  constexpr BwdBars B_(R);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {   // the 128-byte swizzle needs 1024-byte aligned tiles
+    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    return;
+  }
+  const uint32_t sRing = base;
+  const uint32_t ctl_off = R * 2 * kStepTile;
   const uint32_t bars = base + ctl_off;
-  unsigned char* gctl = gbase + ctl_off;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 104);
-  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 108);
+  unsigned char* gctl = smem_raw + ctl_off;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 8 * kMaxBars + 4);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 8 * kMaxBars + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
@@ -103,8 +129,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
   const int qt = n_qt - 1 - (int)blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int r0 = qt * kBM;
-  // key walk in steps of 64
-  int n_seq, n_dep, dep_c0, seq_full_hi;
+  int n_seq, n_dep, dep_c0, seq_full_hi;   // key walk in steps of 64
   {
     const int r_last = min(r0 + kBM, p.T_q) - 1;
     int lo, hi, lo2, hi2;
@@ -120,39 +145,38 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
   const int n = n_seq + n_dep;
 
   if (tid == 0) {
-    mbar_init(bars + 8 * kBRes, 1);
-    for (int i = 0; i < kRing; ++i) mbar_init(bars + 8 * (kBIn0 + i), 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 8 * (kBS0 + i), 1);
-      mbar_init(bars + 8 * (kBP0 + i), 128);
-      mbar_init(bars + 8 * (kBT0 + i), 1);
-    }
+    mbar_init(bars + 8 * B_.res, 256);
+    mbar_init(bars + 8 * B_.done, 1);
+    for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128); }
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
-    tmem_alloc(bars + 96, 512);
+    tmem_alloc(bars + 8 * kMaxBars, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_dQ = tmem + 256;
+  const uint32_t tmem_dQ = tmem + 256, tmem_Q = tmem + 384, tmem_dO = tmem + 448;
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-  if (warp == 4) {
-    if (lane == 0 && n > 0) {
-      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
-      uint32_t pending = 0;   // ring slots with a load in flight
-      uint32_t pend_par[kRing] = {0, 0, 0, 0};
-      auto load_step = [&](int i) {
+  if (warp == 9) {
+    // ---------------------------------------------------------------- TMA warp
+    if (lane == 0) {
+      prefetch_map(&maps.k); prefetch_map(&maps.v);
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; ok && i < n; ++i) {
+        const uint32_t slot = i % R;
+        if (i >= R && !(ok = mbar_wait(bars + 8 * (B_.empty0 + slot), ((i / R) - 1) & 1, abort_flag, B_.empty0 + slot))) break;
         const bool dep = i >= n_seq;
         const int row = dep ? dep_c0 + (i - n_seq) * kStep : i * kStep;
-        const uint32_t slot = i % kRing, dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (kBIn0 + slot);
+        const uint32_t dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (B_.full0 + slot);
         const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         mbar_expect_tx(bar, 2 * kStepTile);
@@ -160,73 +184,86 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
         tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
         tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
-        pending |= 1u << slot; pend_par[slot] = (i / kRing) & 1;
-      };
+        issued = i + 1;
+      }
+      if (!ok) {   // let loads in flight land before the CTA's shared memory is released
+        for (int i = max(0, issued - R); i < issued; ++i)
+          mbar_wait(bars + 8 * (B_.full0 + i % R), (i / R) & 1, drain_flag, B_.full0 + i % R);
+      }
+    }
+  } else if (warp == 8) {
+    // ---------------------------------------------------------------- MMA warp
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
       auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T, dP(i) = dO V(i)^T into TMEM stage i&1
-        const uint32_t slot = i % kRing, sK = sRing + slot * 2 * kStepTile, sV = sK + kStepTile;
+        const uint32_t sK = sRing + (i % R) * 2 * kStepTile;
+        const uint64_t dk = desc_kmajor(sK), dv = desc_kmajor(sK + kStepTile);
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
-          mma_ss(tS, smem_desc_sw128(sQ + offA, 16, 1024), smem_desc_sw128(sK + offB, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(tS, tmem_Q + kk * 8, desc_add(dk, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
-          mma_ss(tP, smem_desc_sw128(sDO + offA, 16, 1024), smem_desc_sw128(sV + offB, 16, 1024), idesc_s, kk > 0);
-        }
-        tc_commit(bars + 8 * (kBS0 + (i & 1)));
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(tP, tmem_dO + kk * 8, desc_add(dv, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+        tc_commit(bars + 8 * (B_.s0 + (i & 1)));
       };
-      prefetch_map(&maps.q); prefetch_map(&maps.dout); prefetch_map(&maps.k); prefetch_map(&maps.v);
-      mbar_expect_tx(bars + 8 * kBRes, 2 * kTileBytes);
-      tma_load_4d(sQ, &maps.q, bars + 8 * kBRes, 0, h, r0, b);
-      tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * kBRes, 64, h, r0, b);
-      tma_load_4d(sDO, &maps.dout, bars + 8 * kBRes, 0, h, r0, b);
-      tma_load_4d(sDO + kHalfBytes, &maps.dout, bars + 8 * kBRes, 64, h, r0, b);
-      for (int i = 0; i < 3 && i < n; ++i) load_step(i);
-      bool ok = mbar_wait(bars + 8 * kBRes, 0, abort_flag, kBRes);
+      bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // Q, dO are in TMEM
+      tc_fence_after();
       for (int i = 0; ok && i < 2 && i < n; ++i) {
-        if (!(ok = mbar_wait(bars + 8 * (kBIn0 + i), 0, abort_flag, kBIn0 + i))) break;
-        pending &= ~(1u << i);
+        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + i), 0, abort_flag, B_.full0 + i))) break;
         tc_fence_after();
         issue_scores(i);
       }
       for (int j = 0; ok && j < n; ++j) {
-        // dQ += dS(j) K(j)
-        if (!(ok = mbar_wait(bars + 8 * (kBP0 + (j & 1)), (j >> 1) & 1, abort_flag, kBP0 + (j & 1)))) break;
+        if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
         tc_fence_after();
-        {
-          const uint32_t slot = j % kRing, sK = sRing + slot * 2 * kStepTile;
+        {   // dQ += dS(j) K(j)
+          const uint32_t slot = j % R;
+          const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
           const uint32_t tA = tmem + (j & 1) * 128;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ts(tmem_dQ, tA + kk * 8, smem_desc_sw128(sK + kk * 2048, kStepHalf, 1024), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(bars + 8 * (kBT0 + (j & 1)));
+            mma_ts(tmem_dQ, tA + kk * 8, desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
+          if (j == n - 1) tc_commit(bars + 8 * B_.done);
         }
         if (j + 2 < n) {
           const int i = j + 2;
-          const uint32_t slot = i % kRing;
-          if (!(ok = mbar_wait(bars + 8 * (kBIn0 + slot), (i / kRing) & 1, abort_flag, kBIn0 + slot))) break;
-          pending &= ~(1u << slot);
+          const uint32_t slot = i % R;
+          if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
           tc_fence_after();
           issue_scores(i);
         }
-        if (j + 3 < n) {   // ring slot of step j+3 was last read by the update of step j-1
-          if (j >= 1) {
-            if (!(ok = mbar_wait(bars + 8 * (kBT0 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, kBT0 + ((j - 1) & 1)))) break;
-          }
-          load_step(j + 3);
-        }
-      }
-      if (!ok) {   // let loads in flight land before the CTA's shared memory is released
-        for (int s = 0; s < kRing; ++s)
-          if (pending & (1u << s)) mbar_wait(bars + 8 * (kBIn0 + s), pend_par[s], drain_flag, kBIn0 + s);
       }
     }
   } else {
-    const int row = warp * 32 + lane;
+    // ---------------------------------------------------------------- softmax warpgroups
+    const int wg = warp >> 2, quarter = warp & 3;   // warpgroup g takes steps i with (i & 1) == g
+    const int row = quarter * 32 + lane;
     const int r = r0 + row;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    {   // stage this thread's Q row (warpgroup 0) or dO row (warpgroup 1) into TMEM as an A operand
+      uint32_t regs[64];
+      if (r < p.T_q) {
+        const View& src = (wg == 0) ? p.q : p.dout;
+        const uint4* g4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(src.ptr) + src.off(b, r, h));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint4 v4 = g4[i];
+          regs[4 * i] = v4.x; regs[4 * i + 1] = v4.y; regs[4 * i + 2] = v4.z; regs[4 * i + 3] = v4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) regs[i] = 0u;
+      }
+      const uint32_t dst = ((wg == 0) ? tmem_Q : tmem_dO) + lane_addr;
+      tmem_st32<0>(dst, regs);
+      tmem_st32<32>(dst + 32, regs);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * B_.res);
+    }
     int slo, shi, dlo, dhi;
     seq_interval(p, r, slo, shi);
     dep_interval(p, r, dlo, dhi);
@@ -237,8 +274,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     }
     const float c = p.scale_log2;
     bool ok = true;
-    for (int i = 0; i < n; ++i) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBS0 + (i & 1)), (i >> 1) & 1, abort_flag, kBS0 + (i & 1)));
+    for (int i = wg; i < n; i += 2) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.s0 + (i & 1)), (i >> 1) & 1, abort_flag, B_.s0 + (i & 1)));
       if (!ok) break;
       tc_fence_after();
       const bool is_dep = i >= n_seq;
@@ -267,14 +304,14 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       tmem_st32<0>(tS, pk);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bars + 8 * (kBP0 + (i & 1)));
+      mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
     }
-    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBT0 + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, kBT0 + ((n - 1) & 1)));
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
     if (ok && n > 0) {
       tc_fence_after();
       T* gdq = reinterpret_cast<T*>(p.dq.ptr) + p.dq.off(b, r, h);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {   // each warpgroup stores half of the row
         uint32_t ov[32];
         tmem_ld32<0>(tmem_dQ + lane_addr + q4 * 32, ov);
         tmem_wait_ld();
@@ -301,30 +338,32 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 }
 
 // =========================================================================== dk / dv
-// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 160 threads; key tiles of 128.
+// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 320 threads; key tiles of 128.
 // TMEM (512 columns): stage s: [s*128, +64) S^T / P^T (16-bit, 32 columns),
 //   [s*128+64, +64) dP^T / dS^T (16-bit, 32 columns); [256,384) dV; [384,512) dK.
-// Shared memory: K, V tile (32 KB each, resident), ring of kRing x {Q step tile, dO step
-// tile, 64 lse, 64 delta}.
-constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
-
+// Shared memory: K, V tile (32 KB each, resident), ring of kDkvRing x {Q step tile, dO step
+// tile} followed by the ring of {64 lse, 64 delta}.
 template <typename T>
-__global__ void __launch_bounds__(160, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
            const float* lse_t, int T_qp, int n_seq_key_tiles) {
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t raw_u32 = smem_u32(smem_raw);
-  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
-  unsigned char* gbase = smem_raw + (base - raw_u32);
+  constexpr int R = kDkvRing;
+  constexpr BwdBars B_(R);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    return;
+  }
   const uint32_t sK = base, sV = base + kTileBytes, sRing = base + 2 * kTileBytes;
-  // ring slot layout: [Q 16 KB][dO 16 KB] for all slots first (keeps tiles 1024-aligned), stats after
-  const uint32_t sStat = sRing + kRing * 2 * kStepTile;
-  const uint32_t ctl_off = 2 * kTileBytes + kRing * kDkvSlot;
+  const uint32_t stat_off = 2 * kTileBytes + R * 2 * kStepTile;
+  const uint32_t sStat = base + stat_off;
+  const uint32_t ctl_off = 2 * kTileBytes + R * kDkvSlot;
   const uint32_t bars = base + ctl_off;
-  unsigned char* gctl = gbase + ctl_off;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 104);
-  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 108);
+  unsigned char* gctl = smem_raw + ctl_off;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 8 * kMaxBars + 4);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 8 * kMaxBars + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
@@ -350,20 +389,17 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
   const int n = (q_end - q_begin + kStep - 1) / kStep;
 
   if (tid == 0) {
-    mbar_init(bars + 8 * kBRes, 1);
-    for (int i = 0; i < kRing; ++i) mbar_init(bars + 8 * (kBIn0 + i), 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 8 * (kBS0 + i), 1);
-      mbar_init(bars + 8 * (kBP0 + i), 128);
-      mbar_init(bars + 8 * (kBT0 + i), 1);
-    }
+    mbar_init(bars + 8 * B_.res, 1);
+    mbar_init(bars + 8 * B_.done, 1);
+    for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128); }
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
-    tmem_alloc(bars + 96, 512);
+    tmem_alloc(bars + 8 * kMaxBars, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -374,15 +410,24 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   const int64_t stat_base = ((int64_t)b * p.H + h) * T_qp;
 
-  if (warp == 4) {
+  if (warp == 9) {
+    // ---------------------------------------------------------------- TMA warp
     if (lane == 0 && n > 0) {
-      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
-      uint32_t pending = 0;
-      uint32_t pend_par[kRing] = {0, 0, 0, 0};
-      auto load_step = [&](int i) {
+      const CUtensorMap* mk = is_dep ? &maps.kd : &maps.k;
+      const CUtensorMap* mv = is_dep ? &maps.vd : &maps.v;
+      prefetch_map(mk); prefetch_map(mv); prefetch_map(&maps.q); prefetch_map(&maps.dout);
+      mbar_expect_tx(bars + 8 * B_.res, 2 * kTileBytes);
+      tma_load_4d(sK, mk, bars + 8 * B_.res, 0, h, c0, b);
+      tma_load_4d(sK + kHalfBytes, mk, bars + 8 * B_.res, 64, h, c0, b);
+      tma_load_4d(sV, mv, bars + 8 * B_.res, 0, h, c0, b);
+      tma_load_4d(sV + kHalfBytes, mv, bars + 8 * B_.res, 64, h, c0, b);
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; ok && i < n; ++i) {
+        const uint32_t slot = i % R;
+        if (i >= R && !(ok = mbar_wait(bars + 8 * (B_.empty0 + slot), ((i / R) - 1) & 1, abort_flag, B_.empty0 + slot))) break;
         const int row = q_begin + i * kStep;
-        const uint32_t slot = i % kRing, dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (kBIn0 + slot);
+        const uint32_t dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (B_.full0 + slot);
         const uint32_t st = sStat + slot * 512;
         mbar_expect_tx(bar, 2 * kStepTile + 512);
         tma_load_4d(dst, &maps.q, bar, 0, h, row, b);
@@ -391,78 +436,70 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         tma_load_4d(dst + kStepTile + kStepHalf, &maps.dout, bar, 64, h, row, b);
         bulk_load(st, lse_t + stat_base + row, 256, bar);
         bulk_load(st + 256, delta_t + stat_base + row, 256, bar);
-        pending |= 1u << slot; pend_par[slot] = (i / kRing) & 1;
-      };
+        issued = i + 1;
+      }
+      if (!ok) {
+        mbar_wait(bars + 8 * B_.res, 0, drain_flag, B_.res);
+        for (int i = max(0, issued - R); i < issued; ++i)
+          mbar_wait(bars + 8 * (B_.full0 + i % R), (i / R) & 1, drain_flag, B_.full0 + i % R);
+      }
+    }
+  } else if (warp == 8) {
+    // ---------------------------------------------------------------- MMA warp
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      const uint64_t dK = desc_kmajor(sK), dV = desc_kmajor(sV);
       auto issue_scores = [&](int i) {   // S^T(i) = K Q(i)^T, dP^T(i) = V dO(i)^T
-        const uint32_t slot = i % kRing, sQ = sRing + slot * 2 * kStepTile, sDO = sQ + kStepTile;
+        const uint32_t sQ = sRing + (i % R) * 2 * kStepTile;
+        const uint64_t dq = desc_kmajor(sQ), ddo = desc_kmajor(sQ + kStepTile);
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
-          mma_ss(tS, smem_desc_sw128(sK + offA, 16, 1024), smem_desc_sw128(sQ + offB, 16, 1024), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t offA = (kk >> 2) * kHalfBytes + (kk & 3) * 32, offB = (kk >> 2) * kStepHalf + (kk & 3) * 32;
-          mma_ss(tP, smem_desc_sw128(sV + offA, 16, 1024), smem_desc_sw128(sDO + offB, 16, 1024), idesc_s, kk > 0);
-        }
-        tc_commit(bars + 8 * (kBS0 + (i & 1)));
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+        tc_commit(bars + 8 * (B_.s0 + (i & 1)));
       };
-      const CUtensorMap* mk = is_dep ? &maps.kd : &maps.k;
-      const CUtensorMap* mv = is_dep ? &maps.vd : &maps.v;
-      prefetch_map(mk); prefetch_map(mv); prefetch_map(&maps.q); prefetch_map(&maps.dout);
-      mbar_expect_tx(bars + 8 * kBRes, 2 * kTileBytes);
-      tma_load_4d(sK, mk, bars + 8 * kBRes, 0, h, c0, b);
-      tma_load_4d(sK + kHalfBytes, mk, bars + 8 * kBRes, 64, h, c0, b);
-      tma_load_4d(sV, mv, bars + 8 * kBRes, 0, h, c0, b);
-      tma_load_4d(sV + kHalfBytes, mv, bars + 8 * kBRes, 64, h, c0, b);
-      for (int i = 0; i < 3 && i < n; ++i) load_step(i);
-      bool ok = mbar_wait(bars + 8 * kBRes, 0, abort_flag, kBRes);
+      bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);
       for (int i = 0; ok && i < 2 && i < n; ++i) {
-        if (!(ok = mbar_wait(bars + 8 * (kBIn0 + i), 0, abort_flag, kBIn0 + i))) break;
-        pending &= ~(1u << i);
+        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + i), 0, abort_flag, B_.full0 + i))) break;
         tc_fence_after();
         issue_scores(i);
       }
       for (int j = 0; ok && j < n; ++j) {
-        if (!(ok = mbar_wait(bars + 8 * (kBP0 + (j & 1)), (j >> 1) & 1, abort_flag, kBP0 + (j & 1)))) break;
+        if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
         tc_fence_after();
         {
-          const uint32_t slot = j % kRing, sQ = sRing + slot * 2 * kStepTile, sDO = sQ + kStepTile;
+          const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
+          const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);
           const uint32_t tPt = tmem + (j & 1) * 128, tDSt = tPt + 64;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO
-            mma_ts(tmem_dV, tPt + kk * 8, smem_desc_sw128(sDO + kk * 2048, kStepHalf, 1024), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            mma_ts(tmem_dV, tPt + kk * 8, desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
-            mma_ts(tmem_dK, tDSt + kk * 8, smem_desc_sw128(sQ + kk * 2048, kStepHalf, 1024), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(bars + 8 * (kBT0 + (j & 1)));
+            mma_ts(tmem_dK, tDSt + kk * 8, desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bars + 8 * (B_.empty0 + slot));
+          if (j == n - 1) tc_commit(bars + 8 * B_.done);
         }
         if (j + 2 < n) {
           const int i = j + 2;
-          const uint32_t slot = i % kRing;
-          if (!(ok = mbar_wait(bars + 8 * (kBIn0 + slot), (i / kRing) & 1, abort_flag, kBIn0 + slot))) break;
-          pending &= ~(1u << slot);
+          const uint32_t slot = i % R;
+          if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
           tc_fence_after();
           issue_scores(i);
         }
-        if (j + 3 < n) {
-          if (j >= 1) {
-            if (!(ok = mbar_wait(bars + 8 * (kBT0 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag, kBT0 + ((j - 1) & 1)))) break;
-          }
-          load_step(j + 3);
-        }
-      }
-      if (!ok) {   // let loads in flight land before the CTA's shared memory is released
-        for (int s = 0; s < kRing; ++s)
-          if (pending & (1u << s)) mbar_wait(bars + 8 * (kBIn0 + s), pend_par[s], drain_flag, kBIn0 + s);
       }
     }
   } else {
-    const int row = warp * 32 + lane;       // key row of the tile == TMEM lane
+    // ---------------------------------------------------------------- softmax warpgroups
+    const int wg = warp >> 2, quarter = warp & 3;   // warpgroup g takes steps i with (i & 1) == g
+    const int row = quarter * 32 + lane;             // key row of the tile == TMEM lane
     const int key = c0 + row;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    // query rows [rlo, rhi) that see this key (see the visibility rule in common.cuh, inverted)
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    // query rows [rlo, rhi) that see this key (the visibility rule of common.cuh, inverted)
     int rlo, rhi;
     if (key >= n_keys) { rlo = 0; rhi = 0; }
     else if (!is_dep) { rlo = (p.mode == kNonCausal) ? 0 : key * p.G; rhi = p.T_q; }
@@ -476,17 +513,17 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     const bool tail_keys = (c0 + kBN > n_keys);
     const float c = p.scale_log2;
     bool ok = true;
-    for (int i = 0; i < n; ++i) {
-      const uint32_t slot = i % kRing;
-      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBIn0 + slot), (i / kRing) & 1, abort_flag, kBIn0 + slot));
+    for (int i = wg; i < n; i += 2) {
+      const uint32_t slot = i % R;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot));
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBS0 + (i & 1)), (i >> 1) & 1, abort_flag, kBS0 + (i & 1)));
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.s0 + (i & 1)), (i >> 1) & 1, abort_flag, B_.s0 + (i & 1)));
       if (!ok) break;
       tc_fence_after();
       const int q0 = q_begin + i * kStep;
       const bool masked = is_dep || tail_keys || q0 < tile_rlo_max || q0 + kStep > p.T_q;
       const uint32_t tS = tmem + (i & 1) * 128 + lane_addr;
-      const float4* st4 = reinterpret_cast<const float4*>(gbase + (sStat - base) + slot * 512);
+      const float4* st4 = reinterpret_cast<const float4*>(smem_raw + stat_off + slot * 512);
       uint32_t su[64], du[64];
       tmem_ld32<0>(tS, su);
       tmem_ld32<32>(tS + 32, su);
@@ -517,35 +554,29 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       tmem_st32<0>(tS + 64, pd);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bars + 8 * (kBP0 + (i & 1)));
+      mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
     }
-    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (kBT0 + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag, kBT0 + ((n - 1) & 1)));
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
     if (ok && n > 0) {
       tc_fence_after();
-      const View& okv = is_dep ? p.dkd : p.dk;
-      const View& ovv = is_dep ? p.dvd : p.dv;
-      T* gdk = reinterpret_cast<T*>(okv.ptr) + okv.off(b, key, h);
-      T* gdv = reinterpret_cast<T*>(ovv.ptr) + ovv.off(b, key, h);
+      const View& ov = (wg == 0) ? (is_dep ? p.dvd : p.dv) : (is_dep ? p.dkd : p.dk);
+      T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, key, h);
+      const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;      // warpgroup 0 stores dV, warpgroup 1 dK
+      const float mul = (wg == 0) ? 1.f : p.scale;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
-        uint32_t ov[32], ok2[32];
-        tmem_ld32<0>(tmem_dV + lane_addr + q4 * 32, ov);
-        tmem_ld32<0>(tmem_dK + lane_addr + q4 * 32, ok2);
+        uint32_t ov32[32];
+        tmem_ld32<0>(tsrc + lane_addr + q4 * 32, ov32);
         tmem_wait_ld();
         if (key < n_keys) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint4 v4, k4;
-            v4.x = Pack<T>::pack(__uint_as_float(ov[i * 8 + 0]), __uint_as_float(ov[i * 8 + 1]));
-            v4.y = Pack<T>::pack(__uint_as_float(ov[i * 8 + 2]), __uint_as_float(ov[i * 8 + 3]));
-            v4.z = Pack<T>::pack(__uint_as_float(ov[i * 8 + 4]), __uint_as_float(ov[i * 8 + 5]));
-            v4.w = Pack<T>::pack(__uint_as_float(ov[i * 8 + 6]), __uint_as_float(ov[i * 8 + 7]));
-            k4.x = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 0]) * p.scale, __uint_as_float(ok2[i * 8 + 1]) * p.scale);
-            k4.y = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 2]) * p.scale, __uint_as_float(ok2[i * 8 + 3]) * p.scale);
-            k4.z = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 4]) * p.scale, __uint_as_float(ok2[i * 8 + 5]) * p.scale);
-            k4.w = Pack<T>::pack(__uint_as_float(ok2[i * 8 + 6]) * p.scale, __uint_as_float(ok2[i * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(gdv + q4 * 32 + i * 8) = v4;
-            *reinterpret_cast<uint4*>(gdk + q4 * 32 + i * 8) = k4;
+            uint4 v4;
+            v4.x = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 0]) * mul, __uint_as_float(ov32[i * 8 + 1]) * mul);
+            v4.y = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 2]) * mul, __uint_as_float(ov32[i * 8 + 3]) * mul);
+            v4.z = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 4]) * mul, __uint_as_float(ov32[i * 8 + 5]) * mul);
+            v4.w = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 6]) * mul, __uint_as_float(ov32[i * 8 + 7]) * mul);
+            *reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8) = v4;
           }
         }
       }
@@ -573,7 +604,7 @@ inline bool make_map_rows(CUtensorMap* m, const View& v, int dtype, int B, int64
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-inline int padded_rows(int T_q) { return (T_q + 63) / 64 * 64 + 64; }   // +64: a step may start in the last block
+inline int padded_rows(int T_q) { return (T_q + 63) / 64 * 64 + 64; }
 
 inline bool bwd_supported(const moda_problem* pr) {
   return pr->D == 128 && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
@@ -595,9 +626,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
 
   DqMaps dqm; DkvMaps dkm;
   memset(&dqm, 0, sizeof(dqm)); memset(&dkm, 0, sizeof(dkm));
-  bool ok = make_map_rows(&dqm.q, p.q, pr->dtype, p.B, p.T_q, p.H, 128) &&
-            make_map_rows(&dqm.dout, p.dout, pr->dtype, p.B, p.T_q, p.H, 128) &&
-            make_map_rows(&dqm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 64) &&
+  bool ok = make_map_rows(&dqm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 64) &&
             make_map_rows(&dqm.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 64) &&
             make_map_rows(&dkm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 128) &&
             make_map_rows(&dkm.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 128) &&
@@ -627,13 +656,13 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
   if ((e = cudaGetLastError()) != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
   *launches += 1;
   {
-    const size_t smem = 2 * (size_t)kTileBytes + kRing * 2 * (size_t)kStepTile + 128 + 1024;
+    const size_t smem = kDqRing * 2 * (size_t)kStepTile + kCtlBytes;
     dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
     auto launch = [&](auto kern) -> cudaError_t {
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (er != cudaSuccess) return er;
       prof::Scope ps(prof::kDqTc, st);
-      kern<<<grid, 160, smem, st>>>(p, dqm, delta_t, lse_t, T_qp);
+      kern<<<grid, kBwdThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp);
       return cudaGetLastError();
     };
     e = bf ? launch(dq_kernel<__nv_bfloat16>) : launch(dq_kernel<__half>);
@@ -641,7 +670,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
     *launches += 1;
   }
   {
-    const size_t smem = 2 * (size_t)kTileBytes + kRing * (size_t)kDkvSlot + 128 + 1024;
+    const size_t smem = 2 * (size_t)kTileBytes + kDkvRing * (size_t)kDkvSlot + kCtlBytes;
     const int n_seq = (p.T_kv + kBN - 1) / kBN;
     const int n_dep = (int)((TL + kBN - 1) / kBN);
     dim3 grid(n_seq + n_dep, p.H, p.B);
@@ -649,7 +678,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (er != cudaSuccess) return er;
       prof::Scope ps(prof::kDkvTc, st);
-      kern<<<grid, 160, smem, st>>>(p, dkm, delta_t, lse_t, T_qp, n_seq);
+      kern<<<grid, kBwdThreads, smem, st>>>(p, dkm, delta_t, lse_t, T_qp, n_seq);
       return cudaGetLastError();
     };
     e = bf ? launch(dkv_kernel<__nv_bfloat16>) : launch(dkv_kernel<__half>);

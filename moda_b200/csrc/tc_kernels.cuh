@@ -37,7 +37,8 @@ namespace tc {
 
 constexpr int kBM = 128;
 constexpr int kBN = 128;
-constexpr uint32_t kSpinLimit = 1u << 22;      // polls per wait before giving up
+constexpr uint32_t kWaitHintNs = 20000;        // one try_wait may sleep this long (ns)
+constexpr uint32_t kWaitTries = 10000;         // tries per wait before giving up (<= 0.2 s)
 constexpr uint32_t kTileBytes = 128 * 128 * 2; // one [128 x 128] 16-bit tile
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
 
@@ -67,10 +68,23 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the limit expired or another thread of the CTA
 // already gave up (abort flag); the caller must then leave through the teardown path.
+// The wait sleeps in hardware (mbarrier.try_wait with a suspend-time hint) instead of
+// spinning: a spinning warp takes issue slots from the producer lane and from the softmax
+// warp that shares its SM sub-partition.  Bound: kWaitTries x kWaitHintNs of sleeping.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(kWaitHintNs) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int bar_id) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test(bar, parity)) return true;
-    if ((i & 63u) == 63u && *abort_flag != 0) return false;
+  if (mbar_test(bar, parity)) return true;
+  for (uint32_t i = 0; i < kWaitTries; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
   }
   *abort_flag = 1;
   atomicCAS(&g_tc_status, 0, (1 << 8) | bar_id);
