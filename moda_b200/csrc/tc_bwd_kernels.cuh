@@ -80,14 +80,14 @@ __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params
 
 // Control block shared by both kernels (placed after the tiles):
 //   [0, 8*kMaxBars) mbarriers; then the TMEM base slot, the abort flag and the drain flag.
-constexpr int kMaxBars = 20;
+constexpr int kMaxBars = 24;
 constexpr uint32_t kCtlBytes = 8 * kMaxBars + 32;
 struct BwdBars {          // barrier indices for a ring of R slots
-  int res, full0, empty0, s0, p0, done;
+  int res, full0, empty0, s0, p0, done, r0, t0;
   __host__ __device__ constexpr explicit BwdBars(int R)
-      : res(0), full0(1), empty0(1 + R), s0(1 + 2 * R), p0(3 + 2 * R), done(5 + 2 * R) {}
+      : res(0), full0(1), empty0(1 + R), s0(1 + 2 * R), p0(3 + 2 * R), done(5 + 2 * R), r0(6 + 2 * R), t0(8 + 2 * R) {}
 };
-static_assert(5 + 2 * kDqRing < kMaxBars && 5 + 2 * kDkvRing < kMaxBars, "control block too small");
+static_assert(9 + 2 * kDqRing < kMaxBars && 9 + 2 * kDkvRing < kMaxBars, "control block too small");
 
 // Base of a 128-byte-swizzle descriptor for a tile at `addr`; per-MMA offsets (multiples of
 // 16 bytes, staying inside the tile) are added to the low word.
@@ -99,13 +99,16 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 
 // ============================================================================ dq
 // grid (ceil(T_q/128), H, B), 320 threads.  TMEM (512 columns):
-//   stage s in {0,1}: [s*128, +64) S (fp32) / dS (16-bit, first 32 columns), [s*128+64, +64) dP;
+//   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32);
 //   [256, 384) dQ (fp32);  [384, 448) Q (16-bit A operand);  [448, 512) dO (16-bit A operand).
-// Shared memory: ring of kDqRing x {K step tile, V step tile} (32 KB per slot).
+// Shared memory: ring of kDqRing x {K step tile, V step tile} (32 KB per slot), then two
+// [128 x 64] dS tiles (K-major, 128-byte swizzle).  A softmax warpgroup releases its TMEM stage
+// as soon as it has the scores in registers, so the next-but-one score MMAs overlap its math;
+// dS reaches the update MMA through shared memory.
 template <typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
-          const float* lse_t, int T_qp) {
+          const float* lse_t, int T_qp, unsigned long long* trace) {
   constexpr int R = kDqRing;
   constexpr BwdBars B_(R);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -115,7 +118,9 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     return;
   }
   const uint32_t sRing = base;
-  const uint32_t ctl_off = R * 2 * kStepTile;
+  const uint32_t ds_off = R * 2 * kStepTile;            // two dS tiles of kStepTile bytes
+  const uint32_t sDS = base + ds_off;
+  const uint32_t ctl_off = ds_off + 2 * kStepTile;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
@@ -148,7 +153,10 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     mbar_init(bars + 8 * B_.res, 256);
     mbar_init(bars + 8 * B_.done, 1);
     for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128);
+      mbar_init(bars + 8 * (B_.r0 + i), 128); mbar_init(bars + 8 * (B_.t0 + i), 1);
+    }
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -167,8 +175,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 
   if (warp == 9) {
     // ---------------------------------------------------------------- TMA warp
-    if (lane == 0) {
-      prefetch_map(&maps.k); prefetch_map(&maps.v);
+    {
+      if (elect_one()) { prefetch_map(&maps.k); prefetch_map(&maps.v); }
       bool ok = true;
       int issued = 0;
       for (int i = 0; ok && i < n; ++i) {
@@ -179,11 +187,14 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const uint32_t dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (B_.full0 + slot);
         const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
-        mbar_expect_tx(bar, 2 * kStepTile);
-        tma_load_4d(dst, mk, bar, 0, h, row, b);
-        tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
-        tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
-        tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
+        if (elect_one()) {
+          mbar_expect_tx(bar, 2 * kStepTile);
+          tma_load_4d(dst, mk, bar, 0, h, row, b);
+          tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
+          tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
+          tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
+        }
+        __syncwarp();
         issued = i + 1;
       }
       if (!ok) {   // let loads in flight land before the CTA's shared memory is released
@@ -193,20 +204,22 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     }
   } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA warp
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
       constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
       auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T, dP(i) = dO V(i)^T into TMEM stage i&1
         const uint32_t sK = sRing + (i % R) * 2 * kStepTile;
         const uint64_t dk = desc_kmajor(sK), dv = desc_kmajor(sK + kStepTile);
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ts(tS, tmem_Q + kk * 8, desc_add(dk, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ts(tP, tmem_dO + kk * 8, desc_add(dv, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-        tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+          for (int kk = 0; kk < 8; ++kk) {
+            mma_ts(tS, tmem_Q + kk * 8, desc_add(dk, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ts(tP, tmem_dO + kk * 8, desc_add(dv, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+          }
+          tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+        }
+        __syncwarp();
       };
       bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // Q, dO are in TMEM
       tc_fence_after();
@@ -215,26 +228,38 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         tc_fence_after();
         issue_scores(i);
       }
+      const bool tr = trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && lane == 0;
       for (int j = 0; ok && j < n; ++j) {
-        if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
-        tc_fence_after();
-        {   // dQ += dS(j) K(j)
-          const uint32_t slot = j % R;
-          const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
-          const uint32_t tA = tmem + (j & 1) * 128;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_ts(tmem_dQ, tA + kk * 8, desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
-          if (j == n - 1) tc_commit(bars + 8 * B_.done);
-        }
-        if (j + 2 < n) {
+        if (tr && j < 64) trace[j * 16 + 0] = clock64();
+        if (j + 2 < n) {   // stage j&1 has been read into registers: its next scores may go
           const int i = j + 2;
           const uint32_t slot = i % R;
+          if (!(ok = mbar_wait(bars + 8 * (B_.r0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.r0 + (j & 1)))) break;
+          if (tr && j < 64) trace[j * 16 + 1] = clock64();
           if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
           tc_fence_after();
+          if (tr && j < 64) trace[j * 16 + 2] = clock64();
           issue_scores(i);
+          if (tr && j < 64) trace[j * 16 + 3] = clock64();
         }
+        if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
+        tc_fence_after();
+        if (tr && j < 64) trace[j * 16 + 4] = clock64();
+        {   // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major
+          const uint32_t slot = j % R;
+          const uint64_t da = desc_kmajor(sDS + (j & 1) * kStepTile);
+          const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
+            tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // dS tile j&1 may be rewritten
+            if (j == n - 1) tc_commit(bars + 8 * B_.done);
+          }
+          __syncwarp();
+        }
+        if (tr && j < 64) trace[j * 16 + 5] = clock64();
       }
     }
   } else {
@@ -274,10 +299,13 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     }
     const float c = p.scale_log2;
     bool ok = true;
+    const bool tr = trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && quarter == 0 && lane == 0;
     for (int i = wg; i < n; i += 2) {
+      if (tr && i < 64) trace[i * 16 + 8] = clock64();
       ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.s0 + (i & 1)), (i >> 1) & 1, abort_flag, B_.s0 + (i & 1)));
       if (!ok) break;
       tc_fence_after();
+      if (tr && i < 64) trace[i * 16 + 9] = clock64();
       const bool is_dep = i >= n_seq;
       const int c0 = is_dep ? dep_c0 + (i - n_seq) * kStep : i * kStep;
       const bool masked = is_dep || (c0 + kStep > seq_full_hi);
@@ -289,6 +317,9 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       tmem_ld32<0>(tS + 64, du);
       tmem_ld32<32>(tS + 96, du);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: stage is free
+      if (tr && i < 64) trace[i * 16 + 10] = clock64();
       uint32_t pk[32];
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) {
@@ -301,10 +332,21 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         }
         pk[jj] = Pack<T>::pack(p0 * (__uint_as_float(du[2 * jj]) - dl_r), p1 * (__uint_as_float(du[2 * jj + 1]) - dl_r));
       }
-      tmem_st32<0>(tS, pk);
-      tmem_wait_st();
-      tc_fence_before();
+      if (tr && i < 64) trace[i * 16 + 11] = clock64();
+      if (i >= 2) {   // the update of step i-2 must have finished reading this dS tile
+        ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
+        if (!ok) break;
+      }
+      {   // row of the K-major, 128B-swizzled [128 x 64] tile: 16-byte chunk c lives at chunk c ^ (row & 7)
+        unsigned char* prow = smem_raw + ds_off + (i & 1) * kStepTile + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+      }
+      if (tr && i < 64) trace[i * 16 + 12] = clock64();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
+      if (tr && i < 64) trace[i * 16 + 13] = clock64();
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
     if (ok && n > 0) {
@@ -412,15 +454,18 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
 
   if (warp == 9) {
     // ---------------------------------------------------------------- TMA warp
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
       const CUtensorMap* mk = is_dep ? &maps.kd : &maps.k;
       const CUtensorMap* mv = is_dep ? &maps.vd : &maps.v;
-      prefetch_map(mk); prefetch_map(mv); prefetch_map(&maps.q); prefetch_map(&maps.dout);
-      mbar_expect_tx(bars + 8 * B_.res, 2 * kTileBytes);
-      tma_load_4d(sK, mk, bars + 8 * B_.res, 0, h, c0, b);
-      tma_load_4d(sK + kHalfBytes, mk, bars + 8 * B_.res, 64, h, c0, b);
-      tma_load_4d(sV, mv, bars + 8 * B_.res, 0, h, c0, b);
-      tma_load_4d(sV + kHalfBytes, mv, bars + 8 * B_.res, 64, h, c0, b);
+      if (elect_one()) {
+        prefetch_map(mk); prefetch_map(mv); prefetch_map(&maps.q); prefetch_map(&maps.dout);
+        mbar_expect_tx(bars + 8 * B_.res, 2 * kTileBytes);
+        tma_load_4d(sK, mk, bars + 8 * B_.res, 0, h, c0, b);
+        tma_load_4d(sK + kHalfBytes, mk, bars + 8 * B_.res, 64, h, c0, b);
+        tma_load_4d(sV, mv, bars + 8 * B_.res, 0, h, c0, b);
+        tma_load_4d(sV + kHalfBytes, mv, bars + 8 * B_.res, 64, h, c0, b);
+      }
+      __syncwarp();
       bool ok = true;
       int issued = 0;
       for (int i = 0; ok && i < n; ++i) {
@@ -429,13 +474,16 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         const int row = q_begin + i * kStep;
         const uint32_t dst = sRing + slot * 2 * kStepTile, bar = bars + 8 * (B_.full0 + slot);
         const uint32_t st = sStat + slot * 512;
-        mbar_expect_tx(bar, 2 * kStepTile + 512);
-        tma_load_4d(dst, &maps.q, bar, 0, h, row, b);
-        tma_load_4d(dst + kStepHalf, &maps.q, bar, 64, h, row, b);
-        tma_load_4d(dst + kStepTile, &maps.dout, bar, 0, h, row, b);
-        tma_load_4d(dst + kStepTile + kStepHalf, &maps.dout, bar, 64, h, row, b);
-        bulk_load(st, lse_t + stat_base + row, 256, bar);
-        bulk_load(st + 256, delta_t + stat_base + row, 256, bar);
+        if (elect_one()) {
+          mbar_expect_tx(bar, 2 * kStepTile + 512);
+          tma_load_4d(dst, &maps.q, bar, 0, h, row, b);
+          tma_load_4d(dst + kStepHalf, &maps.q, bar, 64, h, row, b);
+          tma_load_4d(dst + kStepTile, &maps.dout, bar, 0, h, row, b);
+          tma_load_4d(dst + kStepTile + kStepHalf, &maps.dout, bar, 64, h, row, b);
+          bulk_load(st, lse_t + stat_base + row, 256, bar);
+          bulk_load(st + 256, delta_t + stat_base + row, 256, bar);
+        }
+        __syncwarp();
         issued = i + 1;
       }
       if (!ok) {
@@ -446,7 +494,7 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     }
   } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA warp
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
       constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
       const uint64_t dK = desc_kmajor(sK), dV = desc_kmajor(sV);
@@ -454,13 +502,15 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         const uint32_t sQ = sRing + (i % R) * 2 * kStepTile;
         const uint64_t dq = desc_kmajor(sQ), ddo = desc_kmajor(sQ + kStepTile);
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-        tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+          for (int kk = 0; kk < 8; ++kk) {
+            mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+          }
+          tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+        }
+        __syncwarp();
       };
       bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);
       for (int i = 0; ok && i < 2 && i < n; ++i) {
@@ -475,14 +525,16 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
           const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
           const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);
           const uint32_t tPt = tmem + (j & 1) * 128, tDSt = tPt + 64;
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)   // dV += P^T dO
-            mma_ts(tmem_dV, tPt + kk * 8, desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)   // dK += dS^T Q
-            mma_ts(tmem_dK, tDSt + kk * 8, desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(bars + 8 * (B_.empty0 + slot));
-          if (j == n - 1) tc_commit(bars + 8 * B_.done);
+            for (int kk = 0; kk < 4; ++kk) {   // dV += P^T dO and dK += dS^T Q
+              mma_ts(tmem_dV, tPt + kk * 8, desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+              mma_ts(tmem_dK, tDSt + kk * 8, desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            tc_commit(bars + 8 * (B_.empty0 + slot));
+            if (j == n - 1) tc_commit(bars + 8 * B_.done);
+          }
+          __syncwarp();
         }
         if (j + 2 < n) {
           const int i = j + 2;
@@ -656,13 +708,13 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
   if ((e = cudaGetLastError()) != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
   *launches += 1;
   {
-    const size_t smem = kDqRing * 2 * (size_t)kStepTile + kCtlBytes;
+    const size_t smem = kDqRing * 2 * (size_t)kStepTile + 2 * (size_t)kStepTile + kCtlBytes;
     dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
     auto launch = [&](auto kern) -> cudaError_t {
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (er != cudaSuccess) return er;
       prof::Scope ps(prof::kDqTc, st);
-      kern<<<grid, kBwdThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp);
+      kern<<<grid, kBwdThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp, reinterpret_cast<unsigned long long*>(debug_state().dump));
       return cudaGetLastError();
     };
     e = bf ? launch(dq_kernel<__nv_bfloat16>) : launch(dq_kernel<__half>);

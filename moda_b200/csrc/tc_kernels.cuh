@@ -91,6 +91,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// One lane of a converged warp.  The TMA and MMA warps run their control flow with all 32
+// lanes (so descriptors and addresses stay in uniform registers) and only the asynchronous
+// instruction itself is issued by the elected lane - always the same one, which matters because
+// tcgen05.commit tracks the MMAs of the issuing thread.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
@@ -254,7 +264,7 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
 
   if (warp == 4) {
     // ------------------------------------------------------------- producer lane
-    if (lane == 0 && n_tiles > 0) {
+    if (n_tiles > 0) {   // all lanes run the control flow; one elected lane issues
       constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
       constexpr uint32_t idesc_pv = instr_desc(fmt, 128, true);
       bool pend_k = false, pend_v = false;
@@ -265,15 +275,21 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         const CUtensorMap* m = is_k ? (dep ? &maps.kd : &maps.k) : (dep ? &maps.vd : &maps.v);
         const uint32_t dst = is_k ? sK : sV;
         const uint32_t bar = bars + 8 * (is_k ? kBarK : kBarV);
-        mbar_expect_tx(bar, kTileBytes);
-        tma_load_4d(dst, m, bar, 0, h, row, b);
-        tma_load_4d(dst + kHalfBytes, m, bar, 64, h, row, b);
+        if (elect_one()) {
+          mbar_expect_tx(bar, kTileBytes);
+          tma_load_4d(dst, m, bar, 0, h, row, b);
+          tma_load_4d(dst + kHalfBytes, m, bar, 64, h, row, b);
+        }
+        __syncwarp();
         if (is_k) { pend_k = true; pend_k_par = i & 1; } else { pend_v = true; pend_v_par = i & 1; }
       };
-      prefetch_map(&maps.q); prefetch_map(&maps.k); prefetch_map(&maps.v);
-      mbar_expect_tx(bars + 8 * kBarQ, kTileBytes);
-      tma_load_4d(sQ, &maps.q, bars + 8 * kBarQ, 0, h, r0, b);
-      tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * kBarQ, 64, h, r0, b);
+      if (elect_one()) {
+        prefetch_map(&maps.q); prefetch_map(&maps.k); prefetch_map(&maps.v);
+        mbar_expect_tx(bars + 8 * kBarQ, kTileBytes);
+        tma_load_4d(sQ, &maps.q, bars + 8 * kBarQ, 0, h, r0, b);
+        tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * kBarQ, 64, h, r0, b);
+      }
+      __syncwarp();
       load_kv(0, true);
       load_kv(0, false);
       bool ok = mbar_wait(bars + 8 * kBarQ, 0, abort_flag, kBarQ);
@@ -282,12 +298,15 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         if (!(ok = mbar_wait(bars + 8 * kBarK, par, abort_flag, kBarK))) break;
         pend_k = false;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-          mma_ss(tmem_S, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+            mma_ss(tmem_S, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
+          }
+          tc_commit(bars + 8 * kBarS);
         }
-        tc_commit(bars + 8 * kBarS);
+        __syncwarp();
         if (j > 0) {   // PV(j-1) done => V buffer free
           if (!(ok = mbar_wait(bars + 8 * kBarO, (j - 1) & 1, abort_flag, kBarO))) break;
           load_kv(j, false);
@@ -298,18 +317,21 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         if (!(ok = mbar_wait(bars + 8 * kBarV, par, abort_flag, kBarV))) break;
         pend_v = false;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t bdesc = smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024);
-          const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-          if (kPTmem) {
-            mma_ts(tmem_O, tmem_S + kk * 8, bdesc, idesc_pv, acc);
-          } else {
-            const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-            mma_ss(tmem_O, smem_desc_sw128(sP + off, 16, 1024), bdesc, idesc_pv, acc);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t bdesc = smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024);
+            const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
+            if (kPTmem) {
+              mma_ts(tmem_O, tmem_S + kk * 8, bdesc, idesc_pv, acc);
+            } else {
+              const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+              mma_ss(tmem_O, smem_desc_sw128(sP + off, 16, 1024), bdesc, idesc_pv, acc);
+            }
           }
+          tc_commit(bars + 8 * kBarO);
         }
-        tc_commit(bars + 8 * kBarO);
+        __syncwarp();
       }
       if (!ok) {   // give up: let loads in flight land before the CTA's shared memory is released
         if (pend_k) mbar_wait(bars + 8 * kBarK, pend_k_par, drain_flag, kBarK);
