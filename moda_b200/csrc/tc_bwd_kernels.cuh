@@ -37,6 +37,7 @@ constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delt
 constexpr uint32_t kStepTile = 64 * 128 * 2;   // one [64 x 128] 16-bit tile (two 8 KB boxes)
 constexpr uint32_t kStepHalf = kStepTile / 2;
 constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
+constexpr uint32_t kIdleLimit = 1u << 22;      // idle polls (20 ns sleeps) of an event loop before giving up
 constexpr int kBwdThreads = 320;               // 8 softmax warps + MMA warp + TMA warp
 
 struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
@@ -108,7 +109,7 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 template <typename T>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
-          const float* lse_t, int T_qp, unsigned long long* trace) {
+          const float* lse_t, int T_qp, unsigned long long* trace, int dbg_flags) {
   constexpr int R = kDqRing;
   constexpr BwdBars B_(R);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -188,11 +189,17 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         if (elect_one()) {
+          if (dbg_flags & 16) {   // timing experiment: half the bytes per step
+            mbar_expect_tx(bar, kStepTile);
+            tma_load_4d(dst, mk, bar, 0, h, row, b);
+            tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
+          } else {
           mbar_expect_tx(bar, 2 * kStepTile);
           tma_load_4d(dst, mk, bar, 0, h, row, b);
           tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
           tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
           tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
+          }
         }
         __syncwarp();
         issued = i + 1;
@@ -228,28 +235,36 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         tc_fence_after();
         issue_scores(i);
       }
+      // Event loop.  Two independent sequences share the tensor pipe: "stage jr&1 has been read"
+      // -> scores of step jr+2, and "dS(jp) is in shared memory" -> update of step jp.  Whichever
+      // is ready first is issued first, so a slow softmax step of one warpgroup does not hold
+      // back the other warpgroup's next scores.
       const bool tr = trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && lane == 0;
-      for (int j = 0; ok && j < n; ++j) {
-        if (tr && j < 64) trace[j * 16 + 0] = clock64();
-        if (j + 2 < n) {   // stage j&1 has been read into registers: its next scores may go
-          const int i = j + 2;
+      int jr = 0, jp = 0;
+      const int n_r = n > 2 ? n - 2 : 0;
+      uint32_t idle = 0;
+      while (ok && (jr < n_r || jp < n)) {
+        bool did = false;
+        if (jr < n_r) {
+          const int i = jr + 2;
           const uint32_t slot = i % R;
-          if (!(ok = mbar_wait(bars + 8 * (B_.r0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.r0 + (j & 1)))) break;
-          if (tr && j < 64) trace[j * 16 + 1] = clock64();
-          if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
-          tc_fence_after();
-          if (tr && j < 64) trace[j * 16 + 2] = clock64();
-          issue_scores(i);
-          if (tr && j < 64) trace[j * 16 + 3] = clock64();
+          if (mbar_test(bars + 8 * (B_.r0 + (jr & 1)), (jr >> 1) & 1) &&
+              mbar_test(bars + 8 * (B_.full0 + slot), (i / R) & 1)) {
+            tc_fence_after();
+            if (tr && jr < 64) trace[jr * 16 + 2] = clock64();
+            issue_scores(i);
+            if (tr && jr < 64) trace[jr * 16 + 3] = clock64();
+            ++jr; did = true;
+          }
         }
-        if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
-        tc_fence_after();
-        if (tr && j < 64) trace[j * 16 + 4] = clock64();
-        {   // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major
+        if (jp < n && mbar_test(bars + 8 * (B_.p0 + (jp & 1)), (jp >> 1) & 1)) {
+          tc_fence_after();
+          if (tr && jp < 64) trace[jp * 16 + 4] = clock64();
+          const int j = jp;
           const uint32_t slot = j % R;
           const uint64_t da = desc_kmajor(sDS + (j & 1) * kStepTile);
           const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
-          if (elect_one()) {
+          if (elect_one()) {   // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
               mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
@@ -258,8 +273,16 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
             if (j == n - 1) tc_commit(bars + 8 * B_.done);
           }
           __syncwarp();
+          if (tr && jp < 64) trace[jp * 16 + 5] = clock64();
+          ++jp; did = true;
         }
-        if (tr && j < 64) trace[j * 16 + 5] = clock64();
+        if (did) {
+          idle = 0;
+        } else {
+          __nanosleep(20);
+          if ((++idle & 1023u) == 0 && *abort_flag != 0) ok = false;
+          if (idle > kIdleLimit) { *abort_flag = 1; atomicCAS(&g_tc_status, 0, (3 << 8) | (jp & 0xff)); ok = false; }
+        }
       }
     }
   } else {
@@ -320,18 +343,23 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       tc_fence_before();
       mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: stage is free
       if (tr && i < 64) trace[i * 16 + 10] = clock64();
+      // straight-line passes over the 64 columns (no branches inside, so the scheduler can
+      // overlap the exp2 latency of one column with the arithmetic of the others)
+      float pr[64];
+#pragma unroll
+      for (int jj = 0; jj < 64; ++jj) pr[jj] = fast_exp2(fmaf(__uint_as_float(su[jj]), c, -lse_r));
+      if (masked) {
+#pragma unroll
+        for (int jj = 0; jj < 64; ++jj) {
+          const int col = c0 + jj;
+          pr[jj] = (col >= lo && col < hi) ? pr[jj] : 0.f;
+        }
+      }
       uint32_t pk[32];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
-        float p0 = fast_exp2(fmaf(__uint_as_float(su[2 * jj]), c, -lse_r));
-        float p1 = fast_exp2(fmaf(__uint_as_float(su[2 * jj + 1]), c, -lse_r));
-        if (masked) {
-          const int col = c0 + 2 * jj;
-          if (col < lo || col >= hi) p0 = 0.f;
-          if (col + 1 < lo || col + 1 >= hi) p1 = 0.f;
-        }
-        pk[jj] = Pack<T>::pack(p0 * (__uint_as_float(du[2 * jj]) - dl_r), p1 * (__uint_as_float(du[2 * jj + 1]) - dl_r));
-      }
+      for (int jj = 0; jj < 32; ++jj)
+        pk[jj] = Pack<T>::pack(pr[2 * jj] * (__uint_as_float(du[2 * jj]) - dl_r),
+                               pr[2 * jj + 1] * (__uint_as_float(du[2 * jj + 1]) - dl_r));
       if (tr && i < 64) trace[i * 16 + 11] = clock64();
       if (i >= 2) {   // the update of step i-2 must have finished reading this dS tile
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
@@ -582,25 +610,31 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       tmem_ld32<0>(tS + 64, du);
       tmem_ld32<32>(tS + 96, du);
       tmem_wait_ld();
-      uint32_t pp[32], pd[32];
+      float pr[64], dd[64];
 #pragma unroll
       for (int j4 = 0; j4 < 16; ++j4) {
         const float4 l4 = st4[j4], d4 = st4[16 + j4];
-        const float ls[4] = {l4.x, l4.y, l4.z, l4.w}, ds[4] = {d4.x, d4.y, d4.z, d4.w};
-        float pv[4], dv[4];
+        pr[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 0]), c, -l4.x));
+        pr[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 1]), c, -l4.y));
+        pr[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 2]), c, -l4.z));
+        pr[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 3]), c, -l4.w));
+        dd[4 * j4 + 0] = __uint_as_float(du[4 * j4 + 0]) - d4.x;
+        dd[4 * j4 + 1] = __uint_as_float(du[4 * j4 + 1]) - d4.y;
+        dd[4 * j4 + 2] = __uint_as_float(du[4 * j4 + 2]) - d4.z;
+        dd[4 * j4 + 3] = __uint_as_float(du[4 * j4 + 3]) - d4.w;
+      }
+      if (masked) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int jj = j4 * 4 + e;
-          float pe = fast_exp2(fmaf(__uint_as_float(su[jj]), c, -ls[e]));
-          if (masked) {
-            const int rr = q0 + jj;
-            if (rr < rlo || rr >= rhi) pe = 0.f;
-          }
-          pv[e] = pe;
-          dv[e] = pe * (__uint_as_float(du[jj]) - ds[e]);
+        for (int jj = 0; jj < 64; ++jj) {
+          const int rr = q0 + jj;
+          pr[jj] = (rr >= rlo && rr < rhi) ? pr[jj] : 0.f;
         }
-        pp[j4 * 2] = Pack<T>::pack(pv[0], pv[1]); pp[j4 * 2 + 1] = Pack<T>::pack(pv[2], pv[3]);
-        pd[j4 * 2] = Pack<T>::pack(dv[0], dv[1]); pd[j4 * 2 + 1] = Pack<T>::pack(dv[2], dv[3]);
+      }
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
+        pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
       }
       tmem_st32<0>(tS, pp);
       tmem_st32<0>(tS + 64, pd);
@@ -714,7 +748,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (er != cudaSuccess) return er;
       prof::Scope ps(prof::kDqTc, st);
-      kern<<<grid, kBwdThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp, reinterpret_cast<unsigned long long*>(debug_state().dump));
+      kern<<<grid, kBwdThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp, reinterpret_cast<unsigned long long*>(debug_state().dump), debug_state().variant);
       return cudaGetLastError();
     };
     e = bf ? launch(dq_kernel<__nv_bfloat16>) : launch(dq_kernel<__half>);

@@ -5,9 +5,10 @@
 // (the same walk and the same visibility intervals as the mma.sync kernels).  Two CTAs
 // are resident per SM so that one CTA's softmax overlaps the other's MMAs.
 //
-//   warp 4, one lane : producer.  TMA loads (128B-swizzled [128 x 64] boxes) of Q once
-//                      and of each K and V tile into single-stage buffers; issues
-//                      S = Q K^T and O += P V as tcgen05.mma (M=128, N=128, K=16 steps)
+//   warp 5           : TMA loads (128B-swizzled [128 x 64] boxes) of Q once and of each K and
+//                      V tile into single-stage buffers, refilled as soon as the MMA that read
+//                      them has completed.
+//   warp 4           : issues S = Q K^T and O += P V as tcgen05.mma (M=128, N=128, K=16 steps)
 //                      with fp32 accumulators in TMEM.
 //   warps 0-3        : softmax.  Thread = query row = TMEM lane.  tcgen05.ld of the S
 //                      row, visibility mask on masked tiles only, online softmax in
@@ -191,7 +192,7 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, uint32_t n, bool
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-enum BarId : int { kBarQ = 0, kBarK, kBarV, kBarS, kBarP, kBarO, kBarCount };
+enum BarId : int { kBarQ = 0, kBarK, kBarV, kBarS, kBarP, kBarO, kBarKFree, kBarVFree, kBarCount };
 
 // Tile walk of a 128-row query tile (same construction as simt::make_walk).
 struct Walk { int n_seq, n_dep, dep_c0, seq_full_hi; };
@@ -211,11 +212,11 @@ __device__ __forceinline__ Walk make_walk(const Params& p, int r0) {
 }
 
 // ======================================================================= forward
-// grid (ceil(T_q/128), H, B); 160 threads.  kPTmem: P is handed to the PV MMA through
+// grid (ceil(T_q/128), H, B); 192 threads (4 softmax warps, MMA warp, TMA warp).  kPTmem: P is handed to the PV MMA through
 // TMEM (production).  kPTmem = false stages P through a swizzled shared-memory tile
 // instead (one CTA per SM; kept as a cross-check of the TMEM operand layout).
 template <typename T, bool kPTmem>
-__global__ void __launch_bounds__(160, kPTmem ? 2 : 1)
+__global__ void __launch_bounds__(192, kPTmem ? 2 : 1)
 fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps maps, float* dbg) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -246,6 +247,8 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
     mbar_init(bars + 8 * kBarS, 1);
     mbar_init(bars + 8 * kBarP, 128);
     mbar_init(bars + 8 * kBarO, 1);
+    mbar_init(bars + 8 * kBarKFree, 1);
+    mbar_init(bars + 8 * kBarVFree, 1);
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -262,11 +265,11 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
   const uint32_t tmem_S = tmem, tmem_O = tmem + 128;
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------- producer lane
-    if (n_tiles > 0) {   // all lanes run the control flow; one elected lane issues
-      constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
-      constexpr uint32_t idesc_pv = instr_desc(fmt, 128, true);
+  if (warp == 5) {
+    // ------------------------------------------------------------- TMA warp
+    // All lanes run the control flow; one elected lane issues.  K(j+1) is loaded as soon as
+    // QK(j) has finished reading the K buffer, V(j+1) as soon as PV(j) has finished reading V.
+    if (n_tiles > 0) {
       bool pend_k = false, pend_v = false;
       uint32_t pend_k_par = 0, pend_v_par = 0;
       auto load_kv = [&](int i, bool is_k) {
@@ -292,11 +295,28 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
       __syncwarp();
       load_kv(0, true);
       load_kv(0, false);
+      bool ok = true;
+      for (int j = 0; ok && j + 1 < n_tiles; ++j) {
+        if (!(ok = mbar_wait(bars + 8 * kBarKFree, j & 1, abort_flag, kBarKFree))) break;
+        load_kv(j + 1, true);
+        if (!(ok = mbar_wait(bars + 8 * kBarVFree, j & 1, abort_flag, kBarVFree))) break;
+        load_kv(j + 1, false);
+      }
+      if (!ok) {   // give up: let loads in flight land before the CTA's shared memory is released
+        mbar_wait(bars + 8 * kBarQ, 0, drain_flag, kBarQ);
+        if (pend_k) mbar_wait(bars + 8 * kBarK, pend_k_par, drain_flag, kBarK);
+        if (pend_v) mbar_wait(bars + 8 * kBarV, pend_v_par, drain_flag, kBarV);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------- MMA warp
+    if (n_tiles > 0) {
+      constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
+      constexpr uint32_t idesc_pv = instr_desc(fmt, 128, true);
       bool ok = mbar_wait(bars + 8 * kBarQ, 0, abort_flag, kBarQ);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const uint32_t par = j & 1;
         if (!(ok = mbar_wait(bars + 8 * kBarK, par, abort_flag, kBarK))) break;
-        pend_k = false;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -305,17 +325,11 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
             mma_ss(tmem_S, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
           }
           tc_commit(bars + 8 * kBarS);
+          tc_commit(bars + 8 * kBarKFree);
         }
         __syncwarp();
-        if (j > 0) {   // PV(j-1) done => V buffer free
-          if (!(ok = mbar_wait(bars + 8 * kBarO, (j - 1) & 1, abort_flag, kBarO))) break;
-          load_kv(j, false);
-        }
-        if (!(ok = mbar_wait(bars + 8 * kBarS, par, abort_flag, kBarS))) break;
-        if (j + 1 < n_tiles) load_kv(j + 1, true);   // QK(j) done => K buffer free
         if (!(ok = mbar_wait(bars + 8 * kBarP, par, abort_flag, kBarP))) break;
         if (!(ok = mbar_wait(bars + 8 * kBarV, par, abort_flag, kBarV))) break;
-        pend_v = false;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
@@ -330,12 +344,9 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
             }
           }
           tc_commit(bars + 8 * kBarO);
+          tc_commit(bars + 8 * kBarVFree);
         }
         __syncwarp();
-      }
-      if (!ok) {   // give up: let loads in flight land before the CTA's shared memory is released
-        if (pend_k) mbar_wait(bars + 8 * kBarK, pend_k_par, drain_flag, kBarK);
-        if (pend_v) mbar_wait(bars + 8 * kBarV, pend_v_par, drain_flag, kBarV);
       }
     }
   } else {
@@ -543,7 +554,7 @@ inline int fwd(const Params& p, const moda_problem* pr, cudaStream_t st, int* la
     cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (er != cudaSuccess) return er;
     prof::Scope ps(prof::kFwdTc, st);
-    kern<<<grid, 160, smem, st>>>(p, maps, debug_state().dump);
+    kern<<<grid, 192, smem, st>>>(p, maps, debug_state().dump);
     return cudaGetLastError();
   };
   if (pr->dtype == MODA_BF16) e = p_tmem ? launch(fwd_kernel<__nv_bfloat16, true>) : launch(fwd_kernel<__nv_bfloat16, false>);
