@@ -37,8 +37,8 @@ constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delt
 constexpr uint32_t kStepTile = 64 * 128 * 2;   // one [64 x 128] 16-bit tile (two 8 KB boxes)
 constexpr uint32_t kStepHalf = kStepTile / 2;
 constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
-constexpr uint32_t kIdleLimit = 1u << 22;      // idle polls (20 ns sleeps) of an event loop before giving up
-constexpr int kBwdThreads = 320;               // 8 softmax warps + MMA warp + TMA warp
+constexpr int kBwdThreads = 320;               // dkv: 8 softmax warps + MMA warp + TMA warp
+constexpr int kDqThreads = 352;                // dq: 8 softmax warps + score-MMA, TMA and update-MMA warps
 
 struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
 struct DkvMaps { CUtensorMap k, v, kd, vd, q, dout; };     // k, v, kd, vd: 128-row boxes; q, dout 64-row
@@ -99,7 +99,7 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_s
 __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { return d + (uint64_t)(byte_off >> 4); }
 
 // ============================================================================ dq
-// grid (ceil(T_q/128), H, B), 320 threads.  TMEM (512 columns):
+// grid (ceil(T_q/128), H, B), 352 threads.  TMEM (512 columns):
 //   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32);
 //   [256, 384) dQ (fp32);  [384, 448) Q (16-bit A operand);  [448, 512) dO (16-bit A operand).
 // Shared memory: ring of kDqRing x {K step tile, V step tile} (32 KB per slot), then two
@@ -107,9 +107,9 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 // as soon as it has the scores in registers, so the next-but-one score MMAs overlap its math;
 // dS reaches the update MMA through shared memory.
 template <typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDqThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
-          const float* lse_t, int T_qp, unsigned long long* trace, int dbg_flags) {
+          const float* lse_t, int T_qp) {
   constexpr int R = kDqRing;
   constexpr BwdBars B_(R);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -189,17 +189,11 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         if (elect_one()) {
-          if (dbg_flags & 16) {   // timing experiment: half the bytes per step
-            mbar_expect_tx(bar, kStepTile);
-            tma_load_4d(dst, mk, bar, 0, h, row, b);
-            tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
-          } else {
           mbar_expect_tx(bar, 2 * kStepTile);
           tma_load_4d(dst, mk, bar, 0, h, row, b);
           tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
           tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
           tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
-          }
         }
         __syncwarp();
         issued = i + 1;
@@ -210,12 +204,19 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       }
     }
   } else if (warp == 8) {
-    // ---------------------------------------------------------------- MMA warp
+    // ---------------------------------------------------------------- score-MMA warp
+    // S(i) = Q K(i)^T and dP(i) = dO V(i)^T into TMEM stage i&1, as soon as the warpgroup that
+    // owned the stage has the previous scores in registers and the step tiles have landed.
     if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
-      auto issue_scores = [&](int i) {   // S(i) = Q K(i)^T, dP(i) = dO V(i)^T into TMEM stage i&1
-        const uint32_t sK = sRing + (i % R) * 2 * kStepTile;
+      bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // Q, dO are in TMEM
+      tc_fence_after();
+      for (int i = 0; ok && i < n; ++i) {
+        const uint32_t slot = i % R;
+        if (i >= 2 && !(ok = mbar_wait(bars + 8 * (B_.r0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.r0 + (i & 1)))) break;
+        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
+        tc_fence_after();
+        const uint32_t sK = sRing + slot * 2 * kStepTile;
         const uint64_t dk = desc_kmajor(sK), dv = desc_kmajor(sK + kStepTile);
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
         if (elect_one()) {
@@ -227,62 +228,30 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
           tc_commit(bars + 8 * (B_.s0 + (i & 1)));
         }
         __syncwarp();
-      };
-      bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // Q, dO are in TMEM
-      tc_fence_after();
-      for (int i = 0; ok && i < 2 && i < n; ++i) {
-        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + i), 0, abort_flag, B_.full0 + i))) break;
-        tc_fence_after();
-        issue_scores(i);
       }
-      // Event loop.  Two independent sequences share the tensor pipe: "stage jr&1 has been read"
-      // -> scores of step jr+2, and "dS(jp) is in shared memory" -> update of step jp.  Whichever
-      // is ready first is issued first, so a slow softmax step of one warpgroup does not hold
-      // back the other warpgroup's next scores.
-      const bool tr = trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && lane == 0;
-      int jr = 0, jp = 0;
-      const int n_r = n > 2 ? n - 2 : 0;
-      uint32_t idle = 0;
-      while (ok && (jr < n_r || jp < n)) {
-        bool did = false;
-        if (jr < n_r) {
-          const int i = jr + 2;
-          const uint32_t slot = i % R;
-          if (mbar_test(bars + 8 * (B_.r0 + (jr & 1)), (jr >> 1) & 1) &&
-              mbar_test(bars + 8 * (B_.full0 + slot), (i / R) & 1)) {
-            tc_fence_after();
-            if (tr && jr < 64) trace[jr * 16 + 2] = clock64();
-            issue_scores(i);
-            if (tr && jr < 64) trace[jr * 16 + 3] = clock64();
-            ++jr; did = true;
-          }
-        }
-        if (jp < n && mbar_test(bars + 8 * (B_.p0 + (jp & 1)), (jp >> 1) & 1)) {
-          tc_fence_after();
-          if (tr && jp < 64) trace[jp * 16 + 4] = clock64();
-          const int j = jp;
-          const uint32_t slot = j % R;
-          const uint64_t da = desc_kmajor(sDS + (j & 1) * kStepTile);
-          const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
-          if (elect_one()) {   // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major
+    }
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- update-MMA warp
+    // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major.  A warp of
+    // its own, so that an update never waits behind the issue of the next scores.
+    if (n > 0) {
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      bool ok = true;
+      for (int j = 0; ok && j < n; ++j) {
+        if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
+        tc_fence_after();
+        const uint32_t slot = j % R;
+        const uint64_t da = desc_kmajor(sDS + (j & 1) * kStepTile);
+        const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
+        if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
-              mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-            tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
-            tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // dS tile j&1 may be rewritten
-            if (j == n - 1) tc_commit(bars + 8 * B_.done);
-          }
-          __syncwarp();
-          if (tr && jp < 64) trace[jp * 16 + 5] = clock64();
-          ++jp; did = true;
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
+          tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // dS tile j&1 may be rewritten
+          if (j == n - 1) tc_commit(bars + 8 * B_.done);
         }
-        if (did) {
-          idle = 0;
-        } else {
-          __nanosleep(20);
-          if ((++idle & 1023u) == 0 && *abort_flag != 0) ok = false;
-          if (idle > kIdleLimit) { *abort_flag = 1; atomicCAS(&g_tc_status, 0, (3 << 8) | (jp & 0xff)); ok = false; }
-        }
+        __syncwarp();
       }
     }
   } else {
@@ -322,13 +291,10 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     }
     const float c = p.scale_log2;
     bool ok = true;
-    const bool tr = trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && quarter == 0 && lane == 0;
     for (int i = wg; i < n; i += 2) {
-      if (tr && i < 64) trace[i * 16 + 8] = clock64();
       ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.s0 + (i & 1)), (i >> 1) & 1, abort_flag, B_.s0 + (i & 1)));
       if (!ok) break;
       tc_fence_after();
-      if (tr && i < 64) trace[i * 16 + 9] = clock64();
       const bool is_dep = i >= n_seq;
       const int c0 = is_dep ? dep_c0 + (i - n_seq) * kStep : i * kStep;
       const bool masked = is_dep || (c0 + kStep > seq_full_hi);
@@ -342,7 +308,6 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: stage is free
-      if (tr && i < 64) trace[i * 16 + 10] = clock64();
       // straight-line passes over the 64 columns (no branches inside, so the scheduler can
       // overlap the exp2 latency of one column with the arithmetic of the others)
       float pr[64];
@@ -360,7 +325,6 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       for (int jj = 0; jj < 32; ++jj)
         pk[jj] = Pack<T>::pack(pr[2 * jj] * (__uint_as_float(du[2 * jj]) - dl_r),
                                pr[2 * jj + 1] * (__uint_as_float(du[2 * jj + 1]) - dl_r));
-      if (tr && i < 64) trace[i * 16 + 11] = clock64();
       if (i >= 2) {   // the update of step i-2 must have finished reading this dS tile
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
         if (!ok) break;
@@ -371,10 +335,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         for (int ch = 0; ch < 8; ++ch)
           *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
       }
-      if (tr && i < 64) trace[i * 16 + 12] = clock64();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
-      if (tr && i < 64) trace[i * 16 + 13] = clock64();
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
     if (ok && n > 0) {
@@ -748,7 +710,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (er != cudaSuccess) return er;
       prof::Scope ps(prof::kDqTc, st);
-      kern<<<grid, kBwdThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp, reinterpret_cast<unsigned long long*>(debug_state().dump), debug_state().variant);
+      kern<<<grid, kDqThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp);
       return cudaGetLastError();
     };
     e = bf ? launch(dq_kernel<__nv_bfloat16>) : launch(dq_kernel<__half>);
