@@ -13,9 +13,9 @@
 //                from shared memory; softmax warps form dS = P (dP - delta) in TMEM;
 //                dQ += dS K (A from TMEM, K tile read MN-major).  dq = scale * dQ.
 //   dkv_kernel : CTA = 128 keys of the sequence K/V or of the depth K/V; walks the query
-//                rows that can see them in steps of 64 rows.  S^T = K Q^T, dP^T = V dO^T
-//                (both operands in shared memory, N = 64) -> P^T and dS^T in TMEM ->
-//                dV += P^T dO, dK += dS^T Q (A from TMEM, Q/dO tiles read MN-major).
+//                rows that can see them in steps of 64 rows.  K and V rows sit in TMEM as
+//                A operands; S^T = K Q^T, dP^T = V dO^T (N = 64) -> P^T and dS^T written to
+//                shared memory -> dV += P^T dO, dK += dS^T Q (Q/dO tiles read MN-major).
 //                The G heads of a KV head are rows of the same folded query tile, so the
 //                GQA sum happens inside the MMA.  dk = scale * dK.
 //
@@ -37,8 +37,7 @@ constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delt
 constexpr uint32_t kStepTile = 64 * 128 * 2;   // one [64 x 128] 16-bit tile (two 8 KB boxes)
 constexpr uint32_t kStepHalf = kStepTile / 2;
 constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
-constexpr int kBwdThreads = 320;               // dkv: 8 softmax warps + MMA warp + TMA warp
-constexpr int kDqThreads = 352;                // dq: 8 softmax warps + score-MMA, TMA and update-MMA warps
+constexpr int kDqThreads = 352;                // 8 softmax warps + score-MMA, TMA and update-MMA warps
 
 struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
 struct DkvMaps { CUtensorMap k, v, kd, vd, q, dout; };     // k, v, kd, vd: 128-row boxes; q, dout 64-row
@@ -370,13 +369,18 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 }
 
 // =========================================================================== dk / dv
-// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 320 threads; key tiles of 128.
-// TMEM (512 columns): stage s: [s*128, +64) S^T / P^T (16-bit, 32 columns),
-//   [s*128+64, +64) dP^T / dS^T (16-bit, 32 columns); [256,384) dV; [384,512) dK.
-// Shared memory: K, V tile (32 KB each, resident), ring of kDkvRing x {Q step tile, dO step
-// tile} followed by the ring of {64 lse, 64 delta}.
+// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 352 threads; key tiles of 128.
+// TMEM (512 columns): [0, 64) S^T and [64, 128) dP^T (one fp32 score stage);
+//   [128, 256) dV; [256, 384) dK; [384, 448) K and [448, 512) V rows as 16-bit A operands.
+// Shared memory: ring of kDkvRing x {Q step tile, dO step tile}; two {P^T, dS^T} tile pairs
+// ([128 keys x 64 rows], K-major, 128-byte swizzle), one per softmax warpgroup; the ring of
+// {64 lse, 64 delta}.  A warpgroup releases the score stage as soon as the scores are in its
+// registers, so the next step's score MMAs overlap its math; P^T and dS^T reach the update
+// MMAs through shared memory.
+constexpr uint32_t kDkvPairBytes = 2 * kStepTile;   // P^T tile + dS^T tile
+
 template <typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDqThreads, 1)
 dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
            const float* lse_t, int T_qp, int n_seq_key_tiles) {
   constexpr int R = kDkvRing;
@@ -387,10 +391,12 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
     return;
   }
-  const uint32_t sK = base, sV = base + kTileBytes, sRing = base + 2 * kTileBytes;
-  const uint32_t stat_off = 2 * kTileBytes + R * 2 * kStepTile;
+  const uint32_t sRing = base;
+  const uint32_t pt_off = R * 2 * kStepTile;
+  const uint32_t sPT = base + pt_off;
+  const uint32_t stat_off = pt_off + 2 * kDkvPairBytes;
   const uint32_t sStat = base + stat_off;
-  const uint32_t ctl_off = 2 * kTileBytes + R * kDkvSlot;
+  const uint32_t ctl_off = stat_off + R * 512;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
@@ -421,10 +427,13 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
   const int n = (q_end - q_begin + kStep - 1) / kStep;
 
   if (tid == 0) {
-    mbar_init(bars + 8 * B_.res, 1);
+    mbar_init(bars + 8 * B_.res, 256);
     mbar_init(bars + 8 * B_.done, 1);
     for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128);
+      mbar_init(bars + 8 * (B_.r0 + i), 128); mbar_init(bars + 8 * (B_.t0 + i), 1);
+    }
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -438,24 +447,15 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_dV = tmem + 256, tmem_dK = tmem + 384;
+  const uint32_t tmem_S = tmem, tmem_P = tmem + 64, tmem_dV = tmem + 128, tmem_dK = tmem + 256;
+  const uint32_t tmem_K = tmem + 384, tmem_V = tmem + 448;
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   const int64_t stat_base = ((int64_t)b * p.H + h) * T_qp;
 
   if (warp == 9) {
     // ---------------------------------------------------------------- TMA warp
     if (n > 0) {
-      const CUtensorMap* mk = is_dep ? &maps.kd : &maps.k;
-      const CUtensorMap* mv = is_dep ? &maps.vd : &maps.v;
-      if (elect_one()) {
-        prefetch_map(mk); prefetch_map(mv); prefetch_map(&maps.q); prefetch_map(&maps.dout);
-        mbar_expect_tx(bars + 8 * B_.res, 2 * kTileBytes);
-        tma_load_4d(sK, mk, bars + 8 * B_.res, 0, h, c0, b);
-        tma_load_4d(sK + kHalfBytes, mk, bars + 8 * B_.res, 64, h, c0, b);
-        tma_load_4d(sV, mv, bars + 8 * B_.res, 0, h, c0, b);
-        tma_load_4d(sV + kHalfBytes, mv, bars + 8 * B_.res, 64, h, c0, b);
-      }
-      __syncwarp();
+      if (elect_one()) { prefetch_map(&maps.q); prefetch_map(&maps.dout); }
       bool ok = true;
       int issued = 0;
       for (int i = 0; ok && i < n; ++i) {
@@ -476,63 +476,61 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         __syncwarp();
         issued = i + 1;
       }
-      if (!ok) {
-        mbar_wait(bars + 8 * B_.res, 0, drain_flag, B_.res);
+      if (!ok) {   // let loads in flight land before the CTA's shared memory is released
         for (int i = max(0, issued - R); i < issued; ++i)
           mbar_wait(bars + 8 * (B_.full0 + i % R), (i / R) & 1, drain_flag, B_.full0 + i % R);
       }
     }
   } else if (warp == 8) {
-    // ---------------------------------------------------------------- MMA warp
+    // ---------------------------------------------------------------- score-MMA warp
+    // S^T(i) = K Q(i)^T and dP^T(i) = V dO(i)^T (A from TMEM) into the score stage, as soon as
+    // the previous step's scores have been read into registers and the step tiles have landed.
     if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
-      const uint64_t dK = desc_kmajor(sK), dV = desc_kmajor(sV);
-      auto issue_scores = [&](int i) {   // S^T(i) = K Q(i)^T, dP^T(i) = V dO(i)^T
-        const uint32_t sQ = sRing + (i % R) * 2 * kStepTile;
+      bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // K, V are in TMEM
+      tc_fence_after();
+      for (int i = 0; ok && i < n; ++i) {
+        const uint32_t slot = i % R;
+        if (i >= 1 && !(ok = mbar_wait(bars + 8 * (B_.r0 + ((i - 1) & 1)), ((i - 1) >> 1) & 1, abort_flag, B_.r0 + ((i - 1) & 1)))) break;
+        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
+        tc_fence_after();
+        const uint32_t sQ = sRing + slot * 2 * kStepTile;
         const uint64_t dq = desc_kmajor(sQ), ddo = desc_kmajor(sQ + kStepTile);
-        const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-            mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ts(tmem_S, tmem_K + kk * 8, desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ts(tmem_P, tmem_V + kk * 8, desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           }
           tc_commit(bars + 8 * (B_.s0 + (i & 1)));
         }
         __syncwarp();
-      };
-      bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);
-      for (int i = 0; ok && i < 2 && i < n; ++i) {
-        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + i), 0, abort_flag, B_.full0 + i))) break;
-        tc_fence_after();
-        issue_scores(i);
       }
+    }
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- update-MMA warp
+    // dV += P^T(j) dO(j) and dK += dS^T(j) Q(j): A = tiles written by warpgroup j&1, B = the
+    // step tiles read MN-major.
+    if (n > 0) {
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
         if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
         tc_fence_after();
-        {
-          const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
-          const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);
-          const uint32_t tPt = tmem + (j & 1) * 128, tDSt = tPt + 64;
-          if (elect_one()) {
+        const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
+        const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);
+        const uint64_t dpt = desc_kmajor(sPT + (j & 1) * kDkvPairBytes), dst = desc_kmajor(sPT + (j & 1) * kDkvPairBytes + kStepTile);
+        if (elect_one()) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {   // dV += P^T dO and dK += dS^T Q
-              mma_ts(tmem_dV, tPt + kk * 8, desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-              mma_ts(tmem_dK, tDSt + kk * 8, desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-            }
-            tc_commit(bars + 8 * (B_.empty0 + slot));
-            if (j == n - 1) tc_commit(bars + 8 * B_.done);
+          for (int kk = 0; kk < 4; ++kk) {
+            mma_ss(tmem_dV, desc_add(dpt, kk * 32), desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            mma_ss(tmem_dK, desc_add(dst, kk * 32), desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
           }
-          __syncwarp();
+          tc_commit(bars + 8 * (B_.empty0 + slot));      // ring slot j may be refilled
+          tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // tile pair j&1 may be rewritten
+          if (j == n - 1) tc_commit(bars + 8 * B_.done);
         }
-        if (j + 2 < n) {
-          const int i = j + 2;
-          const uint32_t slot = i % R;
-          if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
-          tc_fence_after();
-          issue_scores(i);
-        }
+        __syncwarp();
       }
     }
   } else {
@@ -541,6 +539,27 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     const int row = quarter * 32 + lane;             // key row of the tile == TMEM lane
     const int key = c0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    {   // stage this thread's K row (warpgroup 0) or V row (warpgroup 1) into TMEM as an A operand
+      uint32_t regs[64];
+      if (key < n_keys) {
+        const View& src = (wg == 0) ? (is_dep ? p.kd : p.k) : (is_dep ? p.vd : p.v);
+        const uint4* g4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(src.ptr) + src.off(b, key, h));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint4 v4 = g4[i];
+          regs[4 * i] = v4.x; regs[4 * i + 1] = v4.y; regs[4 * i + 2] = v4.z; regs[4 * i + 3] = v4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) regs[i] = 0u;
+      }
+      const uint32_t dst = ((wg == 0) ? tmem_K : tmem_V) + lane_addr;
+      tmem_st32<0>(dst, regs);
+      tmem_st32<32>(dst + 32, regs);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * B_.res);
+    }
     // query rows [rlo, rhi) that see this key (the visibility rule of common.cuh, inverted)
     int rlo, rhi;
     if (key >= n_keys) { rlo = 0; rhi = 0; }
@@ -564,14 +583,15 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       tc_fence_after();
       const int q0 = q_begin + i * kStep;
       const bool masked = is_dep || tail_keys || q0 < tile_rlo_max || q0 + kStep > p.T_q;
-      const uint32_t tS = tmem + (i & 1) * 128 + lane_addr;
       const float4* st4 = reinterpret_cast<const float4*>(smem_raw + stat_off + slot * 512);
       uint32_t su[64], du[64];
-      tmem_ld32<0>(tS, su);
-      tmem_ld32<32>(tS + 32, su);
-      tmem_ld32<0>(tS + 64, du);
-      tmem_ld32<32>(tS + 96, du);
+      tmem_ld32<0>(tmem_S + lane_addr, su);
+      tmem_ld32<32>(tmem_S + lane_addr + 32, su);
+      tmem_ld32<0>(tmem_P + lane_addr, du);
+      tmem_ld32<32>(tmem_P + lane_addr + 32, du);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: the stage is free
       float pr[64], dd[64];
 #pragma unroll
       for (int j4 = 0; j4 < 16; ++j4) {
@@ -598,10 +618,20 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
         pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
       }
-      tmem_st32<0>(tS, pp);
-      tmem_st32<0>(tS + 64, pd);
-      tmem_wait_st();
-      tc_fence_before();
+      if (i >= 2) {   // the update of step i-2 must have finished reading this warpgroup's tile pair
+        ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
+        if (!ok) break;
+      }
+      {   // rows of the K-major, 128B-swizzled [128 x 64] tiles: 16-byte chunk c lives at chunk c ^ (row & 7)
+        unsigned char* prow = smem_raw + pt_off + (i & 1) * kDkvPairBytes + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint32_t o = (uint32_t)((ch ^ (row & 7)) << 4);
+          *reinterpret_cast<uint4*>(prow + o) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(prow + kStepTile + o) = make_uint4(pd[4 * ch], pd[4 * ch + 1], pd[4 * ch + 2], pd[4 * ch + 3]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
@@ -718,7 +748,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
     *launches += 1;
   }
   {
-    const size_t smem = 2 * (size_t)kTileBytes + kDkvRing * (size_t)kDkvSlot + kCtlBytes;
+    const size_t smem = kDkvRing * (size_t)kDkvSlot + 2 * (size_t)kDkvPairBytes + kCtlBytes;
     const int n_seq = (p.T_kv + kBN - 1) / kBN;
     const int n_dep = (int)((TL + kBN - 1) / kBN);
     dim3 grid(n_seq + n_dep, p.H, p.B);
@@ -726,7 +756,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (er != cudaSuccess) return er;
       prof::Scope ps(prof::kDkvTc, st);
-      kern<<<grid, kBwdThreads, smem, st>>>(p, dkm, delta_t, lse_t, T_qp, n_seq);
+      kern<<<grid, kDqThreads, smem, st>>>(p, dkm, delta_t, lse_t, T_qp, n_seq);
       return cudaGetLastError();
     };
     e = bf ? launch(dkv_kernel<__nv_bfloat16>) : launch(dkv_kernel<__half>);
