@@ -102,7 +102,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -362,11 +362,17 @@ def main():
             alg = 10 * D * p_sh
         avg_ms = tot_ms / cnt
         if mode in ("fda",):
-            e = 2
-            by = (2 * T * G * D * e + 2 * T * L * D * e) * B * Hkv * shard_frac
+            # algorithmic bytes of the depth-only kernels (bf16): forward reads q and the depth
+            # K/V and writes o + lse; backward reads q, o, dout and the depth K/V, writes dq and
+            # the depth gradients
+            nq, nd, nl = T * G * D * 2, T * L * D * 2, T * G * 4
+            per_unit = (2 * nq + 2 * nd + nl) if name == "fda_fwd" else (4 * nq + 4 * nd + nl)
+            by = per_unit * B * Hkv * shard_frac
             ach = by / (avg_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                        "frac": ach / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": pk["source"]}
+                        "frac": ach / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": pk["source"],
+                        "avg_launch_ms": avg_ms,
+                        "kernels": {k: {"launches": c, "total_ms": round(m, 3)} for k, (c, m) in prof.items()}}
         else:
             ach = alg / (avg_ms * 1e-3) / 1e12
             roofline = {"bound": "tensor", "kernel": name, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
@@ -433,7 +439,8 @@ def main():
 
     if rank == 0:
         line = {
-            "metric": "MoDA fwd+bwd TFLOP/s (bf16, T=64K, L=32)" if not args.fwd_only else "MoDA fwd TFLOP/s",
+            "metric": ("MoDA fwd+bwd TFLOP/s (bf16, T=64K, L=32)" if args.workload == DEFAULT_WORKLOAD else "MoDA fwd+bwd TFLOP/s")
+            if not args.fwd_only else "MoDA fwd TFLOP/s",
             "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",

@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include "profiler.cuh"
 #include "simt_mma_kernels.cuh"
+#include "fda_kernels.cuh"
 #ifndef MODA_NO_TCGEN05
 #include "tc_kernels.cuh"
 #include "tc_bwd_kernels.cuh"
@@ -141,6 +142,48 @@ int simt_bwd_d(const Params& p, int D, cudaStream_t st) {
   return D == 64 ? simt_bwd<T, 64>(p, st) : simt_bwd<T, 128>(p, st);
 }
 
+// ----------------------------------------------------------------- depth-only (FDA) bandwidth path
+bool use_fda(const moda_problem* pr, bool is_bwd) {
+  if (pr->mode != MODA_DEPTH_ONLY || pr->path == MODA_PATH_SIMT_MMA || pr->path == MODA_PATH_TCGEN05) return false;
+  return !is_bwd || fda::bwd_supported(pr->G, pr->D);
+}
+
+template <typename T, int D>
+int fda_fwd(const Params& p, cudaStream_t st) {
+  const int64_t units = (int64_t)p.B * p.T_kv * p.H;
+  int blocks = (int)((units + 7) / 8);
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  {
+    prof::Scope ps(prof::kFdaFwd, st);
+    fda::fwd_kernel<T, D><<<blocks, 256, 0, st>>>(p);
+  }
+  MODA_CUDA(cudaGetLastError());
+  g_last_launches += 1;
+  return MODA_OK;
+}
+
+template <typename T, int D>
+int fda_bwd(const Params& p, cudaStream_t st) {
+  const int64_t units = (int64_t)p.B * p.T_kv * p.H;
+  int blocks = (int)((units + 3) / 4);
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  {
+    prof::Scope ps(prof::kFdaBwd, st);
+    if (p.G == 1) fda::bwd_kernel<T, D, 1><<<blocks, 128, 0, st>>>(p);
+    else if (p.G == 2) fda::bwd_kernel<T, D, 2><<<blocks, 128, 0, st>>>(p);
+    else if constexpr (D == 64) fda::bwd_kernel<T, D, 4><<<blocks, 128, 0, st>>>(p);
+  }
+  MODA_CUDA(cudaGetLastError());
+  g_last_launches += 1;
+  return MODA_OK;
+}
+
+template <typename T>
+int fda_dispatch(const Params& p, int D, bool is_bwd, cudaStream_t st) {
+  if (is_bwd) return D == 64 ? fda_bwd<T, 64>(p, st) : fda_bwd<T, 128>(p, st);
+  return D == 64 ? fda_fwd<T, 64>(p, st) : fda_fwd<T, 128>(p, st);
+}
+
 int resolve_path(const moda_problem* pr, bool is_bwd) {
 #ifndef MODA_NO_TCGEN05
   const bool ok = is_bwd ? tc::bwd_supported(pr) : tc::fwd_supported(pr);
@@ -204,6 +247,9 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (!guard.ok) return cuda_fail(guard.err);
   g_last_launches = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (use_fda(prob, false))
+    return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, st)
+                                    : fda_dispatch<__half>(p, prob->D, false, st);
 #ifndef MODA_NO_TCGEN05
   if (path == MODA_PATH_TCGEN05) return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
 #endif
@@ -265,6 +311,9 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (!guard.ok) return cuda_fail(guard.err);
   g_last_launches = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (use_fda(prob, true))
+    return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, st)
+                                    : fda_dispatch<__half>(p, prob->D, true, st);
 #ifndef MODA_NO_TCGEN05
   if (path == MODA_PATH_TCGEN05) {
     void* extra = reinterpret_cast<unsigned char*>(workspace) + delta_bytes(prob);

@@ -269,3 +269,31 @@ def test_tcgen05_backward_bitwise_reproducible_and_batched(M):
             assert torch.equal(a, b)
     finally:
         M.set_kernel_path(old)
+
+
+# ------------------------------------------------------------------ depth-only bandwidth kernels
+@pytest.mark.parametrize("D,T,L,G,dt", [
+    (128, 1, 1, 1, "bf16"), (128, 33, 5, 2, "bf16"), (128, 100, 32, 1, "bf16"), (128, 64, 40, 1, "fp16"),
+    (128, 50, 7, 4, "bf16"), (64, 197, 11, 1, "bf16"), (64, 60, 33, 4, "fp16"), (64, 17, 3, 8, "bf16"),
+])
+def test_depth_only_bandwidth_kernels(M, D, T, L, G, dt):
+    """parallel_fda on the default path: one warp per (batch, position, head), fp32 registers.
+    (G values the backward kernel does not hold in registers fall back to the mma.sync path.)"""
+    _run_case(M, mo.MODE_DEPTH_ONLY, 2, T, 3, D, L, G, DT[dt], None, seed=300 + T + L)
+
+
+def test_depth_only_paths_agree(M):
+    dev = torch.device("cuda", 0)
+    q, _, _, kd, vd, dout = mo.make_inputs(55, 2, 77, 2, 128, 9, 2, dtype=torch.bfloat16, with_seq=False)
+    q, kd, vd, dout = [x.to(dev) for x in (q, kd, vd, dout)]
+    outs = {}
+    for path in (M.PATH_AUTO, M.PATH_SIMT_MMA):
+        old = M.set_kernel_path(path)
+        try:
+            o, lse = M.parallel_fda_fwd(q, cached_k=kd, cached_v=vd, moda_group_num=2)
+            g = M.parallel_fda_bwd(q, o, None, lse, dout, cached_k=kd, cached_v=vd, moda_group_num=2)
+            outs[path] = [o, lse] + [x for x in g if x is not None]
+        finally:
+            M.set_kernel_path(old)
+    for a, b in zip(outs[M.PATH_AUTO], outs[M.PATH_SIMT_MMA]):
+        assert max_abs(a.float(), b.float()) <= 2e-2
