@@ -229,3 +229,69 @@ def make_inputs(seed, B, T_kv, H, D, L, G, dtype=torch.float32, with_seq=True, w
     vd = draw(B, T_kv * L, H, D) if L > 0 else None
     dout = draw(B, T_kv * G, H, D) if with_dout else None
     return q, k, v, kd, vd, dout
+
+
+# ---------------------------------------------------------------------------------------
+# Single-row forms, for sampling rows of problems too large for the full restatement.
+# The same rule as moda_attention_ref (one softmax over the visible sequence keys and the
+# visible depth rows of the query: moda_v14.py:1966-1989, moda_v16.py:2553-2580), written
+# for one (b, h, r) at a time so that cost is O(T) per sampled row.
+# ---------------------------------------------------------------------------------------
+def row_terms(q, k, v, depth_k, depth_v, dout, b, h, r, scale, G, mode, chunk_positions):
+    """fp32 terms of query row r of head (b, h): dict with o, lse (base 2), the softmax
+    weights over the visible sequence keys [0, s_end) and depth rows [d_lo, d_hi), and - when
+    ``dout`` is given - dS over the same two ranges and dq."""
+    D = q.shape[-1]
+    T_kv = q.shape[1] // G
+    L = depth_k.shape[1] // T_kv if depth_k is not None else 0
+    t = r // G
+    s_end = 0 if mode == MODE_DEPTH_ONLY else (T_kv if mode == MODE_NONCAUSAL else t + 1)
+    t0 = (t // chunk_positions) * chunk_positions if mode == MODE_CHUNK_VISIBLE else t
+    d_lo, d_hi = t0 * L, (t + 1) * L
+    qr = q[b, r, h].float()
+    keys, vals = [], []
+    if s_end > 0:
+        keys.append(k[b, :s_end, h].float()); vals.append(v[b, :s_end, h].float())
+    if d_hi > d_lo:
+        keys.append(depth_k[b, d_lo:d_hi, h].float()); vals.append(depth_v[b, d_lo:d_hi, h].float())
+    K, V = torch.cat(keys), torch.cat(vals)
+    logits = (K @ qr) * scale
+    w = torch.softmax(logits, dim=0)
+    o = w @ V
+    out = {"o": o, "lse": torch.logsumexp(logits, 0) / _LN2, "s_end": s_end, "d_lo": d_lo, "d_hi": d_hi,
+           "w_seq": w[:s_end], "w_dep": w[s_end:]}
+    if dout is not None:
+        dor = dout[b, r, h].float()
+        dS = w * (V @ dor - (o * dor).sum())
+        out["dS_seq"], out["dS_dep"] = dS[:s_end], dS[s_end:]
+        out["dq"] = scale * (dS @ K)
+    return out
+
+
+def depth_row_grads(q, k, v, depth_k, depth_v, dout, b, h, c, scale, G, mode, chunk_positions):
+    """(d_depth_k[c], d_depth_v[c]) of depth row c of head (b, h): sums over the (at most one
+    chunk of) query rows that can see it."""
+    T_kv = q.shape[1] // G
+    L = depth_k.shape[1] // T_kv
+    tp = c // L
+    t_end = min((tp // chunk_positions + 1) * chunk_positions, T_kv) if mode == MODE_CHUNK_VISIBLE else tp + 1
+    dk = torch.zeros(q.shape[-1]); dv = torch.zeros(q.shape[-1])
+    for r in range(tp * G, t_end * G):
+        tm = row_terms(q, k, v, depth_k, depth_v, dout, b, h, r, scale, G, mode, chunk_positions)
+        j = c - tm["d_lo"]
+        dk += scale * tm["dS_dep"][j] * q[b, r, h].float()
+        dv += tm["w_dep"][j] * dout[b, r, h].float()
+    return dk, dv
+
+
+def seq_key_grads(q, k, v, depth_k, depth_v, dout, b, h, j, scale, G, mode, chunk_positions):
+    """(dk[j], dv[j]) of sequence key j of head (b, h); cost O(rows that see j) x O(T), so meant
+    for keys near the end of a causal sequence."""
+    T_q = q.shape[1]
+    r_lo = 0 if mode == MODE_NONCAUSAL else j * G
+    dk = torch.zeros(q.shape[-1]); dv = torch.zeros(q.shape[-1])
+    for r in range(r_lo, T_q):
+        tm = row_terms(q, k, v, depth_k, depth_v, dout, b, h, r, scale, G, mode, chunk_positions)
+        dk += scale * tm["dS_seq"][j] * q[b, r, h].float()
+        dv += tm["w_seq"][j] * dout[b, r, h].float()
+    return dk, dv

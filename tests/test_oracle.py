@@ -79,3 +79,22 @@ def test_lse_is_base2_and_rows_normalised():
     # row 0 sees key 0 and its own 2 depth rows
     logits = torch.cat([(q[0, 0, 0] @ k[0, :1, 0].T), (kd[0, :2, 0] @ q[0, 0, 0])]) * 0.25
     assert abs(lse[0, 0, 0].item() - torch.logsumexp(logits, 0).item() / math.log(2.0)) < 1e-5
+
+
+@pytest.mark.parametrize("mode,G,L,cp", [(mo.MODE_CAUSAL, 2, 3, 1), (mo.MODE_CHUNK_VISIBLE, 4, 2, 16),
+                                         (mo.MODE_NONCAUSAL, 1, 2, 1)])
+def test_single_row_forms_match_full_restatement(mode, G, L, cp):
+    """The per-row helpers used to sample full-size problems agree with the full oracle."""
+    q, k, v, kd, vd, dout = mo.make_inputs(8, 1, 40, 2, 32, L, G)
+    o, lse, dq, dk, dv, dkd, dvd = mo.moda_attention_ref_grads(q, k, v, kd, vd, dout, None, G, mode, cp)
+    scale = 32 ** -0.5
+    for r in (0, 7, 40 * G - 1):
+        tm = mo.row_terms(q, k, v, kd, vd, dout, 0, 1, r, scale, G, mode, cp)
+        assert max_abs(tm["o"], o[0, r, 1]) <= 1e-5 and abs(tm["lse"].item() - lse[0, r, 1].item()) <= 1e-5
+        assert max_abs(tm["dq"], dq[0, r, 1]) <= 1e-5
+    for c in (0, 17, 40 * L - 1):
+        a, b_ = mo.depth_row_grads(q, k, v, kd, vd, dout, 0, 0, c, scale, G, mode, cp)
+        assert max_abs(a, dkd[0, c, 0]) <= 1e-5 and max_abs(b_, dvd[0, c, 0]) <= 1e-5
+    for j in (36, 39):
+        a, b_ = mo.seq_key_grads(q, k, v, kd, vd, dout, 0, 0, j, scale, G, mode, cp)
+        assert max_abs(a, dk[0, j, 0]) <= 1e-5 and max_abs(b_, dv[0, j, 0]) <= 1e-5
