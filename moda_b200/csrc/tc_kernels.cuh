@@ -384,18 +384,22 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
 #pragma unroll
         for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = s[i];
       }
-      float mx = -INFINITY;
       if (masked) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
           const int col = c0 + i;
-          if (col < lo || col >= hi) s[i] = -INFINITY;
-          mx = fmaxf(mx, s[i]);
+          s[i] = (col >= lo && col < hi) ? s[i] : -INFINITY;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, s[i]);
       }
+      // row maximum as a tree over 8 partial maxima (a single running maximum would be a
+      // 128-deep dependent chain for the one warp this sub-partition has on the job)
+      float mx8[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
+      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       const float m_new = fmaxf(m_used, mx * c);   // scale > 0 is required by this path
       // lazy rescale: keep the old reference maximum unless it is more than 2^8 too small
       float alpha = 1.f;
@@ -407,16 +411,16 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       l *= alpha;
-      float sum = 0.f;
+      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       uint32_t pk[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
         const float p0 = fast_exp2(fmaf(s[2 * i], c, -m_sub));
         const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, -m_sub));
-        sum += p0 + p1;
+        sum8[i & 7] += p0 + p1;
         pk[i] = Pack<T>::pack(p0, p1);
       }
-      l += sum;
+      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       if (kPTmem) {
         tmem_st32<0>(tmem_S + lane_addr + 0, pk);
         tmem_st32<32>(tmem_S + lane_addr + 32, pk);
