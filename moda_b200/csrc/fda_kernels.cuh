@@ -5,7 +5,7 @@
 // attention-tile pipeline (tensor cores, 128-row tiles) would multiply every query against
 // the depth rows of 127 other positions; here one warp owns one (batch, position, head),
 // streams its L K rows and L V rows once with 16-byte loads (8 lanes per 256-byte row, four
-// rows per pass), keeps scores, softmax and accumulators in fp32 registers, and writes o /
+// rows per pass, sixteen rows per online-softmax block), keeps scores, softmax and accumulators in fp32 registers, and writes o /
 // lse (forward) or dq, d_depth_k, d_depth_v (backward; rows are owner-exclusive, no atomics).
 // Numerics as in the other kernels: scores scaled by scale*log2(e), exp2, lse = m + log2(l),
 // delta from the stored o, dq and dk scaled by `scale` at the end.
@@ -46,7 +46,7 @@ __device__ __forceinline__ float cross4_max(float x) {
 // One warp per (b, t, h); all G query rows of the position reuse the K/V rows (L1-resident on
 // the second and later reads).
 template <typename T, int D>
-__global__ void __launch_bounds__(256) fwd_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Params p) {
   constexpr int CH = D / 64;
   const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
   const int64_t n_units = (int64_t)p.B * p.T_kv * p.H;
@@ -76,11 +76,11 @@ __global__ void __launch_bounds__(256) fwd_kernel(const __grid_constant__ Params
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[c][e] = 0.f;
 
-      for (int l0 = 0; l0 < p.L; l0 += 32) {
-        uint4 raw[8][CH];
-        float s[8];
+      for (int l0 = 0; l0 < p.L; l0 += 16) {
+        uint4 raw[4][CH];
+        float s[4];
 #pragma unroll
-        for (int ps = 0; ps < 8; ++ps) {          // all K loads of the block in flight together
+        for (int ps = 0; ps < 4; ++ps) {          // all K loads of the block in flight together
           const int key = l0 + ps * 4 + grp;
 #pragma unroll
           for (int c = 0; c < CH; ++c)
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(256) fwd_kernel(const __grid_constant__ Params
         }
         float bm = -INFINITY;
 #pragma unroll
-        for (int ps = 0; ps < 8; ++ps) {
+        for (int ps = 0; ps < 4; ++ps) {
           float d = 0.f;
 #pragma unroll
           for (int c = 0; c < CH; ++c) {
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(256) fwd_kernel(const __grid_constant__ Params
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[c][e] *= alpha;
 #pragma unroll
-        for (int ps = 0; ps < 8; ++ps) {          // V loads of the block
+        for (int ps = 0; ps < 4; ++ps) {          // V loads of the block
           const int key = l0 + ps * 4 + grp;
 #pragma unroll
           for (int c = 0; c < CH; ++c)
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256) fwd_kernel(const __grid_constant__ Params
                                      : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int ps = 0; ps < 8; ++ps) {
+        for (int ps = 0; ps < 4; ++ps) {
           const float pw = fast_exp2(s[ps] - m);  // 0 for invalid keys (s = -inf)
           lsum += pw;
 #pragma unroll
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(256) fwd_kernel(const __grid_constant__ Params
 // ------------------------------------------------------------------------- backward
 // One warp per (b, t, h), G query rows held in registers (G is a template parameter).
 template <typename T, int D, int G>
-__global__ void __launch_bounds__(128) bwd_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(128, (G == 1) ? 3 : 2) bwd_kernel(const __grid_constant__ Params p) {
   constexpr int CH = D / 64;
   const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
   const int64_t n_units = (int64_t)p.B * p.T_kv * p.H;
