@@ -42,6 +42,8 @@ WORKLOADS = {
     "config3_fda_T8192": ("fda", 8, 8192, 16, 1, 128, 32),
     "config5_deit_noncausal_T197": ("noncausal", 256, 197, 6, 1, 64, 11),
     "small_chunk_visible_T8192": ("chunk", 1, 8192, 8, 4, 128, 32),
+    # sequence-only twin of config 4 (same kernels, L = 0): gives the depth-KV overhead
+    "config4_seq_only_twin_T65536": ("chunk", 1, 65536, 8, 4, 128, 0),
 }
 DEFAULT_WORKLOAD = "config4_chunk_visible_T65536"
 CHUNK_ROWS = 64

@@ -668,6 +668,252 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
   }
 }
 
+// ==================================================================== depth dk / dv
+// Gradients of the depth K/V, query-stationary: the depth rows a block of 64 query rows can
+// see (its chunk's rows, or its positions' rows) are seen by no other query row when 64 is a
+// multiple of G (and of the chunk), so one CTA per (64-row block, h, b) owns them outright.
+// The CTA keeps the block's Q, dO, lse, delta in shared memory and streams its depth keys in
+// tiles of 128 (TMA, two buffers): S^T = Kd Q^T, dP^T = Vd dO^T (SS, N = 64) -> softmax
+// threads (thread = key row) write P^T and dS^T over the scores in TMEM -> dVd = P^T dO,
+// dKd = dS^T Q (TS, fresh accumulators) -> rows stored.  A key-tile CTA of dkv_kernel would
+// spend its whole life in set-up for the one or two steps such keys have; here the set-up is
+// paid once per 64 query rows.
+// grid (ceil(T_q / 64), H, B), 192 threads.  TMEM (512 columns): [0,64) S^T / P^T,
+// [64,128) dP^T / dS^T, [128,256) dVd, [256,384) dKd.
+enum DgBar : int { kDgRes = 0, kDgFull0 = 1, kDgEmpty0 = 3, kDgS = 5, kDgP = 6, kDgU = 7, kDgE = 8, kDgCount = 9 };
+constexpr uint32_t kDgSmem = 2 * kStepTile + 1024 + 2 * 2 * kTileBytes + 128;
+
+template <typename T>
+__global__ void __launch_bounds__(192, 1)
+depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
+                  const float* lse_t, int T_qp) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    return;
+  }
+  const uint32_t sQ = base, sDO = base + kStepTile, sStat = base + 2 * kStepTile;
+  const uint32_t sKV = base + 2 * kStepTile + 1024;          // 2 x {Kd tile, Vd tile}
+  const uint32_t ctl_off = 2 * kStepTile + 1024 + 4 * kTileBytes;
+  const uint32_t bars = base + ctl_off;
+  unsigned char* gctl = smem_raw + ctl_off;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 80);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 84);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 88);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
+
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = (int)blockIdx.x * kStep;
+  const int r_last = min(q0 + kStep, p.T_q) - 1;
+  int k_lo, k_hi, tmp;
+  dep_interval(p, q0, k_lo, tmp);
+  dep_interval(p, r_last, tmp, k_hi);
+  const int n = (k_hi - k_lo + kBN - 1) / kBN;          // key tiles of 128
+
+  if (tid == 0) {
+    mbar_init(bars + 8 * kDgRes, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (kDgFull0 + i), 1); mbar_init(bars + 8 * (kDgEmpty0 + i), 1); }
+    mbar_init(bars + 8 * kDgS, 1);
+    mbar_init(bars + 8 * kDgP, 128);
+    mbar_init(bars + 8 * kDgU, 1);
+    mbar_init(bars + 8 * kDgE, 128);
+    *abort_flag = 0;
+    *drain_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(bars + 80, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_S = tmem, tmem_P = tmem + 64, tmem_dV = tmem + 128, tmem_dK = tmem + 256;
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  const int64_t stat_base = ((int64_t)b * p.H + h) * T_qp;
+
+  if (warp == 5) {
+    // ---------------------------------------------------------------- TMA warp
+    if (n > 0) {
+      if (elect_one()) {
+        prefetch_map(&maps.q); prefetch_map(&maps.dout); prefetch_map(&maps.kd); prefetch_map(&maps.vd);
+        mbar_expect_tx(bars + 8 * kDgRes, 2 * kStepTile + 512);
+        tma_load_4d(sQ, &maps.q, bars + 8 * kDgRes, 0, h, q0, b);
+        tma_load_4d(sQ + kStepHalf, &maps.q, bars + 8 * kDgRes, 64, h, q0, b);
+        tma_load_4d(sDO, &maps.dout, bars + 8 * kDgRes, 0, h, q0, b);
+        tma_load_4d(sDO + kStepHalf, &maps.dout, bars + 8 * kDgRes, 64, h, q0, b);
+        bulk_load(sStat, lse_t + stat_base + q0, 256, bars + 8 * kDgRes);
+        bulk_load(sStat + 256, delta_t + stat_base + q0, 256, bars + 8 * kDgRes);
+      }
+      __syncwarp();
+      bool ok = true;
+      int issued = 0;
+      for (int i = 0; ok && i < n; ++i) {
+        const uint32_t slot = i & 1;
+        if (i >= 2 && !(ok = mbar_wait(bars + 8 * (kDgEmpty0 + slot), ((i >> 1) - 1) & 1, abort_flag, kDgEmpty0 + slot))) break;
+        const int row = k_lo + i * kBN;
+        const uint32_t dst = sKV + slot * 2 * kTileBytes, bar = bars + 8 * (kDgFull0 + slot);
+        if (elect_one()) {
+          mbar_expect_tx(bar, 2 * kTileBytes);
+          tma_load_4d(dst, &maps.kd, bar, 0, h, row, b);
+          tma_load_4d(dst + kHalfBytes, &maps.kd, bar, 64, h, row, b);
+          tma_load_4d(dst + kTileBytes, &maps.vd, bar, 0, h, row, b);
+          tma_load_4d(dst + kTileBytes + kHalfBytes, &maps.vd, bar, 64, h, row, b);
+        }
+        __syncwarp();
+        issued = i + 1;
+      }
+      if (!ok) {
+        mbar_wait(bars + 8 * kDgRes, 0, drain_flag, kDgRes);
+        for (int i = max(0, issued - 2); i < issued; ++i)
+          mbar_wait(bars + 8 * (kDgFull0 + (i & 1)), (i >> 1) & 1, drain_flag, kDgFull0 + (i & 1));
+      }
+    }
+  } else if (warp == 4) {
+    // ---------------------------------------------------------------- MMA warp
+    if (n > 0) {
+      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
+      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      const uint64_t dq_k = desc_kmajor(sQ), ddo_k = desc_kmajor(sDO);
+      const uint64_t dq_mn = desc_mnmajor(sQ, kStepHalf), ddo_mn = desc_mnmajor(sDO, kStepHalf);
+      bool ok = mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes);
+      for (int i = 0; ok && i < n; ++i) {
+        const uint32_t slot = i & 1, par = i & 1;
+        if (!(ok = mbar_wait(bars + 8 * (kDgFull0 + slot), (i >> 1) & 1, abort_flag, kDgFull0 + slot))) break;
+        tc_fence_after();
+        const uint64_t dK = desc_kmajor(sKV + slot * 2 * kTileBytes), dV = desc_kmajor(sKV + slot * 2 * kTileBytes + kTileBytes);
+        if (elect_one()) {   // scores of tile i (the updates of tile i-1 precede them in the pipe)
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            mma_ss(tmem_S, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ss(tmem_P, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+          }
+          tc_commit(bars + 8 * kDgS);
+          tc_commit(bars + 8 * (kDgEmpty0 + slot));      // Kd/Vd tile i has been read
+        }
+        __syncwarp();
+        if (!(ok = mbar_wait(bars + 8 * kDgP, par, abort_flag, kDgP))) break;       // P^T, dS^T written
+        if (i >= 1 && !(ok = mbar_wait(bars + 8 * kDgE, (i - 1) & 1, abort_flag, kDgE))) break;   // outputs of tile i-1 stored
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            mma_ts(tmem_dV, tmem_S + kk * 8, desc_add(ddo_mn, kk * 2048), idesc_t, kk > 0);
+            mma_ts(tmem_dK, tmem_P + kk * 8, desc_add(dq_mn, kk * 2048), idesc_t, kk > 0);
+          }
+          tc_commit(bars + 8 * kDgU);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / store warps
+    const int row = warp * 32 + lane;                 // key row of the tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const float c = p.scale_log2;
+    bool ok = n > 0;
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes));   // stats landed
+    for (int i = 0; ok && i < n; ++i) {
+      const int key = k_lo + i * kBN + row;
+      const bool valid = key < k_hi;
+      int rlo = 0, rhi = 0;                            // query rows that see this key
+      if (valid) {
+        const int tp = key / p.L;
+        rlo = tp * p.G;
+        rhi = ((p.mode == kChunkVisible) ? min((tp / p.Cb + 1) * p.Cb, p.T_kv) : tp + 1) * p.G;
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgS, i & 1, abort_flag, kDgS));
+      if (!ok) break;
+      tc_fence_after();
+      const float4* st4 = reinterpret_cast<const float4*>(smem_raw + 2 * kStepTile);
+      uint32_t su[64], du[64];
+      tmem_ld32<0>(tmem_S + lane_addr, su);
+      tmem_ld32<32>(tmem_S + lane_addr + 32, su);
+      tmem_ld32<0>(tmem_P + lane_addr, du);
+      tmem_ld32<32>(tmem_P + lane_addr + 32, du);
+      tmem_wait_ld();
+      float pr[64], dd[64];
+#pragma unroll
+      for (int j4 = 0; j4 < 16; ++j4) {
+        const float4 l4 = st4[j4], d4 = st4[16 + j4];
+        pr[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 0]), c, -l4.x));
+        pr[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 1]), c, -l4.y));
+        pr[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 2]), c, -l4.z));
+        pr[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 3]), c, -l4.w));
+        dd[4 * j4 + 0] = __uint_as_float(du[4 * j4 + 0]) - d4.x;
+        dd[4 * j4 + 1] = __uint_as_float(du[4 * j4 + 1]) - d4.y;
+        dd[4 * j4 + 2] = __uint_as_float(du[4 * j4 + 2]) - d4.z;
+        dd[4 * j4 + 3] = __uint_as_float(du[4 * j4 + 3]) - d4.w;
+      }
+#pragma unroll
+      for (int jj = 0; jj < 64; ++jj) {
+        const int rr = q0 + jj;
+        pr[jj] = (rr >= rlo && rr < rhi) ? pr[jj] : 0.f;
+      }
+      uint32_t pp[32], pd[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
+        pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
+      }
+      tmem_st32<0>(tmem_S + lane_addr, pp);
+      tmem_st32<0>(tmem_P + lane_addr, pd);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * kDgP);
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgU, i & 1, abort_flag, kDgU));
+      if (!ok) break;
+      tc_fence_after();
+      T* gdk = reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, key, h);
+      T* gdv = reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(b, key, h);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint32_t ov[32], ok2[32];
+        tmem_ld32<0>(tmem_dV + lane_addr + q4 * 32, ov);
+        tmem_ld32<0>(tmem_dK + lane_addr + q4 * 32, ok2);
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint4 v4, k4;
+            v4.x = Pack<T>::pack(__uint_as_float(ov[e * 8 + 0]), __uint_as_float(ov[e * 8 + 1]));
+            v4.y = Pack<T>::pack(__uint_as_float(ov[e * 8 + 2]), __uint_as_float(ov[e * 8 + 3]));
+            v4.z = Pack<T>::pack(__uint_as_float(ov[e * 8 + 4]), __uint_as_float(ov[e * 8 + 5]));
+            v4.w = Pack<T>::pack(__uint_as_float(ov[e * 8 + 6]), __uint_as_float(ov[e * 8 + 7]));
+            k4.x = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 0]) * p.scale, __uint_as_float(ok2[e * 8 + 1]) * p.scale);
+            k4.y = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 2]) * p.scale, __uint_as_float(ok2[e * 8 + 3]) * p.scale);
+            k4.z = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 4]) * p.scale, __uint_as_float(ok2[e * 8 + 5]) * p.scale);
+            k4.w = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 6]) * p.scale, __uint_as_float(ok2[e * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(gdv + q4 * 32 + e * 8) = v4;
+            *reinterpret_cast<uint4*>(gdk + q4 * 32 + e * 8) = k4;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bars + 8 * kDgE);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// The query-stationary depth-gradient kernel owns its depth rows only when a 64-row block
+// holds whole positions (64 % G == 0) and, for chunk-visible, whole chunks.
+inline bool depth_grad_applies(const Params& p, const moda_problem* pr) {
+  if (p.L <= 0 || (kStep % p.G) != 0) return false;
+  if (pr->mode == MODA_CHUNK_VISIBLE && (kStep % pr->chunk_rows) != 0) return false;
+  return true;
+}
+
 // ------------------------------------------------------------------ host side
 inline bool make_map_rows(CUtensorMap* m, const View& v, int dtype, int B, int64_t T, int H, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -749,8 +995,9 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
   }
   {
     const size_t smem = kDkvRing * (size_t)kDkvSlot + 2 * (size_t)kDkvPairBytes + kCtlBytes;
+    const bool dg = depth_grad_applies(p, pr);
     const int n_seq = (p.T_kv + kBN - 1) / kBN;
-    const int n_dep = (int)((TL + kBN - 1) / kBN);
+    const int n_dep = dg ? 0 : (int)((TL + kBN - 1) / kBN);
     dim3 grid(n_seq + n_dep, p.H, p.B);
     auto launch = [&](auto kern) -> cudaError_t {
       cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -762,6 +1009,19 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
     e = bf ? launch(dkv_kernel<__nv_bfloat16>) : launch(dkv_kernel<__half>);
     if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
     *launches += 1;
+    if (dg) {
+      dim3 ggrid((p.T_q + kStep - 1) / kStep, p.H, p.B);
+      auto glaunch = [&](auto kern) -> cudaError_t {
+        cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDgSmem);
+        if (er != cudaSuccess) return er;
+        prof::Scope ps(prof::kDepthGradTc, st);
+        kern<<<ggrid, 192, kDgSmem, st>>>(p, dkm, delta_t, lse_t, T_qp);
+        return cudaGetLastError();
+      };
+      e = bf ? glaunch(depth_grad_kernel<__nv_bfloat16>) : glaunch(depth_grad_kernel<__half>);
+      if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+      *launches += 1;
+    }
   }
   return MODA_OK;
 }
