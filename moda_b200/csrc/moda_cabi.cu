@@ -12,6 +12,7 @@
 #ifndef MODA_NO_TCGEN05
 #include "tc_kernels.cuh"
 #include "tc_bwd_kernels.cuh"
+#include "tc_fwd2_kernel.cuh"
 #endif
 
 namespace {
@@ -251,7 +252,15 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
     return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, st)
                                     : fda_dispatch<__half>(p, prob->D, false, st);
 #ifndef MODA_NO_TCGEN05
-  if (path == MODA_PATH_TCGEN05) return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+  if (path == MODA_PATH_TCGEN05) {
+    // Two forwards exist.  Default: two CTAs per SM, each a simple QK -> softmax -> PV sequence
+    // (tc_kernels.cuh).  Alternative (debug variant bit 64): one CTA per SM with Q in TMEM and
+    // decoupled score / PV / TMA warps (tc_fwd2_kernel.cuh).  Measured on config 4 they take the
+    // same number of SM clocks per key tile (both are bound by the softmax warps), so the simpler
+    // one is the default.
+    if (tc::debug_state().variant & 64) return tc::fwd2(p, prob, st, &g_last_launches, &g_last_cuda_error);
+    return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+  }
 #endif
   return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)
                                   : simt_fwd_d<__half>(p, prob->D, st);

@@ -297,3 +297,19 @@ def test_depth_only_paths_agree(M):
             M.set_kernel_path(old)
     for a, b in zip(outs[M.PATH_AUTO], outs[M.PATH_SIMT_MMA]):
         assert max_abs(a.float(), b.float()) <= 2e-2
+
+
+@pytest.mark.parametrize("mode,T,L,G", [(mo.MODE_CAUSAL, 300, 5, 4), (mo.MODE_CHUNK_VISIBLE, 1000, 3, 4),
+                                        (mo.MODE_NONCAUSAL, 129, 2, 1), (mo.MODE_CAUSAL, 2048, 24, 4)])
+def test_tcgen05_pipelined_forward_variant(M, mode, T, L, G):
+    """The alternative forward (one CTA per SM, Q in TMEM, decoupled MMA warps), selected through
+    the library's bring-up switch; same parity bar as the default forward."""
+    import ctypes
+    from moda_b200 import _cabi
+    lib = _cabi.load()
+    lib.moda_b200_debug_set(None, 64)
+    try:
+        _run_case(M, mode, 1, T, 2, 128, L, G, torch.bfloat16, None, seed=400 + T, path=M.PATH_TCGEN05, check_bwd=False)
+        assert _cabi.device_status() == 0
+    finally:
+        lib.moda_b200_debug_set(None, 0)
