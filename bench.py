@@ -368,7 +368,7 @@ def main():
         else:
             alg = 10 * D * p_sh
         avg_ms = tot_ms / cnt
-        if mode in ("fda",):
+        if name in ("fda_fwd", "fda_bwd"):
             # algorithmic bytes of the depth-only kernels (bf16): forward reads q and the depth
             # K/V and writes o + lse; backward reads q, o, dout and the depth K/V, writes dq and
             # the depth gradients

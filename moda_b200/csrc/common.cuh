@@ -29,6 +29,11 @@ struct Params {
   int Cb;                           // chunk-visible: base positions per chunk (chunk_rows / G)
   float scale;                      // softmax scale
   float scale_log2;                 // scale * log2(e); reference constant 1.4426950216 (moda_v14.py:109)
+  // Split evaluation of the own-position depth modes: the bandwidth kernels have already written
+  // the depth-only partial (forward: o = softmax over the depth rows alone, lse = its log-sum-exp;
+  // backward: dq = the depth rows' share) and this launch, run with L = 0, folds its sequence
+  // part into it in the epilogue.
+  int merge_depth;
 };
 
 // ---------------------------------------------------------------------------
@@ -78,6 +83,36 @@ template <> struct Pack<__half> {
     return __half22float2(*reinterpret_cast<__half2*>(&u));
   }
 };
+
+// Eight fp32 values (as register bits) times a, optionally plus eight stored 16-bit values times b.
+template <typename T> __device__ __forceinline__ uint4 pack8_scaled(const uint32_t* x, float a) {
+  return make_uint4(Pack<T>::pack(__uint_as_float(x[0]) * a, __uint_as_float(x[1]) * a),
+                    Pack<T>::pack(__uint_as_float(x[2]) * a, __uint_as_float(x[3]) * a),
+                    Pack<T>::pack(__uint_as_float(x[4]) * a, __uint_as_float(x[5]) * a),
+                    Pack<T>::pack(__uint_as_float(x[6]) * a, __uint_as_float(x[7]) * a));
+}
+template <typename T> __device__ __forceinline__ uint4 pack8_blend(const uint32_t* x, float a, const uint4& prev, float b) {
+  const float2 p0 = Pack<T>::unpack(prev.x), p1 = Pack<T>::unpack(prev.y), p2 = Pack<T>::unpack(prev.z), p3 = Pack<T>::unpack(prev.w);
+  return make_uint4(Pack<T>::pack(fmaf(__uint_as_float(x[0]), a, p0.x * b), fmaf(__uint_as_float(x[1]), a, p0.y * b)),
+                    Pack<T>::pack(fmaf(__uint_as_float(x[2]), a, p1.x * b), fmaf(__uint_as_float(x[3]), a, p1.y * b)),
+                    Pack<T>::pack(fmaf(__uint_as_float(x[4]), a, p2.x * b), fmaf(__uint_as_float(x[5]), a, p2.y * b)),
+                    Pack<T>::pack(fmaf(__uint_as_float(x[6]), a, p3.x * b), fmaf(__uint_as_float(x[7]), a, p3.y * b)));
+}
+
+// Softmax partials over two disjoint key sets: this kernel's (unnormalised accumulator, running
+// max m, row sum l; lse_self = m + log2 l) and a stored, normalised one with log-sum-exp lse_other.
+// Returns the factor for the accumulator (includes 1/l), the factor for the stored row and the
+// combined lse.  lse_other must be finite.
+__device__ __forceinline__ void merge_partials(float m, float l, float lse_other, float& w_acc, float& w_other, float& lse_out) {
+  if (!(l > 0.f)) { w_acc = 0.f; w_other = 1.f; lse_out = lse_other; return; }
+  const float lse_self = m + log2f(l);
+  const float mx = fmaxf(lse_self, lse_other);
+  const float a = exp2f(lse_self - mx), c = exp2f(lse_other - mx);
+  const float inv = 1.f / (a + c);
+  w_acc = a * inv / l;
+  w_other = c * inv;
+  lse_out = mx + log2f(a + c);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);

@@ -149,6 +149,25 @@ bool use_fda(const moda_problem* pr, bool is_bwd) {
   return !is_bwd || fda::bwd_supported(pr->G, pr->D);
 }
 
+// Own-position depth (parallel_moda, causal or not) as two launches: a query's depth keys are the
+// L rows of its own position, so that part of the softmax is the depth-only operator and runs at
+// HBM rate in the bandwidth kernels; the attention kernels then run on the sequence keys alone
+// and fold their part into the stored partial in the epilogue (Params::merge_depth).  Evaluating
+// those L keys inside 128-column attention tiles instead multiplies each query row against the
+// depth rows of every other position of its tile.
+bool split_depth(const moda_problem* pr, bool is_bwd) {
+  if (pr->path != MODA_PATH_AUTO || pr->L <= 0) return false;
+  if (pr->mode != MODA_CAUSAL && pr->mode != MODA_NONCAUSAL) return false;
+  return !is_bwd || fda::bwd_supported(pr->G, pr->D);
+}
+Params sequence_part(const Params& p) {
+  Params s = p;
+  s.L = 0;
+  s.kd = View{}; s.vd = View{}; s.dkd = View{}; s.dvd = View{};
+  s.merge_depth = 1;
+  return s;
+}
+
 template <typename T, int D>
 int fda_fwd(const Params& p, cudaStream_t st) {
   const int64_t units = (int64_t)p.B * p.T_kv * p.H;
@@ -251,6 +270,16 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (use_fda(prob, false))
     return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, st)
                                     : fda_dispatch<__half>(p, prob->D, false, st);
+  if (split_depth(prob, false)) {
+    if (int rc = prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, st)
+                                          : fda_dispatch<__half>(p, prob->D, false, st)) return rc;
+    p = sequence_part(p);
+#ifndef MODA_NO_TCGEN05
+    if (path == MODA_PATH_TCGEN05) return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+#endif
+    return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)
+                                    : simt_fwd_d<__half>(p, prob->D, st);
+  }
 #ifndef MODA_NO_TCGEN05
   if (path == MODA_PATH_TCGEN05) {
     // Two forwards exist.  Default: two CTAs per SM, each a simple QK -> softmax -> PV sequence
@@ -323,6 +352,11 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (use_fda(prob, true))
     return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, st)
                                     : fda_dispatch<__half>(p, prob->D, true, st);
+  if (split_depth(prob, true)) {   // depth rows' dq share, d_depth_k, d_depth_v; then the sequence part
+    if (int rc = prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, st)
+                                          : fda_dispatch<__half>(p, prob->D, true, st)) return rc;
+    p = sequence_part(p);
+  }
 #ifndef MODA_NO_TCGEN05
   if (path == MODA_PATH_TCGEN05) {
     void* extra = reinterpret_cast<unsigned char*>(workspace) + delta_bytes(prob);

@@ -266,19 +266,34 @@ __global__ void __launch_bounds__(128) fwd_kernel(const __grid_constant__ Params
 
   lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
   lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
-  const float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+  float invA = lA > 0.f ? 1.f / lA : 0.f, invB = lB > 0.f ? 1.f / lB : 0.f;
+  float depA = 0.f, depB = 0.f, lseA = mA + log2f(lA), lseB = mB + log2f(lB);
+  const bool merge = p.merge_depth != 0;
+  if (merge) {   // fold this kernel's sequence part into the stored depth-only partial
+    if (rA < p.T_q) merge_partials(mA, lA, p.lse[((int64_t)b * p.T_q + rA) * p.H + h], invA, depA, lseA);
+    if (rB < p.T_q) merge_partials(mB, lB, p.lse[((int64_t)b * p.T_q + rB) * p.H + h], invB, depB, lseB);
+    __syncwarp();   // every lane of a row's quad has read the stored lse before lane 0 replaces it
+  }
   T* go = reinterpret_cast<T*>(p.o.ptr) + p.o.off(b, 0, h);
   if (rA < p.T_q) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<uint32_t*>(go + (int64_t)rA * p.o.st + i * 8 + tq * 2) = Pack<T>::pack(acc[i][0] * invA, acc[i][1] * invA);
-    if (tq == 0) p.lse[((int64_t)b * p.T_q + rA) * p.H + h] = mA + log2f(lA);
+    for (int i = 0; i < D / 8; ++i) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(go + (int64_t)rA * p.o.st + i * 8 + tq * 2);
+      float x = acc[i][0] * invA, y = acc[i][1] * invA;
+      if (merge) { const float2 prev = Pack<T>::unpack(*dst); x = fmaf(prev.x, depA, x); y = fmaf(prev.y, depA, y); }
+      *dst = Pack<T>::pack(x, y);
+    }
+    if (tq == 0) p.lse[((int64_t)b * p.T_q + rA) * p.H + h] = lseA;
   }
   if (rB < p.T_q) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<uint32_t*>(go + (int64_t)rB * p.o.st + i * 8 + tq * 2) = Pack<T>::pack(acc[i][2] * invB, acc[i][3] * invB);
-    if (tq == 0) p.lse[((int64_t)b * p.T_q + rB) * p.H + h] = mB + log2f(lB);
+    for (int i = 0; i < D / 8; ++i) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(go + (int64_t)rB * p.o.st + i * 8 + tq * 2);
+      float x = acc[i][2] * invB, y = acc[i][3] * invB;
+      if (merge) { const float2 prev = Pack<T>::unpack(*dst); x = fmaf(prev.x, depB, x); y = fmaf(prev.y, depB, y); }
+      *dst = Pack<T>::pack(x, y);
+    }
+    if (tq == 0) p.lse[((int64_t)b * p.T_q + rB) * p.H + h] = lseB;
   }
 }
 
@@ -456,15 +471,24 @@ __global__ void __launch_bounds__(128) dq_kernel(const __grid_constant__ Params 
   cp_async_wait<0>();
 
   T* gdq = reinterpret_cast<T*>(p.dq.ptr) + p.dq.off(b, 0, h);
+  const bool merge = p.merge_depth != 0;   // dq already holds the depth rows' share
   if (rA < p.T_q) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<uint32_t*>(gdq + (int64_t)rA * p.dq.st + i * 8 + tq * 2) = Pack<T>::pack(acc[i][0] * p.scale, acc[i][1] * p.scale);
+    for (int i = 0; i < D / 8; ++i) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(gdq + (int64_t)rA * p.dq.st + i * 8 + tq * 2);
+      float x = acc[i][0] * p.scale, y = acc[i][1] * p.scale;
+      if (merge) { const float2 prev = Pack<T>::unpack(*dst); x += prev.x; y += prev.y; }
+      *dst = Pack<T>::pack(x, y);
+    }
   }
   if (rB < p.T_q) {
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-      *reinterpret_cast<uint32_t*>(gdq + (int64_t)rB * p.dq.st + i * 8 + tq * 2) = Pack<T>::pack(acc[i][2] * p.scale, acc[i][3] * p.scale);
+    for (int i = 0; i < D / 8; ++i) {
+      uint32_t* dst = reinterpret_cast<uint32_t*>(gdq + (int64_t)rB * p.dq.st + i * 8 + tq * 2);
+      float x = acc[i][2] * p.scale, y = acc[i][3] * p.scale;
+      if (merge) { const float2 prev = Pack<T>::unpack(*dst); x += prev.x; y += prev.y; }
+      *dst = Pack<T>::pack(x, y);
+    }
   }
 }
 

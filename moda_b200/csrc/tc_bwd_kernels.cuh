@@ -47,6 +47,15 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// Tile store shared -> global through the tensor map (bulk async-group of the issuing thread).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               :: "l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------ statistics pass
 // One warp per (b, h, r); a block of 8 warps covers 8 consecutive rows of one (b, h).
 template <typename T>
@@ -349,12 +358,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         if (r < p.T_q) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint4 v4;
-            v4.x = Pack<T>::pack(__uint_as_float(ov[i * 8 + 0]) * p.scale, __uint_as_float(ov[i * 8 + 1]) * p.scale);
-            v4.y = Pack<T>::pack(__uint_as_float(ov[i * 8 + 2]) * p.scale, __uint_as_float(ov[i * 8 + 3]) * p.scale);
-            v4.z = Pack<T>::pack(__uint_as_float(ov[i * 8 + 4]) * p.scale, __uint_as_float(ov[i * 8 + 5]) * p.scale);
-            v4.w = Pack<T>::pack(__uint_as_float(ov[i * 8 + 6]) * p.scale, __uint_as_float(ov[i * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(gdq + q4 * 32 + i * 8) = v4;
+            uint4* dst = reinterpret_cast<uint4*>(gdq + q4 * 32 + i * 8);
+            *dst = p.merge_depth ? pack8_blend<T>(ov + i * 8, p.scale, *dst, 1.f) : pack8_scaled<T>(ov + i * 8, p.scale);
           }
         }
       }
@@ -678,15 +683,35 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
 // dKd = dS^T Q (TS, fresh accumulators) -> rows stored.  A key-tile CTA of dkv_kernel would
 // spend its whole life in set-up for the one or two steps such keys have; here the set-up is
 // paid once per 64 query rows.
-// grid (ceil(T_q / 64), H, B), 192 threads.  TMEM (512 columns): [0,64) S^T / P^T,
-// [64,128) dP^T / dS^T, [128,256) dVd, [256,384) dKd.
-enum DgBar : int { kDgRes = 0, kDgFull0 = 1, kDgEmpty0 = 3, kDgS = 5, kDgP = 6, kDgU = 7, kDgE = 8, kDgCount = 9 };
-constexpr uint32_t kDgSmem = 2 * kStepTile + 1024 + 2 * 2 * kTileBytes + 128;
+//
+// Two score stages in TMEM let the scores of tile i+1 be issued ahead of the updates of tile i,
+// and the softmax threads work in the order softmax(i+1), then store(i): the tensor pipe runs
+// the updates of tile i under softmax(i+1) and the scores of tile i+2 under store(i).
+//
+// The two [128 x 128] gradient tiles of a key tile leave through shared memory and TMA tile
+// stores, one 32-row box per warp (a warp stages and stores its own rows, so no barrier is
+// involved, only the issuing lane's bulk-group wait before the rows are reused).  Stored
+// row-wise instead - a thread owns one key row, 32 threads each writing 16 bytes of their own
+// row per instruction - every store instruction half-fills 32 sectors, and the stores were the
+// longest phase of a tile.  A warp whose 32 rows are not all this block's (window not a multiple
+// of 32 rows) keeps the row-wise stores, masked per row.
+// Eight softmax / store warps: warp w and warp w + 4 share TMEM lanes 32 (w & 3) .. + 31 (key
+// rows); warps 0-3 take query columns [0,32) of the scores and stage dVd, warps 4-7 take query
+// columns [32,64) and stage dKd.
+// grid (ceil(T_q / 64), H, B), 320 threads.  TMEM (512 columns): stage s at [128 s, 128 s + 64)
+// S^T / P^T and [128 s + 64, 128 s + 128) dP^T / dS^T (the packed 16-bit P^T / dS^T of query
+// columns 32 g .. + 31 sit in the first 16 columns of that group's 32 fp32 columns);
+// [256,384) dVd, [384,512) dKd.
+enum DgBar : int { kDgRes = 0, kDgFull0 = 1, kDgEmpty0 = 3, kDgS0 = 5, kDgP0 = 7, kDgU = 9, kDgE = 10, kDgCount = 11 };
+constexpr uint32_t kDgOutOff = 2 * kStepTile + 1024 + 2 * 2 * kTileBytes;      // {dVd tile, dKd tile} staging
+constexpr uint32_t kDgSmem = kDgOutOff + 2 * kTileBytes + 128;
+struct DgOutMaps { CUtensorMap dkd, dvd; };                                     // 32-row boxes
+constexpr int kDgThreads = 320;                                                 // 8 softmax/store warps, MMA warp, TMA warp
 
 template <typename T>
-__global__ void __launch_bounds__(192, 1)
-depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
-                  const float* lse_t, int T_qp) {
+__global__ void __launch_bounds__(kDgThreads, 1)
+depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps,
+                  const __grid_constant__ DgOutMaps omaps, const float* delta_t, const float* lse_t, int T_qp) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {
@@ -695,12 +720,13 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
   }
   const uint32_t sQ = base, sDO = base + kStepTile, sStat = base + 2 * kStepTile;
   const uint32_t sKV = base + 2 * kStepTile + 1024;          // 2 x {Kd tile, Vd tile}
-  const uint32_t ctl_off = 2 * kStepTile + 1024 + 4 * kTileBytes;
+  const uint32_t sOut = base + kDgOutOff;
+  const uint32_t ctl_off = kDgOutOff + 2 * kTileBytes;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 80);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 84);
-  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 88);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 100);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 104);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
@@ -715,29 +741,32 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
 
   if (tid == 0) {
     mbar_init(bars + 8 * kDgRes, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (kDgFull0 + i), 1); mbar_init(bars + 8 * (kDgEmpty0 + i), 1); }
-    mbar_init(bars + 8 * kDgS, 1);
-    mbar_init(bars + 8 * kDgP, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (kDgFull0 + i), 1);
+      mbar_init(bars + 8 * (kDgEmpty0 + i), 1);
+      mbar_init(bars + 8 * (kDgS0 + i), 1);
+      mbar_init(bars + 8 * (kDgP0 + i), 256);
+    }
     mbar_init(bars + 8 * kDgU, 1);
-    mbar_init(bars + 8 * kDgE, 128);
+    mbar_init(bars + 8 * kDgE, 256);
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
-    tmem_alloc(bars + 80, 512);
+    tmem_alloc(bars + 96, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_S = tmem, tmem_P = tmem + 64, tmem_dV = tmem + 128, tmem_dK = tmem + 256;
+  const uint32_t tmem_dV = tmem + 256, tmem_dK = tmem + 384;   // score stage s: tmem + 128 s (+ 64 for dP^T)
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
   const int64_t stat_base = ((int64_t)b * p.H + h) * T_qp;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ---------------------------------------------------------------- TMA warp
     if (n > 0) {
       if (elect_one()) {
@@ -774,37 +803,47 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
           mbar_wait(bars + 8 * (kDgFull0 + (i & 1)), (i >> 1) & 1, drain_flag, kDgFull0 + (i & 1));
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA warp
     if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
       constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
       const uint64_t dq_k = desc_kmajor(sQ), ddo_k = desc_kmajor(sDO);
       const uint64_t dq_mn = desc_mnmajor(sQ, kStepHalf), ddo_mn = desc_mnmajor(sDO, kStepHalf);
-      bool ok = mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes);
-      for (int i = 0; ok && i < n; ++i) {
-        const uint32_t slot = i & 1, par = i & 1;
-        if (!(ok = mbar_wait(bars + 8 * (kDgFull0 + slot), (i >> 1) & 1, abort_flag, kDgFull0 + slot))) break;
+      // scores of tile j into stage j & 1; the updates that read that stage last (tile j - 2) were
+      // issued before, and the pipe runs in issue order
+      auto scores = [&](int j) -> bool {
+        const uint32_t slot = j & 1;
+        if (!mbar_wait(bars + 8 * (kDgFull0 + slot), (j >> 1) & 1, abort_flag, kDgFull0 + slot)) return false;
         tc_fence_after();
         const uint64_t dK = desc_kmajor(sKV + slot * 2 * kTileBytes), dV = desc_kmajor(sKV + slot * 2 * kTileBytes + kTileBytes);
-        if (elect_one()) {   // scores of tile i (the updates of tile i-1 precede them in the pipe)
+        const uint32_t tS = tmem + slot * 128, tP = tS + 64;
+        if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            mma_ss(tmem_S, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-            mma_ss(tmem_P, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           }
-          tc_commit(bars + 8 * kDgS);
-          tc_commit(bars + 8 * (kDgEmpty0 + slot));      // Kd/Vd tile i has been read
+          tc_commit(bars + 8 * (kDgS0 + slot));
+          tc_commit(bars + 8 * (kDgEmpty0 + slot));      // Kd/Vd tile j has been read
         }
         __syncwarp();
-        if (!(ok = mbar_wait(bars + 8 * kDgP, par, abort_flag, kDgP))) break;       // P^T, dS^T written
-        if (i >= 1 && !(ok = mbar_wait(bars + 8 * kDgE, (i - 1) & 1, abort_flag, kDgE))) break;   // outputs of tile i-1 stored
+        return true;
+      };
+      bool ok = mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes);
+      if (ok) ok = scores(0);
+      for (int i = 0; ok && i < n; ++i) {
+        if (i + 1 < n && !(ok = scores(i + 1))) break;
+        if (!(ok = mbar_wait(bars + 8 * (kDgP0 + (i & 1)), (i >> 1) & 1, abort_flag, kDgP0 + (i & 1)))) break;   // P^T, dS^T written
+        if (i >= 1 && !(ok = mbar_wait(bars + 8 * kDgE, (i - 1) & 1, abort_flag, kDgE))) break;   // accumulators of tile i-1 read
         tc_fence_after();
+        const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            mma_ts(tmem_dV, tmem_S + kk * 8, desc_add(ddo_mn, kk * 2048), idesc_t, kk > 0);
-            mma_ts(tmem_dK, tmem_P + kk * 8, desc_add(dq_mn, kk * 2048), idesc_t, kk > 0);
+            const uint32_t acol = (kk >> 1) * 32 + (kk & 1) * 8;   // query rows 16 kk .. + 15 of P^T / dS^T
+            mma_ts(tmem_dV, tS + acol, desc_add(ddo_mn, kk * 2048), idesc_t, kk > 0);
+            mma_ts(tmem_dK, tP + acol, desc_add(dq_mn, kk * 2048), idesc_t, kk > 0);
           }
           tc_commit(bars + 8 * kDgU);
         }
@@ -813,33 +852,33 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
     }
   } else {
     // ---------------------------------------------------------------- softmax / store warps
-    const int row = warp * 32 + lane;                 // key row of the tile == TMEM lane
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int wq = warp & 3, wg = warp >> 2;          // TMEM lane quarter; column half / output tensor
+    const int row = wq * 32 + lane;                   // key row of the tile == TMEM lane
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const float c = p.scale_log2;
-    bool ok = n > 0;
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes));   // stats landed
-    for (int i = 0; ok && i < n; ++i) {
-      const int key = k_lo + i * kBN + row;
-      const bool valid = key < k_hi;
-      int rlo = 0, rhi = 0;                            // query rows that see this key
-      if (valid) {
+
+    // this warp's 32 query columns of P^T and dS^T of tile j, over its scores (stage j & 1)
+    auto softmax = [&](int j) -> bool {
+      const int key = k_lo + j * kBN + row;
+      int jlo = 0, jn = 0;                            // query rows [q0 + jlo, q0 + jlo + jn) see this key
+      if (key < k_hi) {
         const int tp = key / p.L;
-        rlo = tp * p.G;
-        rhi = ((p.mode == kChunkVisible) ? min((tp / p.Cb + 1) * p.Cb, p.T_kv) : tp + 1) * p.G;
+        const int rlo = tp * p.G;
+        const int rhi = ((p.mode == kChunkVisible) ? min((tp / p.Cb + 1) * p.Cb, p.T_kv) : tp + 1) * p.G;
+        jlo = rlo - q0 - 32 * wg;
+        jn = rhi - rlo;
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgS, i & 1, abort_flag, kDgS));
-      if (!ok) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kDgS0 + (j & 1)), (j >> 1) & 1, abort_flag, kDgS0 + (j & 1)))) return false;
       tc_fence_after();
-      const float4* st4 = reinterpret_cast<const float4*>(smem_raw + 2 * kStepTile);
-      uint32_t su[64], du[64];
-      tmem_ld32<0>(tmem_S + lane_addr, su);
-      tmem_ld32<32>(tmem_S + lane_addr + 32, su);
-      tmem_ld32<0>(tmem_P + lane_addr, du);
-      tmem_ld32<32>(tmem_P + lane_addr + 32, du);
+      const uint32_t tS = tmem + (j & 1) * 128 + lane_addr, tP = tS + 64;
+      const float4* st4 = reinterpret_cast<const float4*>(smem_raw + 2 * kStepTile) + 8 * wg;
+      uint32_t su[32], du[32];
+      tmem_ld32<0>(tS + 32 * wg, su);
+      tmem_ld32<0>(tP + 32 * wg, du);
       tmem_wait_ld();
-      float pr[64], dd[64];
+      float pr[32], dd[32];
 #pragma unroll
-      for (int j4 = 0; j4 < 16; ++j4) {
+      for (int j4 = 0; j4 < 8; ++j4) {
         const float4 l4 = st4[j4], d4 = st4[16 + j4];
         pr[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 0]), c, -l4.x));
         pr[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 1]), c, -l4.y));
@@ -851,52 +890,80 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
         dd[4 * j4 + 3] = __uint_as_float(du[4 * j4 + 3]) - d4.w;
       }
 #pragma unroll
-      for (int jj = 0; jj < 64; ++jj) {
-        const int rr = q0 + jj;
-        pr[jj] = (rr >= rlo && rr < rhi) ? pr[jj] : 0.f;
-      }
-      uint32_t pp[32], pd[32];
+      for (int jj = 0; jj < 32; ++jj) pr[jj] = ((unsigned)(jj - jlo) < (unsigned)jn) ? pr[jj] : 0.f;
+      uint32_t pp[16], pd[16];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
+      for (int jj = 0; jj < 16; ++jj) {
         pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
         pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
       }
-      tmem_st32<0>(tmem_S + lane_addr, pp);
-      tmem_st32<0>(tmem_P + lane_addr, pd);
+      // 16-bit pairs over the first half of the warp's own fp32 columns (the other warpgroup may
+      // still be reading its columns): query columns 32 wg .. + 31 at TMEM columns 32 wg .. + 15
+      tmem_st16<0>(tS + 32 * wg, pp);
+      tmem_st16<0>(tP + 32 * wg, pd);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bars + 8 * kDgP);
+      mbar_arrive(bars + 8 * (kDgP0 + (j & 1)));
+      return true;
+    };
+
+    bool ok = n > 0;
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes));   // stats landed
+    if (ok) ok = softmax(0);
+    for (int i = 0; ok && i < n; ++i) {
+      if (i + 1 < n && !(ok = softmax(i + 1))) break;
       ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgU, i & 1, abort_flag, kDgU));
       if (!ok) break;
       tc_fence_after();
-      T* gdk = reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, key, h);
-      T* gdv = reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(b, key, h);
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        uint32_t ov[32], ok2[32];
-        tmem_ld32<0>(tmem_dV + lane_addr + q4 * 32, ov);
-        tmem_ld32<0>(tmem_dK + lane_addr + q4 * 32, ok2);
+      const int key0 = k_lo + i * kBN + wq * 32;           // first key row of this warp
+      const uint32_t tacc = (wg ? tmem_dK : tmem_dV) + lane_addr;
+      const float f = wg ? p.scale : 1.f;
+      if (key0 + 32 <= k_hi) {                             // every row of the warp is this block's
+        if (lane == 0) bulk_wait_read_all();               // this warp's previous store has read its rows
+        __syncwarp();
+        // staging = the TMA box layout: two [128 rows x 128 B] halves per tensor, 16-byte chunk c of
+        // row r at chunk c ^ (r & 7)
+        unsigned char* orow = smem_raw + kDgOutOff + wg * kTileBytes + row * 128;
+        uint32_t ov[128];
+        tmem_ld32<0>(tacc, ov);
+        tmem_ld32<32>(tacc + 32, ov);
+        tmem_ld32<64>(tacc + 64, ov);
+        tmem_ld32<96>(tacc + 96, ov);
         tmem_wait_ld();
-        if (valid) {
+        tc_fence_before();
+        mbar_arrive(bars + 8 * kDgE);                      // accumulator values are in registers
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            uint4 v4, k4;
-            v4.x = Pack<T>::pack(__uint_as_float(ov[e * 8 + 0]), __uint_as_float(ov[e * 8 + 1]));
-            v4.y = Pack<T>::pack(__uint_as_float(ov[e * 8 + 2]), __uint_as_float(ov[e * 8 + 3]));
-            v4.z = Pack<T>::pack(__uint_as_float(ov[e * 8 + 4]), __uint_as_float(ov[e * 8 + 5]));
-            v4.w = Pack<T>::pack(__uint_as_float(ov[e * 8 + 6]), __uint_as_float(ov[e * 8 + 7]));
-            k4.x = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 0]) * p.scale, __uint_as_float(ok2[e * 8 + 1]) * p.scale);
-            k4.y = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 2]) * p.scale, __uint_as_float(ok2[e * 8 + 3]) * p.scale);
-            k4.z = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 4]) * p.scale, __uint_as_float(ok2[e * 8 + 5]) * p.scale);
-            k4.w = Pack<T>::pack(__uint_as_float(ok2[e * 8 + 6]) * p.scale, __uint_as_float(ok2[e * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(gdv + q4 * 32 + e * 8) = v4;
-            *reinterpret_cast<uint4*>(gdk + q4 * 32 + e * 8) = k4;
+        for (int ch = 0; ch < 16; ++ch)
+          *reinterpret_cast<uint4*>(orow + (ch >> 3) * kHalfBytes + (((ch & 7) ^ (row & 7)) << 4)) = pack8_scaled<T>(ov + ch * 8, f);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t src = sOut + wg * kTileBytes + wq * 32 * 128;
+          const CUtensorMap* om = wg ? &omaps.dkd : &omaps.dvd;
+          tma_store_4d(om, src, 0, h, key0, b);
+          tma_store_4d(om, src + kHalfBytes, 64, h, key0, b);
+          bulk_commit();
+        }
+        __syncwarp();
+      } else {
+        const int key = key0 + lane;
+        const bool valid = key < k_hi;
+        T* gout = wg ? reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, key, h) : reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(b, key, h);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint32_t ov[32];
+          tmem_ld32<0>(tacc + q4 * 32, ov);
+          tmem_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) *reinterpret_cast<uint4*>(gout + q4 * 32 + e * 8) = pack8_scaled<T>(ov + e * 8, f);
           }
         }
+        tc_fence_before();
+        mbar_arrive(bars + 8 * kDgE);
       }
-      tc_fence_before();
-      mbar_arrive(bars + 8 * kDgE);
     }
+    if (lane == 0) bulk_wait_read_all();                   // staged rows are read before the CTA's smem goes
   }
   tc_fence_before();
   __syncthreads();
@@ -996,6 +1063,9 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
   {
     const size_t smem = kDkvRing * (size_t)kDkvSlot + 2 * (size_t)kDkvPairBytes + kCtlBytes;
     const bool dg = depth_grad_applies(p, pr);
+    DgOutMaps om;
+    if (dg && !(make_map_rows(&om.dkd, p.dkd, pr->dtype, p.B, TL, p.H, 32) && make_map_rows(&om.dvd, p.dvd, pr->dtype, p.B, TL, p.H, 32)))
+      return MODA_ERR_UNSUPPORTED;
     const int n_seq = (p.T_kv + kBN - 1) / kBN;
     const int n_dep = dg ? 0 : (int)((TL + kBN - 1) / kBN);
     dim3 grid(n_seq + n_dep, p.H, p.B);
@@ -1015,7 +1085,7 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
         cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDgSmem);
         if (er != cudaSuccess) return er;
         prof::Scope ps(prof::kDepthGradTc, st);
-        kern<<<ggrid, 192, kDgSmem, st>>>(p, dkm, delta_t, lse_t, T_qp);
+        kern<<<ggrid, kDgThreads, kDgSmem, st>>>(p, dkm, om, delta_t, lse_t, T_qp);
         return cudaGetLastError();
       };
       e = bf ? glaunch(depth_grad_kernel<__nv_bfloat16>) : glaunch(depth_grad_kernel<__half>);

@@ -53,17 +53,6 @@ __device__ __forceinline__ bool pair_exchange(volatile unsigned long long* xchg,
   atomicCAS(&g_tc_status, 0, (4 << 8));
   return false;
 }
-template <int OFF, int N>
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[N]) {
-  static_assert(OFF + 16 <= N, "register window out of range");
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      :: "r"(taddr), "r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]), "r"(r[OFF + 4]), "r"(r[OFF + 5]),
-         "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]), "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]),
-         "r"(r[OFF + 12]), "r"(r[OFF + 13]), "r"(r[OFF + 14]), "r"(r[OFF + 15])
-      : "memory");
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kF2Threads, 1)
 fwd2_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd2Maps maps) {

@@ -171,6 +171,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[N]
          "r"(r[OFF + 30]), "r"(r[OFF + 31])
       : "memory");
 }
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[N]) {
+  static_assert(OFF + 16 <= N, "register window out of range");
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      :: "r"(taddr), "r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]), "r"(r[OFF + 4]), "r"(r[OFF + 5]),
+         "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]), "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]),
+         "r"(r[OFF + 12]), "r"(r[OFF + 13]), "r"(r[OFF + 14]), "r"(r[OFF + 15])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -371,56 +381,64 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
       const bool masked = is_dep || (c0 + kBN > walk.seq_full_hi);
       const int lo = is_dep ? dlo : slo, hi = is_dep ? dhi : shi;
 
-      uint32_t su[128];
-      tmem_ld32<0>(tmem_S + lane_addr + 0, su);
-      tmem_ld32<32>(tmem_S + lane_addr + 32, su);
-      tmem_ld32<64>(tmem_S + lane_addr + 64, su);
-      tmem_ld32<96>(tmem_S + lane_addr + 96, su);
-      tmem_wait_ld();
-      float s[128];
-#pragma unroll
-      for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
-      if (dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = s[i];
-      }
-      if (masked) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const int col = c0 + i;
-          s[i] = (col >= lo && col < hi) ? s[i] : -INFINITY;
-        }
-      }
-      // row maximum as a tree over 8 partial maxima (a single running maximum would be a
-      // 128-deep dependent chain for the one warp this sub-partition has on the job)
-      float mx8[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = s[i];
-#pragma unroll
-      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      const float m_new = fmaxf(m_used, mx * c);   // scale > 0 is required by this path
-      // lazy rescale: keep the old reference maximum unless it is more than 2^8 too small
+      // A depth tile holds the rows of several positions; a warp whose 32 query rows see none of
+      // its columns contributes an all-zero P block and skips the scores altogether.
+      const bool none = is_dep && __all_sync(0xffffffffu, (c0 + kBN <= lo) || (c0 >= hi));
       float alpha = 1.f;
       bool grow = false;
-      if (m_new > m_used + 8.f) {        // also true for the first finite maximum (m_used = -inf)
-        alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
-        grow = (m_used != -INFINITY);    // nothing accumulated yet => nothing to rescale
-        m_used = m_new;
-      }
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      l *= alpha;
-      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       uint32_t pk[64];
+      if (none) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = fast_exp2(fmaf(s[2 * i], c, -m_sub));
-        const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, -m_sub));
-        sum8[i & 7] += p0 + p1;
-        pk[i] = Pack<T>::pack(p0, p1);
+        for (int i = 0; i < 64; ++i) pk[i] = 0u;
+      } else {
+        uint32_t su[128];
+        tmem_ld32<0>(tmem_S + lane_addr + 0, su);
+        tmem_ld32<32>(tmem_S + lane_addr + 32, su);
+        tmem_ld32<64>(tmem_S + lane_addr + 64, su);
+        tmem_ld32<96>(tmem_S + lane_addr + 96, su);
+        tmem_wait_ld();
+        float s[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
+        if (dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = s[i];
+        }
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            const int col = c0 + i;
+            s[i] = (col >= lo && col < hi) ? s[i] : -INFINITY;
+          }
+        }
+        // row maximum as a tree over 8 partial maxima (a single running maximum would be a
+        // 128-deep dependent chain for the one warp this sub-partition has on the job)
+        float mx8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx8[i] = s[i];
+#pragma unroll
+        for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
+        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                               fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        const float m_new = fmaxf(m_used, mx * c);   // scale > 0 is required by this path
+        // lazy rescale: keep the old reference maximum unless it is more than 2^8 too small
+        if (m_new > m_used + 8.f) {        // also true for the first finite maximum (m_used = -inf)
+          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+          grow = (m_used != -INFINITY);    // nothing accumulated yet => nothing to rescale
+          m_used = m_new;
+        }
+        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+        l *= alpha;
+        float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float p0 = fast_exp2(fmaf(s[2 * i], c, -m_sub));
+          const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, -m_sub));
+          sum8[i & 7] += p0 + p1;
+          pk[i] = Pack<T>::pack(p0, p1);
+        }
+        l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       }
-      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       if (kPTmem) {
         tmem_st32<0>(tmem_S + lane_addr + 0, pk);
         tmem_st32<32>(tmem_S + lane_addr + 32, pk);
@@ -460,7 +478,10 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
     if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kBarO, (n_tiles - 1) & 1, abort_flag, kBarO));
     if (ok && n_tiles > 0) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      float inv = l > 0.f ? 1.f / l : 0.f, w_dep = 0.f, lse_out = m_used + log2f(l);
+      const bool merge = p.merge_depth != 0;
+      const int64_t lse_idx = ((int64_t)b * p.T_q + (r < p.T_q ? r : 0)) * p.H + h;
+      if (merge) merge_partials(m_used, l, p.lse[lse_idx], inv, w_dep, lse_out);
       T* go = reinterpret_cast<T*>(p.o.ptr) + p.o.off(b, r, h);
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -470,16 +491,12 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         if (r < p.T_q) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint4 v4;
-            v4.x = Pack<T>::pack(__uint_as_float(ov[i * 8 + 0]) * inv, __uint_as_float(ov[i * 8 + 1]) * inv);
-            v4.y = Pack<T>::pack(__uint_as_float(ov[i * 8 + 2]) * inv, __uint_as_float(ov[i * 8 + 3]) * inv);
-            v4.z = Pack<T>::pack(__uint_as_float(ov[i * 8 + 4]) * inv, __uint_as_float(ov[i * 8 + 5]) * inv);
-            v4.w = Pack<T>::pack(__uint_as_float(ov[i * 8 + 6]) * inv, __uint_as_float(ov[i * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(go + q4 * 32 + i * 8) = v4;
+            uint4* dst = reinterpret_cast<uint4*>(go + q4 * 32 + i * 8);
+            *dst = merge ? pack8_blend<T>(ov + i * 8, inv, *dst, w_dep) : pack8_scaled<T>(ov + i * 8, inv);
           }
         }
       }
-      if (r < p.T_q) p.lse[((int64_t)b * p.T_q + r) * p.H + h] = m_used + log2f(l);
+      if (r < p.T_q) p.lse[lse_idx] = lse_out;
     }
   }
 

@@ -95,8 +95,12 @@ def test_causal_moda_d64(M, B, T, H, L, G, dt, scale):
 @pytest.mark.parametrize("mode", [mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE, mo.MODE_DEPTH_ONLY])
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("T,L,G", [(1, 1, 1), (70, 3, 1), (197, 11, 1), (128, 4, 4), (130, 2, 2), (96, 5, 8)])
-def test_all_modes(M, mode, D, T, L, G):
-    _run_case(M, mode, 2, T, 2, D, L, G, torch.bfloat16, None, seed=7 + T + D)
+@pytest.mark.parametrize("forced", [False, True], ids=["auto", "mma_sync"])
+def test_all_modes(M, mode, D, T, L, G, forced):
+    # "auto" evaluates own-position depth rows in the bandwidth kernels and merges the sequence
+    # part in the attention kernels' epilogue; "mma_sync" keeps everything in one attention kernel
+    _run_case(M, mode, 2, T, 2, D, L, G, torch.bfloat16, None, seed=7 + T + D,
+              path=(M.PATH_SIMT_MMA if forced else None))
 
 
 @pytest.mark.parametrize("mode", [mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE])
