@@ -57,8 +57,8 @@ typedef enum moda_dtype { MODA_BF16 = 0, MODA_FP16 = 1 } moda_dtype;
 typedef enum moda_path {
   MODA_PATH_AUTO = 0,    /* tcgen05 kernels where they apply (D = 128), otherwise the mma.sync
                             kernels; the bandwidth kernels for MODA_DEPTH_ONLY and for the
-                            own-position depth rows of MODA_CAUSAL / MODA_NONCAUSAL (whose
-                            partial result the attention kernel merges in its epilogue) */
+                            own-position depth rows of MODA_CAUSAL / MODA_NONCAUSAL at G = 1
+                            (whose partial result the attention kernel merges in its epilogue) */
   MODA_PATH_SIMT_MMA = 1,/* warp-level mma.sync kernels (every shape) */
   MODA_PATH_TCGEN05 = 2  /* tcgen05/TMEM/TMA kernels; MODA_ERR_UNSUPPORTED if they do not apply */
 } moda_path;

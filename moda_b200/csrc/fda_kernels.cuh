@@ -39,6 +39,21 @@ __device__ __forceinline__ float cross4_max(float x) {
   return x;
 }
 
+// (b, t, h) of a flattened unit index; 32-bit division when the index fits (64-bit division
+// costs hundreds of clocks, which a unit with a few KB of depth rows does not hide).
+__device__ __forceinline__ void decode_unit(int64_t unit, int H, int T_kv, int& b, int& t, int& h) {
+  if (unit <= 0x7fffffffLL) {
+    const unsigned u = (unsigned)unit, uh = u / (unsigned)H;
+    h = (int)(u - uh * (unsigned)H);
+    b = (int)(uh / (unsigned)T_kv);
+    t = (int)(uh - (unsigned)b * (unsigned)T_kv);
+  } else {
+    h = (int)(unit % H);
+    t = (int)((unit / H) % T_kv);
+    b = (int)(unit / ((int64_t)H * T_kv));
+  }
+}
+
 // Lane layout: sub = lane & 7 picks the 16-byte chunks {sub, sub + 8, ...} of a row (CH = D/64
 // chunks per lane), grp = lane >> 3 picks which of the 4 rows of a pass the lane works on.
 
@@ -52,9 +67,8 @@ __global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Par
   const int64_t n_units = (int64_t)p.B * p.T_kv * p.H;
   const int64_t wstride = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < n_units; unit += wstride) {
-    const int h = (int)(unit % p.H);
-    const int t = (int)((unit / p.H) % p.T_kv);
-    const int b = (int)(unit / ((int64_t)p.H * p.T_kv));
+    int b, t, h;
+    decode_unit(unit, p.H, p.T_kv, b, t, h);
     const T* kb = reinterpret_cast<const T*>(p.kd.ptr) + p.kd.off(b, (int64_t)t * p.L, h);
     const T* vb = reinterpret_cast<const T*>(p.vd.ptr) + p.vd.off(b, (int64_t)t * p.L, h);
     for (int g = 0; g < p.G; ++g) {
@@ -78,6 +92,7 @@ __global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Par
 
       for (int l0 = 0; l0 < p.L; l0 += 16) {
         uint4 raw[4][CH];
+        uint4 vraw[4][1];                         // D = 64: the V rows travel with the K rows
         float s[4];
 #pragma unroll
         for (int ps = 0; ps < 4; ++ps) {          // all K loads of the block in flight together
@@ -86,6 +101,9 @@ __global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Par
           for (int c = 0; c < CH; ++c)
             raw[ps][c] = (key < p.L) ? *reinterpret_cast<const uint4*>(kb + (int64_t)key * p.kd.st + (sub + 8 * c) * 8)
                                      : make_uint4(0, 0, 0, 0);
+          if constexpr (CH == 1)
+            vraw[ps][0] = (key < p.L) ? *reinterpret_cast<const uint4*>(vb + (int64_t)key * p.vd.st + sub * 8)
+                                      : make_uint4(0, 0, 0, 0);
         }
         float bm = -INFINITY;
 #pragma unroll
@@ -111,13 +129,18 @@ __global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Par
         for (int c = 0; c < CH; ++c)
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[c][e] *= alpha;
+        if constexpr (CH == 1) {
 #pragma unroll
-        for (int ps = 0; ps < 4; ++ps) {          // V loads of the block
-          const int key = l0 + ps * 4 + grp;
+          for (int ps = 0; ps < 4; ++ps) raw[ps][0] = vraw[ps][0];
+        } else {
 #pragma unroll
-          for (int c = 0; c < CH; ++c)
-            raw[ps][c] = (key < p.L) ? *reinterpret_cast<const uint4*>(vb + (int64_t)key * p.vd.st + (sub + 8 * c) * 8)
-                                     : make_uint4(0, 0, 0, 0);
+          for (int ps = 0; ps < 4; ++ps) {          // V loads of the block
+            const int key = l0 + ps * 4 + grp;
+#pragma unroll
+            for (int c = 0; c < CH; ++c)
+              raw[ps][c] = (key < p.L) ? *reinterpret_cast<const uint4*>(vb + (int64_t)key * p.vd.st + (sub + 8 * c) * 8)
+                                       : make_uint4(0, 0, 0, 0);
+          }
         }
 #pragma unroll
         for (int ps = 0; ps < 4; ++ps) {
@@ -157,9 +180,8 @@ __global__ void __launch_bounds__(128, (G == 1) ? 3 : 2) bwd_kernel(const __grid
   const int64_t n_units = (int64_t)p.B * p.T_kv * p.H;
   const int64_t wstride = (int64_t)gridDim.x * (blockDim.x >> 5);
   for (int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < n_units; unit += wstride) {
-    const int h = (int)(unit % p.H);
-    const int t = (int)((unit / p.H) % p.T_kv);
-    const int b = (int)(unit / ((int64_t)p.H * p.T_kv));
+    int b, t, h;
+    decode_unit(unit, p.H, p.T_kv, b, t, h);
     const T* kb = reinterpret_cast<const T*>(p.kd.ptr) + p.kd.off(b, (int64_t)t * p.L, h);
     const T* vb = reinterpret_cast<const T*>(p.vd.ptr) + p.vd.off(b, (int64_t)t * p.L, h);
     T* dkb = reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, (int64_t)t * p.L, h);

@@ -149,14 +149,17 @@ bool use_fda(const moda_problem* pr, bool is_bwd) {
   return !is_bwd || fda::bwd_supported(pr->G, pr->D);
 }
 
-// Own-position depth (parallel_moda, causal or not) as two launches: a query's depth keys are the
-// L rows of its own position, so that part of the softmax is the depth-only operator and runs at
-// HBM rate in the bandwidth kernels; the attention kernels then run on the sequence keys alone
-// and fold their part into the stored partial in the epilogue (Params::merge_depth).  Evaluating
-// those L keys inside 128-column attention tiles instead multiplies each query row against the
-// depth rows of every other position of its tile.
+// Own-position depth (parallel_moda, causal or not) with one query row per position (G = 1) as
+// two launches: a query's depth keys are the L rows of its own position, so that part of the
+// softmax is the depth-only operator and runs at HBM rate in the bandwidth kernels; the attention
+// kernels then run on the sequence keys alone and fold their part into the stored partial in the
+// epilogue (Params::merge_depth).  Inside the attention kernels a 128-row query tile at G = 1
+// spans 128 positions and has to multiply against 128 L depth columns of which each row uses L
+// (L extra key tiles per query tile; at T = 197, L = 11 that is 11 tiles beside 2 sequence
+// tiles).  With G = 4 the tile spans 32 positions, the extra tiles are a small share of the
+// sequence tiles, and one launch is faster (measured at T = 4096, L = 24: 0.30 ms against 0.45).
 bool split_depth(const moda_problem* pr, bool is_bwd) {
-  if (pr->path != MODA_PATH_AUTO || pr->L <= 0) return false;
+  if (pr->path != MODA_PATH_AUTO || pr->L <= 0 || pr->G != 1) return false;
   if (pr->mode != MODA_CAUSAL && pr->mode != MODA_NONCAUSAL) return false;
   return !is_bwd || fda::bwd_supported(pr->G, pr->D);
 }

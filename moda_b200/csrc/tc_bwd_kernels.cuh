@@ -698,15 +698,36 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
 // Eight softmax / store warps: warp w and warp w + 4 share TMEM lanes 32 (w & 3) .. + 31 (key
 // rows); warps 0-3 take query columns [0,32) of the scores and stage dVd, warps 4-7 take query
 // columns [32,64) and stage dKd.
-// grid (ceil(T_q / 64), H, B), 320 threads.  TMEM (512 columns): stage s at [128 s, 128 s + 64)
+// Persistent: one CTA per SM walks the (64-row block, h, b) list with a stride of the grid, so
+// the TMEM allocation and barrier set-up are paid once per SM and the key tiles of the next
+// block are already on their way while the current one finishes; only Q, dO and the row
+// statistics (single-buffered) wait for the previous block's last update MMAs.
+// grid (min(blocks, SMs)), 320 threads.  TMEM (512 columns): stage s at [128 s, 128 s + 64)
 // S^T / P^T and [128 s + 64, 128 s + 128) dP^T / dS^T (the packed 16-bit P^T / dS^T of query
 // columns 32 g .. + 31 sit in the first 16 columns of that group's 32 fp32 columns);
 // [256,384) dVd, [384,512) dKd.
-enum DgBar : int { kDgRes = 0, kDgFull0 = 1, kDgEmpty0 = 3, kDgS0 = 5, kDgP0 = 7, kDgU = 9, kDgE = 10, kDgCount = 11 };
+enum DgBar : int { kDgRes = 0, kDgFull0 = 1, kDgEmpty0 = 3, kDgS0 = 5, kDgP0 = 7, kDgU = 9, kDgE = 10, kDgQFree = 11, kDgCount = 12 };
 constexpr uint32_t kDgOutOff = 2 * kStepTile + 1024 + 2 * 2 * kTileBytes;      // {dVd tile, dKd tile} staging
 constexpr uint32_t kDgSmem = kDgOutOff + 2 * kTileBytes + 128;
 struct DgOutMaps { CUtensorMap dkd, dvd; };                                     // 32-row boxes
 constexpr int kDgThreads = 320;                                                 // 8 softmax/store warps, MMA warp, TMA warp
+
+// One 64-row query block of the depth-gradient kernel.
+struct DgBlock { int q0, h, b, k_lo, k_hi, n; int64_t stat_base; };
+__device__ __forceinline__ DgBlock dg_block(const Params& p, int idx, int n_xb, int T_qp) {
+  DgBlock k;
+  const int xb = idx % n_xb, hb = idx / n_xb;
+  k.h = hb % p.H;
+  k.b = hb / p.H;
+  k.q0 = xb * kStep;
+  const int r_last = min(k.q0 + kStep, p.T_q) - 1;
+  int tmp;
+  dep_interval(p, k.q0, k.k_lo, tmp);
+  dep_interval(p, r_last, tmp, k.k_hi);
+  k.n = (k.k_hi - k.k_lo + kBN - 1) / kBN;              // key tiles of 128
+  k.stat_base = ((int64_t)k.b * p.H + k.h) * T_qp;
+  return k;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kDgThreads, 1)
@@ -724,20 +745,15 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
   const uint32_t ctl_off = kDgOutOff + 2 * kTileBytes;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 100);
-  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 104);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 104);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 108);
+  volatile int* drain_flag = reinterpret_cast<volatile int*>(gctl + 112);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
 
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int q0 = (int)blockIdx.x * kStep;
-  const int r_last = min(q0 + kStep, p.T_q) - 1;
-  int k_lo, k_hi, tmp;
-  dep_interval(p, q0, k_lo, tmp);
-  dep_interval(p, r_last, tmp, k_hi);
-  const int n = (k_hi - k_lo + kBN - 1) / kBN;          // key tiles of 128
+  const int n_xb = (p.T_q + kStep - 1) / kStep;
+  const int total = n_xb * p.H * p.B;                   // 64-row blocks; this CTA takes blockIdx.x, + gridDim.x, ...
 
   if (tid == 0) {
     mbar_init(bars + 8 * kDgRes, 1);
@@ -749,13 +765,14 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
     }
     mbar_init(bars + 8 * kDgU, 1);
     mbar_init(bars + 8 * kDgE, 256);
+    mbar_init(bars + 8 * kDgQFree, 1);
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
-    tmem_alloc(bars + 96, 512);
+    tmem_alloc(bars + 104, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -764,80 +781,103 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_dV = tmem + 256, tmem_dK = tmem + 384;   // score stage s: tmem + 128 s (+ 64 for dP^T)
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
-  const int64_t stat_base = ((int64_t)b * p.H + h) * T_qp;
 
+  // Every role walks the same blocks in the same order; g counts key tiles and kb blocks since the
+  // CTA started, and all slot / stage / phase choices derive from them.
   if (warp == 9) {
     // ---------------------------------------------------------------- TMA warp
-    if (n > 0) {
-      if (elect_one()) {
-        prefetch_map(&maps.q); prefetch_map(&maps.dout); prefetch_map(&maps.kd); prefetch_map(&maps.vd);
-        mbar_expect_tx(bars + 8 * kDgRes, 2 * kStepTile + 512);
-        tma_load_4d(sQ, &maps.q, bars + 8 * kDgRes, 0, h, q0, b);
-        tma_load_4d(sQ + kStepHalf, &maps.q, bars + 8 * kDgRes, 64, h, q0, b);
-        tma_load_4d(sDO, &maps.dout, bars + 8 * kDgRes, 0, h, q0, b);
-        tma_load_4d(sDO + kStepHalf, &maps.dout, bars + 8 * kDgRes, 64, h, q0, b);
-        bulk_load(sStat, lse_t + stat_base + q0, 256, bars + 8 * kDgRes);
-        bulk_load(sStat + 256, delta_t + stat_base + q0, 256, bars + 8 * kDgRes);
-      }
-      __syncwarp();
-      bool ok = true;
-      int issued = 0;
-      for (int i = 0; ok && i < n; ++i) {
-        const uint32_t slot = i & 1;
-        if (i >= 2 && !(ok = mbar_wait(bars + 8 * (kDgEmpty0 + slot), ((i >> 1) - 1) & 1, abort_flag, kDgEmpty0 + slot))) break;
-        const int row = k_lo + i * kBN;
+    if (elect_one()) { prefetch_map(&maps.q); prefetch_map(&maps.dout); prefetch_map(&maps.kd); prefetch_map(&maps.vd); }
+    __syncwarp();
+    bool ok = true;
+    int g = 0, kb = 0;
+    int issued = 0, res_kb = -1;                        // key tiles / block loads issued so far
+    for (int idx = blockIdx.x; ok && idx < total; idx += gridDim.x) {
+      const DgBlock k = dg_block(p, idx, n_xb, T_qp);
+      if (k.n <= 0) continue;
+      auto load_tile = [&](int i) -> bool {
+        const int gi = g + i;
+        const uint32_t slot = gi & 1;
+        if (gi >= 2 && !mbar_wait(bars + 8 * (kDgEmpty0 + slot), ((gi >> 1) - 1) & 1, abort_flag, kDgEmpty0 + slot)) return false;
+        const int row = k.k_lo + i * kBN;
         const uint32_t dst = sKV + slot * 2 * kTileBytes, bar = bars + 8 * (kDgFull0 + slot);
         if (elect_one()) {
           mbar_expect_tx(bar, 2 * kTileBytes);
-          tma_load_4d(dst, &maps.kd, bar, 0, h, row, b);
-          tma_load_4d(dst + kHalfBytes, &maps.kd, bar, 64, h, row, b);
-          tma_load_4d(dst + kTileBytes, &maps.vd, bar, 0, h, row, b);
-          tma_load_4d(dst + kTileBytes + kHalfBytes, &maps.vd, bar, 64, h, row, b);
+          tma_load_4d(dst, &maps.kd, bar, 0, k.h, row, k.b);
+          tma_load_4d(dst + kHalfBytes, &maps.kd, bar, 64, k.h, row, k.b);
+          tma_load_4d(dst + kTileBytes, &maps.vd, bar, 0, k.h, row, k.b);
+          tma_load_4d(dst + kTileBytes + kHalfBytes, &maps.vd, bar, 64, k.h, row, k.b);
         }
         __syncwarp();
-        issued = i + 1;
+        issued = gi + 1;
+        return true;
+      };
+      // the first two key tiles only need free slots; Q, dO and the row statistics replace the
+      // previous block's, which its last update MMAs still read
+      int i = 0;
+      for (; ok && i < min(k.n, 2); ++i) ok = load_tile(i);
+      if (!ok) break;
+      if (kb >= 1 && !(ok = mbar_wait(bars + 8 * kDgQFree, (kb - 1) & 1, abort_flag, kDgQFree))) break;
+      if (elect_one()) {
+        mbar_expect_tx(bars + 8 * kDgRes, 2 * kStepTile + 512);
+        tma_load_4d(sQ, &maps.q, bars + 8 * kDgRes, 0, k.h, k.q0, k.b);
+        tma_load_4d(sQ + kStepHalf, &maps.q, bars + 8 * kDgRes, 64, k.h, k.q0, k.b);
+        tma_load_4d(sDO, &maps.dout, bars + 8 * kDgRes, 0, k.h, k.q0, k.b);
+        tma_load_4d(sDO + kStepHalf, &maps.dout, bars + 8 * kDgRes, 64, k.h, k.q0, k.b);
+        bulk_load(sStat, lse_t + k.stat_base + k.q0, 256, bars + 8 * kDgRes);
+        bulk_load(sStat + 256, delta_t + k.stat_base + k.q0, 256, bars + 8 * kDgRes);
       }
-      if (!ok) {
-        mbar_wait(bars + 8 * kDgRes, 0, drain_flag, kDgRes);
-        for (int i = max(0, issued - 2); i < issued; ++i)
-          mbar_wait(bars + 8 * (kDgFull0 + (i & 1)), (i >> 1) & 1, drain_flag, kDgFull0 + (i & 1));
-      }
+      __syncwarp();
+      res_kb = kb;
+      for (; ok && i < k.n; ++i) ok = load_tile(i);
+      if (!ok) break;
+      g += k.n;
+      ++kb;
+    }
+    if (!ok) {   // let what is in flight land before the CTA's smem goes
+      if (res_kb >= 0) mbar_wait(bars + 8 * kDgRes, res_kb & 1, drain_flag, kDgRes);
+      for (int gi = max(0, issued - 2); gi < issued; ++gi)
+        mbar_wait(bars + 8 * (kDgFull0 + (gi & 1)), (gi >> 1) & 1, drain_flag, kDgFull0 + (gi & 1));
     }
   } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA warp
-    if (n > 0) {
-      constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
-      const uint64_t dq_k = desc_kmajor(sQ), ddo_k = desc_kmajor(sDO);
-      const uint64_t dq_mn = desc_mnmajor(sQ, kStepHalf), ddo_mn = desc_mnmajor(sDO, kStepHalf);
-      // scores of tile j into stage j & 1; the updates that read that stage last (tile j - 2) were
-      // issued before, and the pipe runs in issue order
-      auto scores = [&](int j) -> bool {
-        const uint32_t slot = j & 1;
-        if (!mbar_wait(bars + 8 * (kDgFull0 + slot), (j >> 1) & 1, abort_flag, kDgFull0 + slot)) return false;
-        tc_fence_after();
-        const uint64_t dK = desc_kmajor(sKV + slot * 2 * kTileBytes), dV = desc_kmajor(sKV + slot * 2 * kTileBytes + kTileBytes);
-        const uint32_t tS = tmem + slot * 128, tP = tS + 64;
-        if (elect_one()) {
+    constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
+    constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+    const uint64_t dq_k = desc_kmajor(sQ), ddo_k = desc_kmajor(sDO);
+    const uint64_t dq_mn = desc_mnmajor(sQ, kStepHalf), ddo_mn = desc_mnmajor(sDO, kStepHalf);
+    // scores of tile gj into stage gj & 1; the updates that read that stage last (tile gj - 2) were
+    // issued before, and the pipe runs in issue order
+    auto scores = [&](int gj) -> bool {
+      const uint32_t slot = gj & 1;
+      if (!mbar_wait(bars + 8 * (kDgFull0 + slot), (gj >> 1) & 1, abort_flag, kDgFull0 + slot)) return false;
+      tc_fence_after();
+      const uint64_t dK = desc_kmajor(sKV + slot * 2 * kTileBytes), dV = desc_kmajor(sKV + slot * 2 * kTileBytes + kTileBytes);
+      const uint32_t tS = tmem + slot * 128, tP = tS + 64;
+      if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-            mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-          }
-          tc_commit(bars + 8 * (kDgS0 + slot));
-          tc_commit(bars + 8 * (kDgEmpty0 + slot));      // Kd/Vd tile j has been read
+        for (int kk = 0; kk < 8; ++kk) {
+          mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+          mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
         }
-        __syncwarp();
-        return true;
-      };
-      bool ok = mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes);
-      if (ok) ok = scores(0);
-      for (int i = 0; ok && i < n; ++i) {
-        if (i + 1 < n && !(ok = scores(i + 1))) break;
-        if (!(ok = mbar_wait(bars + 8 * (kDgP0 + (i & 1)), (i >> 1) & 1, abort_flag, kDgP0 + (i & 1)))) break;   // P^T, dS^T written
-        if (i >= 1 && !(ok = mbar_wait(bars + 8 * kDgE, (i - 1) & 1, abort_flag, kDgE))) break;   // accumulators of tile i-1 read
+        tc_commit(bars + 8 * (kDgS0 + slot));
+        tc_commit(bars + 8 * (kDgEmpty0 + slot));      // Kd/Vd tile gj has been read
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = true;
+    int g = 0, kb = 0;
+    for (int idx = blockIdx.x; ok && idx < total; idx += gridDim.x) {
+      const DgBlock k = dg_block(p, idx, n_xb, T_qp);
+      if (k.n <= 0) continue;
+      if (!(ok = mbar_wait(bars + 8 * kDgRes, kb & 1, abort_flag, kDgRes))) break;
+      if (!(ok = scores(g))) break;
+      for (int i = 0; ok && i < k.n; ++i) {
+        const int gi = g + i;
+        if (i + 1 < k.n && !(ok = scores(gi + 1))) break;
+        if (!(ok = mbar_wait(bars + 8 * (kDgP0 + (gi & 1)), (gi >> 1) & 1, abort_flag, kDgP0 + (gi & 1)))) break;   // P^T, dS^T written
+        if (gi >= 1 && !(ok = mbar_wait(bars + 8 * kDgE, (gi - 1) & 1, abort_flag, kDgE))) break;   // accumulators of tile gi-1 read
         tc_fence_after();
-        const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
+        const uint32_t tS = tmem + (gi & 1) * 128, tP = tS + 64;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
@@ -846,9 +886,12 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
             mma_ts(tmem_dK, tP + acol, desc_add(dq_mn, kk * 2048), idesc_t, kk > 0);
           }
           tc_commit(bars + 8 * kDgU);
+          if (i + 1 == k.n) tc_commit(bars + 8 * kDgQFree);   // the block's Q, dO, statistics are done with
         }
         __syncwarp();
       }
+      g += k.n;
+      ++kb;
     }
   } else {
     // ---------------------------------------------------------------- softmax / store warps
@@ -856,112 +899,121 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
     const int row = wq * 32 + lane;                   // key row of the tile == TMEM lane
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const float c = p.scale_log2;
+    bool ok = true;
+    int g = 0, kb = 0;
+    for (int idx = blockIdx.x; ok && idx < total; idx += gridDim.x) {
+      const DgBlock k = dg_block(p, idx, n_xb, T_qp);
+      if (k.n <= 0) continue;
 
-    // this warp's 32 query columns of P^T and dS^T of tile j, over its scores (stage j & 1)
-    auto softmax = [&](int j) -> bool {
-      const int key = k_lo + j * kBN + row;
-      int jlo = 0, jn = 0;                            // query rows [q0 + jlo, q0 + jlo + jn) see this key
-      if (key < k_hi) {
-        const int tp = key / p.L;
-        const int rlo = tp * p.G;
-        const int rhi = ((p.mode == kChunkVisible) ? min((tp / p.Cb + 1) * p.Cb, p.T_kv) : tp + 1) * p.G;
-        jlo = rlo - q0 - 32 * wg;
-        jn = rhi - rlo;
-      }
-      if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kDgS0 + (j & 1)), (j >> 1) & 1, abort_flag, kDgS0 + (j & 1)))) return false;
-      tc_fence_after();
-      const uint32_t tS = tmem + (j & 1) * 128 + lane_addr, tP = tS + 64;
-      const float4* st4 = reinterpret_cast<const float4*>(smem_raw + 2 * kStepTile) + 8 * wg;
-      uint32_t su[32], du[32];
-      tmem_ld32<0>(tS + 32 * wg, su);
-      tmem_ld32<0>(tP + 32 * wg, du);
-      tmem_wait_ld();
-      float pr[32], dd[32];
-#pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4) {
-        const float4 l4 = st4[j4], d4 = st4[16 + j4];
-        pr[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 0]), c, -l4.x));
-        pr[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 1]), c, -l4.y));
-        pr[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 2]), c, -l4.z));
-        pr[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 3]), c, -l4.w));
-        dd[4 * j4 + 0] = __uint_as_float(du[4 * j4 + 0]) - d4.x;
-        dd[4 * j4 + 1] = __uint_as_float(du[4 * j4 + 1]) - d4.y;
-        dd[4 * j4 + 2] = __uint_as_float(du[4 * j4 + 2]) - d4.z;
-        dd[4 * j4 + 3] = __uint_as_float(du[4 * j4 + 3]) - d4.w;
-      }
-#pragma unroll
-      for (int jj = 0; jj < 32; ++jj) pr[jj] = ((unsigned)(jj - jlo) < (unsigned)jn) ? pr[jj] : 0.f;
-      uint32_t pp[16], pd[16];
-#pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
-        pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
-        pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
-      }
-      // 16-bit pairs over the first half of the warp's own fp32 columns (the other warpgroup may
-      // still be reading its columns): query columns 32 wg .. + 31 at TMEM columns 32 wg .. + 15
-      tmem_st16<0>(tS + 32 * wg, pp);
-      tmem_st16<0>(tP + 32 * wg, pd);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars + 8 * (kDgP0 + (j & 1)));
-      return true;
-    };
-
-    bool ok = n > 0;
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgRes, 0, abort_flag, kDgRes));   // stats landed
-    if (ok) ok = softmax(0);
-    for (int i = 0; ok && i < n; ++i) {
-      if (i + 1 < n && !(ok = softmax(i + 1))) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgU, i & 1, abort_flag, kDgU));
-      if (!ok) break;
-      tc_fence_after();
-      const int key0 = k_lo + i * kBN + wq * 32;           // first key row of this warp
-      const uint32_t tacc = (wg ? tmem_dK : tmem_dV) + lane_addr;
-      const float f = wg ? p.scale : 1.f;
-      if (key0 + 32 <= k_hi) {                             // every row of the warp is this block's
-        if (lane == 0) bulk_wait_read_all();               // this warp's previous store has read its rows
-        __syncwarp();
-        // staging = the TMA box layout: two [128 rows x 128 B] halves per tensor, 16-byte chunk c of
-        // row r at chunk c ^ (r & 7)
-        unsigned char* orow = smem_raw + kDgOutOff + wg * kTileBytes + row * 128;
-        uint32_t ov[128];
-        tmem_ld32<0>(tacc, ov);
-        tmem_ld32<32>(tacc + 32, ov);
-        tmem_ld32<64>(tacc + 64, ov);
-        tmem_ld32<96>(tacc + 96, ov);
+      // this warp's 32 query columns of P^T and dS^T of the block's tile i (tile g + i of the CTA),
+      // over its scores
+      auto softmax = [&](int i) -> bool {
+        const int gj = g + i;
+        const int key = k.k_lo + i * kBN + row;
+        int jlo = 0, jn = 0;                            // query rows [q0 + jlo, q0 + jlo + jn) see this key
+        if (key < k.k_hi) {
+          const int tp = key / p.L;
+          const int rlo = tp * p.G;
+          const int rhi = ((p.mode == kChunkVisible) ? min((tp / p.Cb + 1) * p.Cb, p.T_kv) : tp + 1) * p.G;
+          jlo = rlo - k.q0 - 32 * wg;
+          jn = rhi - rlo;
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (kDgS0 + (gj & 1)), (gj >> 1) & 1, abort_flag, kDgS0 + (gj & 1)))) return false;
+        tc_fence_after();
+        const uint32_t tS = tmem + (gj & 1) * 128 + lane_addr, tP = tS + 64;
+        const float4* st4 = reinterpret_cast<const float4*>(smem_raw + 2 * kStepTile) + 8 * wg;
+        uint32_t su[32], du[32];
+        tmem_ld32<0>(tS + 32 * wg, su);
+        tmem_ld32<0>(tP + 32 * wg, du);
         tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(bars + 8 * kDgE);                      // accumulator values are in registers
+        float pr[32], dd[32];
 #pragma unroll
-        for (int ch = 0; ch < 16; ++ch)
-          *reinterpret_cast<uint4*>(orow + (ch >> 3) * kHalfBytes + (((ch & 7) ^ (row & 7)) << 4)) = pack8_scaled<T>(ov + ch * 8, f);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t src = sOut + wg * kTileBytes + wq * 32 * 128;
-          const CUtensorMap* om = wg ? &omaps.dkd : &omaps.dvd;
-          tma_store_4d(om, src, 0, h, key0, b);
-          tma_store_4d(om, src + kHalfBytes, 64, h, key0, b);
-          bulk_commit();
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 l4 = st4[j4], d4 = st4[16 + j4];
+          pr[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 0]), c, -l4.x));
+          pr[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 1]), c, -l4.y));
+          pr[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 2]), c, -l4.z));
+          pr[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 3]), c, -l4.w));
+          dd[4 * j4 + 0] = __uint_as_float(du[4 * j4 + 0]) - d4.x;
+          dd[4 * j4 + 1] = __uint_as_float(du[4 * j4 + 1]) - d4.y;
+          dd[4 * j4 + 2] = __uint_as_float(du[4 * j4 + 2]) - d4.z;
+          dd[4 * j4 + 3] = __uint_as_float(du[4 * j4 + 3]) - d4.w;
         }
-        __syncwarp();
-      } else {
-        const int key = key0 + lane;
-        const bool valid = key < k_hi;
-        T* gout = wg ? reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, key, h) : reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(b, key, h);
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint32_t ov[32];
-          tmem_ld32<0>(tacc + q4 * 32, ov);
+        for (int jj = 0; jj < 32; ++jj) pr[jj] = ((unsigned)(jj - jlo) < (unsigned)jn) ? pr[jj] : 0.f;
+        uint32_t pp[16], pd[16];
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj) {
+          pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
+          pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
+        }
+        // 16-bit pairs over the first half of the warp's own fp32 columns (the other warpgroup may
+        // still be reading its columns): query columns 32 wg .. + 31 at TMEM columns 32 wg .. + 15
+        tmem_st16<0>(tS + 32 * wg, pp);
+        tmem_st16<0>(tP + 32 * wg, pd);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bars + 8 * (kDgP0 + (gj & 1)));
+        return true;
+      };
+
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgRes, kb & 1, abort_flag, kDgRes));   // statistics landed
+      if (ok) ok = softmax(0);
+      for (int i = 0; ok && i < k.n; ++i) {
+        if (i + 1 < k.n && !(ok = softmax(i + 1))) break;
+        ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kDgU, (g + i) & 1, abort_flag, kDgU));
+        if (!ok) break;
+        tc_fence_after();
+        const int key0 = k.k_lo + i * kBN + wq * 32;         // first key row of this warp
+        const uint32_t tacc = (wg ? tmem_dK : tmem_dV) + lane_addr;
+        const float f = wg ? p.scale : 1.f;
+        if (key0 + 32 <= k.k_hi) {                           // every row of the warp is this block's
+          if (lane == 0) bulk_wait_read_all();               // this warp's previous store has read its rows
+          __syncwarp();
+          // staging = the TMA box layout: two [128 rows x 128 B] halves per tensor, 16-byte chunk c of
+          // row r at chunk c ^ (r & 7)
+          unsigned char* orow = smem_raw + kDgOutOff + wg * kTileBytes + row * 128;
+          uint32_t ov[128];
+          tmem_ld32<0>(tacc, ov);
+          tmem_ld32<32>(tacc + 32, ov);
+          tmem_ld32<64>(tacc + 64, ov);
+          tmem_ld32<96>(tacc + 96, ov);
           tmem_wait_ld();
-          if (valid) {
+          tc_fence_before();
+          mbar_arrive(bars + 8 * kDgE);                      // accumulator values are in registers
 #pragma unroll
-            for (int e = 0; e < 4; ++e) *reinterpret_cast<uint4*>(gout + q4 * 32 + e * 8) = pack8_scaled<T>(ov + e * 8, f);
+          for (int ch = 0; ch < 16; ++ch)
+            *reinterpret_cast<uint4*>(orow + (ch >> 3) * kHalfBytes + (((ch & 7) ^ (row & 7)) << 4)) = pack8_scaled<T>(ov + ch * 8, f);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t src = sOut + wg * kTileBytes + wq * 32 * 128;
+            const CUtensorMap* om = wg ? &omaps.dkd : &omaps.dvd;
+            tma_store_4d(om, src, 0, k.h, key0, k.b);
+            tma_store_4d(om, src + kHalfBytes, 64, k.h, key0, k.b);
+            bulk_commit();
           }
+          __syncwarp();
+        } else {
+          const int key = key0 + lane;
+          const bool valid = key < k.k_hi;
+          T* gout = wg ? reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(k.b, key, k.h) : reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(k.b, key, k.h);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint32_t ov[32];
+            tmem_ld32<0>(tacc + q4 * 32, ov);
+            tmem_wait_ld();
+            if (valid) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) *reinterpret_cast<uint4*>(gout + q4 * 32 + e * 8) = pack8_scaled<T>(ov + e * 8, f);
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(bars + 8 * kDgE);
         }
-        tc_fence_before();
-        mbar_arrive(bars + 8 * kDgE);
       }
+      g += k.n;
+      ++kb;
     }
     if (lane == 0) bulk_wait_read_all();                   // staged rows are read before the CTA's smem goes
   }
@@ -1080,7 +1132,14 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
     if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
     *launches += 1;
     if (dg) {
-      dim3 ggrid((p.T_q + kStep - 1) / kStep, p.H, p.B);
+      int dev = 0, n_sm = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) {
+        *cuda_err = (int)cudaGetLastError();
+        return MODA_ERR_CUDA;
+      }
+      const int64_t n_blocks = (int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B;
+      if (n_blocks > 0x7fffffff) return MODA_ERR_UNSUPPORTED;
+      dim3 ggrid((unsigned)(n_blocks < n_sm ? n_blocks : n_sm));
       auto glaunch = [&](auto kern) -> cudaError_t {
         cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDgSmem);
         if (er != cudaSuccess) return er;
