@@ -263,6 +263,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fwd-only", action="store_true", help="time forward only (exploration; not the headline)")
+    ap.add_argument("--fwd-variant", type=int, default=0, help="bring-up switch of the forward kernel (exploration)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     mode, B, T, Hkv, G, D, L = wl
@@ -290,6 +291,8 @@ def main():
     from moda_b200 import _cabi
     from moda_b200.sharding import gather_units, partition_units
     M.set_kernel_path({"auto": M.PATH_AUTO, "simt": M.PATH_SIMT_MMA, "tcgen05": M.PATH_TCGEN05}[args.path])
+    if args.fwd_variant:
+        _cabi.load().moda_b200_debug_set(None, args.fwd_variant)
 
     n_units = B * Hkv
     units = partition_units(n_units, world, rank)

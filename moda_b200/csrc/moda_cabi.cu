@@ -13,6 +13,7 @@
 #include "tc_kernels.cuh"
 #include "tc_bwd_kernels.cuh"
 #include "tc_fwd2_kernel.cuh"
+#include "tc_fwd3_kernel.cuh"
 #endif
 
 namespace {
@@ -218,6 +219,27 @@ int resolve_path(const moda_problem* pr, bool is_bwd) {
   return ok ? MODA_PATH_TCGEN05 : MODA_PATH_SIMT_MMA;
 }
 
+#ifndef MODA_NO_TCGEN05
+int tc_forward(const Params& p, const moda_problem* prob, cudaStream_t st) {
+  // Three forwards exist.  tc::fwd3 (two 128-row query tiles per CTA, one CTA per SM, one MMA warp
+  // ordering the work of both tiles) is the fastest once its grid fills the GPU: config 4 forward
+  // 33.1 ms against 35.2 ms.  tc::fwd (one query tile per CTA, two CTAs per SM) has twice as many,
+  // smaller CTAs and serves the small problems.  tc::fwd2 (Q in TMEM, column-split softmax) is
+  // kept selectable: 36.8 ms.  Bring-up switch bits force one of them: 32, 128, 64.
+  const int variant = tc::debug_state().variant;
+  if (variant & 64) return tc::fwd2(p, prob, st, &g_last_launches, &g_last_cuda_error);
+  bool two_tiles = (variant & 128) != 0;
+  if (!(variant & (32 | 128))) {
+    int n_sm = 0;
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, prob->device) != cudaSuccess) n_sm = 0;
+    const int64_t n_cta = (int64_t)((p.T_q + 255) / 256) * p.H * p.B;
+    two_tiles = n_sm > 0 && n_cta >= n_sm;
+  }
+  if (two_tiles) return tc::fwd3(p, prob, st, &g_last_launches, &g_last_cuda_error);
+  return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+}
+#endif
+
 size_t delta_bytes(const moda_problem* pr) {
   const size_t n = (size_t)pr->B * pr->T_kv * pr->G * pr->H * sizeof(float);
   return (n + 255) & ~(size_t)255;
@@ -278,20 +300,14 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
                                           : fda_dispatch<__half>(p, prob->D, false, st)) return rc;
     p = sequence_part(p);
 #ifndef MODA_NO_TCGEN05
-    if (path == MODA_PATH_TCGEN05) return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+    if (path == MODA_PATH_TCGEN05) return tc_forward(p, prob, st);
 #endif
     return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)
                                     : simt_fwd_d<__half>(p, prob->D, st);
   }
 #ifndef MODA_NO_TCGEN05
   if (path == MODA_PATH_TCGEN05) {
-    // Two forwards exist.  Default: two CTAs per SM, each a simple QK -> softmax -> PV sequence
-    // (tc_kernels.cuh).  Alternative (debug variant bit 64): one CTA per SM with Q in TMEM and
-    // decoupled score / PV / TMA warps (tc_fwd2_kernel.cuh).  Measured on config 4 they take the
-    // same number of SM clocks per key tile (both are bound by the softmax warps), so the simpler
-    // one is the default.
-    if (tc::debug_state().variant & 64) return tc::fwd2(p, prob, st, &g_last_launches, &g_last_cuda_error);
-    return tc::fwd(p, prob, st, &g_last_launches, &g_last_cuda_error);
+    return tc_forward(p, prob, st);
   }
 #endif
   return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)

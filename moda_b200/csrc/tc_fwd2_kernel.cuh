@@ -53,7 +53,7 @@ __device__ __forceinline__ bool pair_exchange(volatile unsigned long long* xchg,
   atomicCAS(&g_tc_status, 0, (4 << 8));
   return false;
 }
-template <typename T>
+template <typename T, int kF2PolyEvery>
 __global__ void __launch_bounds__(kF2Threads, 1)
 fwd2_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd2Maps maps) {
   constexpr int R = kF2Ring;
@@ -244,24 +244,29 @@ fwd2_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd2Maps m
           s[k] = (col >= lo && col < hi) ? s[k] : -INFINITY;
         }
       }
-      float mx8[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) mx8[k] = s[k];
-#pragma unroll
-      for (int k = 8; k < 64; ++k) mx8[k & 7] = fmaxf(mx8[k & 7], s[k]);
+      // row maximum over own and partner columns: 8 chains of three-input max
+      float so_f[64];
       if (masked) {
         const int co = t0c + (half ^ 1) * 64;
 #pragma unroll
         for (int k = 0; k < 64; ++k) {
           const int col = co + k;
-          mx8[k & 7] = fmaxf(mx8[k & 7], (col >= lo && col < hi) ? __uint_as_float(so[k]) : -INFINITY);
+          so_f[k] = (col >= lo && col < hi) ? __uint_as_float(so[k]) : -INFINITY;
         }
       } else {
 #pragma unroll
-        for (int k = 0; k < 64; ++k) mx8[k & 7] = fmaxf(mx8[k & 7], __uint_as_float(so[k]));
+        for (int k = 0; k < 64; ++k) so_f[k] = __uint_as_float(so[k]);
       }
-      // (fmax is exact and order-independent, so both threads of the row get the same value)
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      float mx8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float m = fmaxf(s[j], so_f[j]);
+#pragma unroll
+        for (int k = 1; k < 8; ++k) m = fmax3(m, s[j + 8 * k], so_f[j + 8 * k]);
+        mx8[j] = m;
+      }
+      // (max is exact and order-independent, so both threads of the row get the same value)
+      const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
       const float m_new = fmaxf(m_used, mx * c);   // scale > 0 is required by this path
       float alpha = 1.f;
       bool grow = false;
@@ -272,16 +277,29 @@ fwd2_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd2Maps m
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       l *= alpha;
-      float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_sub, -m_sub);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t pk[32];
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
-        const float p0 = fast_exp2(fmaf(s[2 * k], c, -m_sub));
-        const float p1 = fast_exp2(fmaf(s[2 * k + 1], c, -m_sub));
-        sum8[k & 7] += p0 + p1;
+        const uint64_t x2 = ffma2(pack2(s[2 * k], s[2 * k + 1]), c2, nm2);
+        float p0, p1;
+        if (kF2PolyEvery > 0 && (k % (kF2PolyEvery > 0 ? kF2PolyEvery : 1)) == (kF2PolyEvery > 0 ? kF2PolyEvery : 1) - 1) {
+          unpack2(exp2x2_fma(x2), p0, p1);
+        } else {
+          float x0, x1;
+          unpack2(x2, x0, x1);
+          p0 = fast_exp2(x0);
+          p1 = fast_exp2(x1);
+        }
+        sum2[k & 3] = fadd2(sum2[k & 3], pack2(p0, p1));
         pk[k] = Pack<T>::pack(p0, p1);
       }
-      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+      {
+        float a0, a1;
+        unpack2(fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3])), a0, a1);
+        l += a0 + a1;
+      }
       // the P buffer was last read by PV(i-1), after which O is final through tile i-1
       if (i >= 1) {
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_::t0, (i - 1) & 1, abort_flag, B_::t0));
@@ -366,7 +384,7 @@ inline int fwd2(const Params& p, const moda_problem* pr, cudaStream_t st, int* l
     kern<<<grid, kF2Threads, kF2Smem, st>>>(p, maps);
     return cudaGetLastError();
   };
-  e = (pr->dtype == MODA_BF16) ? launch(fwd2_kernel<__nv_bfloat16>) : launch(fwd2_kernel<__half>);
+  e = (pr->dtype == MODA_BF16) ? launch(fwd2_kernel<__nv_bfloat16, 4>) : launch(fwd2_kernel<__half, 4>);
   if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
   *launches += 1;
   return MODA_OK;

@@ -184,6 +184,114 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[N]
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Packed fp32 pairs (sm_100 has two-wide fp32 FMA / ADD / MUL on 64-bit register pairs and a
+// three-input max): the softmax of a 128 x 128 block is bound by instruction issue and by the
+// 16-per-clock exp2 unit, so every fp32 instruction saved in it counts.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d;
+}
+
+// exp2 of two values on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; degree-4
+// polynomial for 2^f (relative error < 4e-6, far inside the 16-bit rounding of P); 2^n goes into
+// the exponent field.  Inputs below -126 (masked columns: -inf) are clamped and come out as 2^-126
+// times the polynomial, which the 16-bit rounding turns into 0.
+__device__ __forceinline__ uint64_t exp2x2_fma(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const uint64_t xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = pack2(12582912.f, 12582912.f);            // 1.5 * 2^23: low mantissa bits = round(x)
+  const uint64_t t2 = fadd2(xc, magic);
+  const uint64_t r2 = fadd2(t2, pack2(-12582912.f, -12582912.f));
+  const uint64_t f2 = ffma2(r2, pack2(-1.f, -1.f), xc);
+  uint64_t q = ffma2(pack2(0.009676037f, 0.009676037f), f2, pack2(0.055922035f, 0.055922035f));
+  q = ffma2(q, f2, pack2(0.24022107f, 0.24022107f));
+  q = ffma2(q, f2, pack2(0.6931210f, 0.6931210f));
+  q = ffma2(q, f2, pack2(1.0000001f, 1.0000001f));
+  float q0, q1, t0, t1;
+  unpack2(q, q0, q1);
+  unpack2(t2, t0, t1);
+  return pack2(__int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23)),
+               __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23)));
+}
+
+// One row's online-softmax step over the 128 scores of a key tile (register bits in su; thread =
+// query row).  Masks columns outside [lo, hi) when `masked`, takes the row maximum, keeps the old
+// reference maximum unless the new one is more than 2^8 larger (lazy rescale: alpha / grow tell
+// the caller to rescale O), and returns P = exp2(s * c - m) as 64 packed 16-bit pairs, with the
+// row sum added to l.  scale > 0 is required (the maximum is taken before scaling).
+template <typename T, int kPolyEvery>
+__device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, int c0, int lo, int hi, float c,
+                                               float& m_used, float& l, float& alpha, bool& grow, uint32_t (&pk)[64]) {
+  float s[128];
+#pragma unroll
+  for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
+  if (masked) {
+#pragma unroll
+    for (int i = 0; i < 128; ++i) {
+      const int col = c0 + i;
+      s[i] = (col >= lo && col < hi) ? s[i] : -INFINITY;
+    }
+  }
+  // row maximum: 8 independent chains of three-input max (a single running maximum would be a
+  // 128-deep dependent chain for the one warp this sub-partition has on the job)
+  float mx8[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float m = s[j];
+#pragma unroll
+    for (int k = 1; k + 1 < 16; k += 2) m = fmax3(m, s[j + 8 * k], s[j + 8 * (k + 1)]);
+    mx8[j] = fmaxf(m, s[j + 8 * 15]);
+  }
+  const float mx = fmaxf(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(fmax3(mx8[3], mx8[4], mx8[5]), mx8[6], mx8[7]));
+  const float m_new = fmaxf(m_used, mx * c);
+  alpha = 1.f;
+  grow = false;
+  if (m_new > m_used + 8.f) {        // also true for the first finite maximum (m_used = -inf)
+    alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+    grow = (m_used != -INFINITY);    // nothing accumulated yet => nothing to rescale
+    m_used = m_new;
+  }
+  const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+  l *= alpha;
+  const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_sub, -m_sub);
+  uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};   // bit pattern of (0.f, 0.f)
+  // One pair in kPolyEvery takes its two exponentials on the FMA pipe (exp2x2_fma) instead of
+  // the exp2 unit, whose 16 results per clock are the narrowest resource of this loop.
+#pragma unroll
+  for (int i = 0; i < 64; ++i) {
+    const uint64_t x2 = ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, nm2);
+    float p0, p1;
+    if (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery > 0 ? kPolyEvery : 1) - 1) {
+      unpack2(exp2x2_fma(x2), p0, p1);
+    } else {
+      float x0, x1;
+      unpack2(x2, x0, x1);
+      p0 = fast_exp2(x0);
+      p1 = fast_exp2(x1);
+    }
+    sum2[i & 3] = fadd2(sum2[i & 3], pack2(p0, p1));
+    pk[i] = Pack<T>::pack(p0, p1);
+  }
+  float a0, a1;
+  unpack2(fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3])), a0, a1);
+  l += a0 + a1;
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
 //   K-major operand  ([rows][64 elem] boxes, 128 B per row):   lbo = 16,   sbo = 1024
 //   MN-major operand ([k rows][64 elem] boxes, second 64-wide
@@ -397,47 +505,12 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         tmem_ld32<64>(tmem_S + lane_addr + 64, su);
         tmem_ld32<96>(tmem_S + lane_addr + 96, su);
         tmem_wait_ld();
-        float s[128];
-#pragma unroll
-        for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
         if (dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = s[i];
+          for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = __uint_as_float(su[i]);
         }
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            const int col = c0 + i;
-            s[i] = (col >= lo && col < hi) ? s[i] : -INFINITY;
-          }
-        }
-        // row maximum as a tree over 8 partial maxima (a single running maximum would be a
-        // 128-deep dependent chain for the one warp this sub-partition has on the job)
-        float mx8[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) mx8[i] = s[i];
-#pragma unroll
-        for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], s[i]);
-        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                               fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-        const float m_new = fmaxf(m_used, mx * c);   // scale > 0 is required by this path
-        // lazy rescale: keep the old reference maximum unless it is more than 2^8 too small
-        if (m_new > m_used + 8.f) {        // also true for the first finite maximum (m_used = -inf)
-          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
-          grow = (m_used != -INFINITY);    // nothing accumulated yet => nothing to rescale
-          m_used = m_new;
-        }
-        const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-        l *= alpha;
-        float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float p0 = fast_exp2(fmaf(s[2 * i], c, -m_sub));
-          const float p1 = fast_exp2(fmaf(s[2 * i + 1], c, -m_sub));
-          sum8[i & 7] += p0 + p1;
-          pk[i] = Pack<T>::pack(p0, p1);
-        }
-        l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+        // same arithmetic as fwd3_kernel, so that a result does not depend on which of the two ran
+        softmax_row128<T, 4>(su, masked, c0, lo, hi, c, m_used, l, alpha, grow, pk);
       }
       if (kPTmem) {
         tmem_st32<0>(tmem_S + lane_addr + 0, pk);

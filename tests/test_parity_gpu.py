@@ -303,15 +303,17 @@ def test_depth_only_paths_agree(M):
         assert max_abs(a.float(), b.float()) <= 2e-2
 
 
+@pytest.mark.parametrize("variant", [32, 64, 128], ids=["one_tile_two_ctas", "pipelined", "two_tiles"])
 @pytest.mark.parametrize("mode,T,L,G", [(mo.MODE_CAUSAL, 300, 5, 4), (mo.MODE_CHUNK_VISIBLE, 1000, 3, 4),
-                                        (mo.MODE_NONCAUSAL, 129, 2, 1), (mo.MODE_CAUSAL, 2048, 24, 4)])
-def test_tcgen05_pipelined_forward_variant(M, mode, T, L, G):
-    """The alternative forward (one CTA per SM, Q in TMEM, decoupled MMA warps), selected through
-    the library's bring-up switch; same parity bar as the default forward."""
-    import ctypes
+                                        (mo.MODE_NONCAUSAL, 129, 2, 1), (mo.MODE_CAUSAL, 2048, 24, 4),
+                                        (mo.MODE_CHUNK_VISIBLE, 96, 32, 4), (mo.MODE_CAUSAL, 1, 1, 1)])
+def test_tcgen05_forward_variants(M, mode, T, L, G, variant):
+    """Each tcgen05 forward forced through the library's bring-up switch (the default picks by grid
+    size): 32 = one query tile per CTA, two CTAs per SM; 64 = one CTA per SM with Q in TMEM and
+    decoupled MMA warps; 128 = two query tiles per CTA with one softmax warpgroup each."""
     from moda_b200 import _cabi
     lib = _cabi.load()
-    lib.moda_b200_debug_set(None, 64)
+    lib.moda_b200_debug_set(None, variant)
     try:
         _run_case(M, mode, 1, T, 2, 128, L, G, torch.bfloat16, None, seed=400 + T, path=M.PATH_TCGEN05, check_bwd=False)
         assert _cabi.device_status() == 0
