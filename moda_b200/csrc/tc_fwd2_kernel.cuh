@@ -277,28 +277,25 @@ fwd2_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd2Maps m
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       l *= alpha;
-      const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_sub, -m_sub);
-      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+      const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_sub, -m_sub);
+      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[32];
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
-        const uint64_t x2 = ffma2(pack2(s[2 * k], s[2 * k + 1]), c2, nm2);
-        float p0, p1;
+        const float2 x = __ffma2_rn(make_float2(s[2 * k], s[2 * k + 1]), c2, nm2);
+        float2 pp;
         if (kF2PolyEvery > 0 && (k % (kF2PolyEvery > 0 ? kF2PolyEvery : 1)) == (kF2PolyEvery > 0 ? kF2PolyEvery : 1) - 1) {
-          unpack2(exp2x2_fma(x2), p0, p1);
+          pp = exp2x2_fma(x);
         } else {
-          float x0, x1;
-          unpack2(x2, x0, x1);
-          p0 = fast_exp2(x0);
-          p1 = fast_exp2(x1);
+          pp.x = fast_exp2(x.x);
+          pp.y = fast_exp2(x.y);
         }
-        sum2[k & 3] = fadd2(sum2[k & 3], pack2(p0, p1));
-        pk[k] = Pack<T>::pack(p0, p1);
+        sum2[k & 3] = __fadd2_rn(sum2[k & 3], pp);
+        pk[k] = Pack<T>::pack(pp.x, pp.y);
       }
       {
-        float a0, a1;
-        unpack2(fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3])), a0, a1);
-        l += a0 + a1;
+        const float2 tot = __fadd2_rn(__fadd2_rn(sum2[0], sum2[1]), __fadd2_rn(sum2[2], sum2[3]));
+        l += tot.x + tot.y;
       }
       // the P buffer was last read by PV(i-1), after which O is final through tile i-1
       if (i >= 1) {

@@ -253,13 +253,22 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       // A depth tile holds the rows of several positions; a warp whose 32 query rows see none of
       // its columns contributes an all-zero P block and skips the scores altogether.
       const bool none = is_dep && __all_sync(0xffffffffu, (c0 + kBN <= lo) || (c0 >= hi));
+      if (none) {
+        uint32_t z[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) z[i] = 0u;
+        tmem_st32<0>(tmem_S + lane_addr + 0, z);
+        tmem_st32<32>(tmem_S + lane_addr + 32, z);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bars + 8 * (B_::p0 + a));
+        ++cnt;
+        continue;
+      }
       float alpha = 1.f;
       bool grow = false;
       uint32_t pk[64];
-      if (none) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) pk[i] = 0u;
-      } else {
+      {
         uint32_t su[128];
         tmem_ld32<0>(tmem_S + lane_addr + 0, su);
         tmem_ld32<32>(tmem_S + lane_addr + 32, su);

@@ -184,24 +184,9 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[N]
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Packed fp32 pairs (sm_100 has two-wide fp32 FMA / ADD / MUL on 64-bit register pairs and a
-// three-input max): the softmax of a 128 x 128 block is bound by instruction issue and by the
-// 16-per-clock exp2 unit, so every fp32 instruction saved in it counts.
-__device__ __forceinline__ uint64_t pack2(float a, float b) {
-  uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d;
-}
-__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
-  uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
-}
-__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
-  uint64_t d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d;
-}
+// Packed fp32 pairs (sm_100 has two-wide fp32 FMA / ADD / MUL on register pairs - the float2
+// intrinsics - and a three-input max): the softmax of a 128 x 128 block is bound by instruction
+// issue, so every fp32 instruction saved in it counts.
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d;
 }
@@ -209,31 +194,26 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 // exp2 of two values on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; degree-4
 // polynomial for 2^f (relative error < 4e-6, far inside the 16-bit rounding of P); 2^n goes into
 // the exponent field.  Inputs below -126 (masked columns: -inf) are clamped and come out as 2^-126
-// times the polynomial, which the 16-bit rounding turns into 0.
-__device__ __forceinline__ uint64_t exp2x2_fma(uint64_t x2) {
-  float x0, x1;
-  unpack2(x2, x0, x1);
-  const uint64_t xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const uint64_t magic = pack2(12582912.f, 12582912.f);            // 1.5 * 2^23: low mantissa bits = round(x)
-  const uint64_t t2 = fadd2(xc, magic);
-  const uint64_t r2 = fadd2(t2, pack2(-12582912.f, -12582912.f));
-  const uint64_t f2 = ffma2(r2, pack2(-1.f, -1.f), xc);
-  uint64_t q = ffma2(pack2(0.009676037f, 0.009676037f), f2, pack2(0.055922035f, 0.055922035f));
-  q = ffma2(q, f2, pack2(0.24022107f, 0.24022107f));
-  q = ffma2(q, f2, pack2(0.6931210f, 0.6931210f));
-  q = ffma2(q, f2, pack2(1.0000001f, 1.0000001f));
-  float q0, q1, t0, t1;
-  unpack2(q, q0, q1);
-  unpack2(t2, t0, t1);
-  return pack2(__int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23)),
-               __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23)));
+// times the polynomial, which the 16-bit rounding turns into 0 or the smallest normal.
+__device__ __forceinline__ float2 exp2x2_fma(float2 x) {
+  const float2 xc = make_float2(fmaxf(x.x, -126.f), fmaxf(x.y, -126.f));
+  const float2 t = __fadd2_rn(xc, make_float2(12582912.f, 12582912.f));   // 1.5 * 2^23: low mantissa bits = round(x)
+  const float2 r = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(r, make_float2(-1.f, -1.f), xc);
+  float2 q = __ffma2_rn(make_float2(0.009676037f, 0.009676037f), f, make_float2(0.055922035f, 0.055922035f));
+  q = __ffma2_rn(q, f, make_float2(0.24022107f, 0.24022107f));
+  q = __ffma2_rn(q, f, make_float2(0.6931210f, 0.6931210f));
+  q = __ffma2_rn(q, f, make_float2(1.0000001f, 1.0000001f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23)));
 }
 
 // One row's online-softmax step over the 128 scores of a key tile (register bits in su; thread =
 // query row).  Masks columns outside [lo, hi) when `masked`, takes the row maximum, keeps the old
 // reference maximum unless the new one is more than 2^8 larger (lazy rescale: alpha / grow tell
 // the caller to rescale O), and returns P = exp2(s * c - m) as 64 packed 16-bit pairs, with the
-// row sum added to l.  scale > 0 is required (the maximum is taken before scaling).
+// row sum added to l.  scale > 0 is required (the maximum is taken before scaling).  One pair in
+// kPolyEvery takes its two exponentials on the FMA pipe (exp2x2_fma) instead of the exp2 unit.
 template <typename T, int kPolyEvery>
 __device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, int c0, int lo, int hi, float c,
                                                float& m_used, float& l, float& alpha, bool& grow, uint32_t (&pk)[64]) {
@@ -268,28 +248,23 @@ __device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool m
   }
   const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
   l *= alpha;
-  const uint64_t c2 = pack2(c, c), nm2 = pack2(-m_sub, -m_sub);
-  uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};   // bit pattern of (0.f, 0.f)
-  // One pair in kPolyEvery takes its two exponentials on the FMA pipe (exp2x2_fma) instead of
-  // the exp2 unit, whose 16 results per clock are the narrowest resource of this loop.
+  const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_sub, -m_sub);
+  float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
   for (int i = 0; i < 64; ++i) {
-    const uint64_t x2 = ffma2(pack2(s[2 * i], s[2 * i + 1]), c2, nm2);
-    float p0, p1;
+    const float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), c2, nm2);
+    float2 pp;
     if (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery > 0 ? kPolyEvery : 1) - 1) {
-      unpack2(exp2x2_fma(x2), p0, p1);
+      pp = exp2x2_fma(x);
     } else {
-      float x0, x1;
-      unpack2(x2, x0, x1);
-      p0 = fast_exp2(x0);
-      p1 = fast_exp2(x1);
+      pp.x = fast_exp2(x.x);
+      pp.y = fast_exp2(x.y);
     }
-    sum2[i & 3] = fadd2(sum2[i & 3], pack2(p0, p1));
-    pk[i] = Pack<T>::pack(p0, p1);
+    sum2[i & 3] = __fadd2_rn(sum2[i & 3], pp);
+    pk[i] = Pack<T>::pack(pp.x, pp.y);
   }
-  float a0, a1;
-  unpack2(fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3])), a0, a1);
-  l += a0 + a1;
+  const float2 tot = __fadd2_rn(__fadd2_rn(sum2[0], sum2[1]), __fadd2_rn(sum2[2], sum2[3]));
+  l += tot.x + tot.y;
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
