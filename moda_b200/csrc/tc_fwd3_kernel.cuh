@@ -212,10 +212,15 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         f3_step(pl, s, part, dep, row);
         part_next = 0;
         if (s + 1 < pl.n) f3_step(pl, s + 1, part_next, dep, row);
+        // a tile that joins at s+1 without taking part in s (alternating depth steps) has a free
+        // score block: its scores go ahead of this step's PVs and run under the other tile's softmax
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+          if (ok && ((part_next & ~part) & (1 << a))) ok = qk(a, s + 1);
 #pragma unroll
         for (int a = 0; a < 2; ++a) {
           if (ok && (part & (1 << a))) ok = pv(a, s, (part >> (a + 1)) == 0);
-          if (ok && (part_next & (1 << a))) ok = qk(a, s + 1);
+          if (ok && ((part_next & part) & (1 << a))) ok = qk(a, s + 1);
         }
       }
       if (ok) {
