@@ -79,7 +79,10 @@ template <> struct Pack<__nv_bfloat16> {
   // round to nearest with ties away from zero in magnitude (a tie is one fp32 value in 65536, and
   // the difference to ties-to-even is then one bf16 ulp).
   static __device__ __forceinline__ uint32_t pack_finite(float a, float b) {
-    return __byte_perm(__float_as_uint(a) + 0x8000u, __float_as_uint(b) + 0x8000u, 0x7632);
+    uint32_t ua, ub;   // the adds as integer multiply-adds: they issue on the FMA pipe, which has room
+    asm("mad.lo.u32 %0, %1, 1, 0x8000;" : "=r"(ua) : "r"(__float_as_uint(a)));
+    asm("mad.lo.u32 %0, %1, 1, 0x8000;" : "=r"(ub) : "r"(__float_as_uint(b)));
+    return __byte_perm(ua, ub, 0x7632);
   }
 };
 template <> struct Pack<__half> {
