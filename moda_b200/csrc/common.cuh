@@ -73,17 +73,6 @@ template <> struct Pack<__nv_bfloat16> {
   static __device__ __forceinline__ float2 unpack(uint32_t u) {
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
   }
-  // For finite values in the softmax inner loops (P, dS): the conversion instruction shares the
-  // 16-lane unit of exp2, where it costs a warp 8 clocks per pair - measured as 40 % of the exp
-  // loop of a 128-column row.  Two integer adds and a byte permute on the ALU do the same job:
-  // round to nearest with ties away from zero in magnitude (a tie is one fp32 value in 65536, and
-  // the difference to ties-to-even is then one bf16 ulp).
-  static __device__ __forceinline__ uint32_t pack_finite(float a, float b) {
-    uint32_t ua, ub;   // the adds as integer multiply-adds: they issue on the FMA pipe, which has room
-    asm("mad.lo.u32 %0, %1, 1, 0x8000;" : "=r"(ua) : "r"(__float_as_uint(a)));
-    asm("mad.lo.u32 %0, %1, 1, 0x8000;" : "=r"(ub) : "r"(__float_as_uint(b)));
-    return __byte_perm(ua, ub, 0x7632);
-  }
 };
 template <> struct Pack<__half> {
   static __device__ __forceinline__ uint32_t pack(float a, float b) {
@@ -93,7 +82,6 @@ template <> struct Pack<__half> {
   static __device__ __forceinline__ float2 unpack(uint32_t u) {
     return __half22float2(*reinterpret_cast<__half2*>(&u));
   }
-  static __device__ __forceinline__ uint32_t pack_finite(float a, float b) { return pack(a, b); }
 };
 
 // Eight fp32 values (as register bits) times a, optionally plus eight stored 16-bit values times b.

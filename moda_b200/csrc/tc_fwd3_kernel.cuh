@@ -68,7 +68,7 @@ __device__ __forceinline__ void f3_step(const F3Plan& pl, int s, int& part, bool
   row = pl.w[a].dep_c0 + d * kBN;
 }
 
-template <typename T, int kPolyEvery, bool kIntPack = false>
+template <typename T, int kPolyEvery>
 __global__ void __launch_bounds__(kF3Threads, 1)
 fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps maps) {
   using B_ = F3Bars;
@@ -280,7 +280,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         tmem_ld32<64>(tmem_S + lane_addr + 64, su);
         tmem_ld32<96>(tmem_S + lane_addr + 96, su);
         tmem_wait_ld();
-        softmax_row128<T, kPolyEvery, kIntPack>(su, masked, c0, lo, hi, c, m_used, l, alpha, grow, pk);
+        softmax_row128<T, kPolyEvery>(su, masked, c0, lo, hi, c, m_used, l, alpha, grow, pk);
       }
       tmem_st32<0>(tmem_S + lane_addr + 0, pk);
       tmem_st32<32>(tmem_S + lane_addr + 32, pk);
@@ -361,14 +361,10 @@ inline int fwd3(const Params& p, const moda_problem* pr, cudaStream_t st, int* l
     return cudaGetLastError();
   };
   // One pair of exponentials in four on the FMA pipe: measured on config 4 (forward only) 33.5 ms,
-  // against 34.1 ms with none, 33.7 ms with one in eight and 36.2 ms with one in two.
-  const int v = debug_state().variant;
-  if (pr->dtype != MODA_BF16) e = launch(fwd3_kernel<__half, 4>);
-  else if ((v & 256) && (v & 512)) e = launch(fwd3_kernel<__nv_bfloat16, 0, true>);
-  else if (v & 256) e = launch(fwd3_kernel<__nv_bfloat16, 4, true>);
-  else if (v & 512) e = launch(fwd3_kernel<__nv_bfloat16, 0, false>);
-  else if (v & 1024) e = launch(fwd3_kernel<__nv_bfloat16, 8, true>);
-  else e = launch(fwd3_kernel<__nv_bfloat16, 4>);
+  // against 34.1 ms with none, 33.7 ms with one in eight and 36.2 ms with one in two.  Rounding P
+  // to 16 bits with integer adds and a byte permute instead of the conversion instruction was
+  // also measured: 33.0 ms against 32.2 ms.
+  e = (pr->dtype == MODA_BF16) ? launch(fwd3_kernel<__nv_bfloat16, 4>) : launch(fwd3_kernel<__half, 4>);
   if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
   *launches += 1;
   return MODA_OK;

@@ -214,7 +214,7 @@ __device__ __forceinline__ float2 exp2x2_fma(float2 x) {
 // the caller to rescale O), and returns P = exp2(s * c - m) as 64 packed 16-bit pairs, with the
 // row sum added to l.  scale > 0 is required (the maximum is taken before scaling).  One pair in
 // kPolyEvery takes its two exponentials on the FMA pipe (exp2x2_fma) instead of the exp2 unit.
-template <typename T, int kPolyEvery, bool kIntPack = false>
+template <typename T, int kPolyEvery>
 __device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, int c0, int lo, int hi, float c,
                                                float& m_used, float& l, float& alpha, bool& grow, uint32_t (&pk)[64]) {
   float s[128];
@@ -261,7 +261,7 @@ __device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool m
       pp.y = fast_exp2(x.y);
     }
     sum2[i & 3] = __fadd2_rn(sum2[i & 3], pp);
-    pk[i] = kIntPack ? Pack<T>::pack_finite(pp.x, pp.y) : Pack<T>::pack(pp.x, pp.y);
+    pk[i] = Pack<T>::pack(pp.x, pp.y);
   }
   const float2 tot = __fadd2_rn(__fadd2_rn(sum2[0], sum2[1]), __fadd2_rn(sum2[2], sum2[3]));
   l += tot.x + tot.y;
