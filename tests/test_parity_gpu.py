@@ -319,3 +319,18 @@ def test_tcgen05_forward_variants(M, mode, T, L, G, variant):
         assert _cabi.device_status() == 0
     finally:
         lib.moda_b200_debug_set(None, 0)
+
+
+@pytest.mark.parametrize("variant", [32, 128], ids=["one_tile_two_ctas", "two_tiles"])
+@pytest.mark.parametrize("mode,T,L", [(mo.MODE_CAUSAL, 700, 6), (mo.MODE_NONCAUSAL, 300, 11)])
+def test_split_depth_merges_into_each_tcgen05_forward(M, mode, T, L, variant):
+    """G = 1 on the auto path: the bandwidth kernels write the own-position depth partial and the
+    tcgen05 forward / dq kernels fold the sequence part into it; each forward forced in turn."""
+    from moda_b200 import _cabi
+    lib = _cabi.load()
+    lib.moda_b200_debug_set(None, variant)
+    try:
+        _run_case(M, mode, 1, T, 2, 128, L, 1, torch.bfloat16, None, seed=900 + T)
+        assert _cabi.device_status() == 0
+    finally:
+        lib.moda_b200_debug_set(None, 0)
