@@ -280,6 +280,9 @@ def run_reference_arm(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run sets OMP_NUM_THREADS=1 for its children; the CPU arm uses every core
+    # this process may run on
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     T_s = min(T, args.cpu_sample_T)
     for _ in range(min(args.warmup, 1)):
         cpu_reference_sample(mode, G, D, L, max(256, T_s // 8))
@@ -549,6 +552,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
         dt, fl, desc = cpu_reference_sample(mode, G, D, L, min(T, args.cpu_sample_T))
         cpu_baseline = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                         "sample": desc, "seconds": dt}
