@@ -317,6 +317,7 @@ def main():
     ap.add_argument("--cpu-sample-T", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-twin", action="store_true", help="skip the sequence-only twin (depth-KV overhead) leg")
     ap.add_argument("--fwd-only", action="store_true", help="time forward only (exploration; not the headline)")
     ap.add_argument("--fwd-variant", type=int, default=0, help="bring-up switch of the forward kernel (exploration)")
     args = ap.parse_args()
@@ -463,6 +464,37 @@ def main():
                         "peak_source": pk["source"] + " (sustained cuBLAS bf16)", "avg_launch_ms": avg_ms,
                         "kernels": {k: {"launches": c, "total_ms": round(m, 3)} for k, (c, m) in prof.items()}}
 
+    # ---- depth-KV overhead: the same kernels on the same q, k, v, dO with L = 0 ---------------
+    # (t_MoDA - t_seq_only) / t_MoDA, the two timed back to back in this process, twin first and
+    # full second in alternation so that both see the same package temperature
+    depth_overhead = None
+    if (not args.fwd_only and not args.no_twin and mode != "fda" and L > 0 and len(units) > 0):
+        t_twin = dict(t)
+        t_twin["kd"] = None
+        t_twin["vd"] = None
+
+        def timed(tt, n_steps):
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(n_steps):
+                op_fwd_bwd(M, mode, tt, G)
+            b_.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b_) / n_steps
+
+        timed(t_twin, 1)
+        pairs_ms = [(timed(t_twin, args.steps), timed(t, args.steps)) for _ in range(2)]
+        tw = sum(x for x, _ in pairs_ms) / len(pairs_ms)
+        fu = sum(y for _, y in pairs_ms) / len(pairs_ms)
+        if world > 1:
+            tt2 = torch.tensor([tw, fu], device=device, dtype=torch.float64)
+            dist.all_reduce(tt2, op=dist.ReduceOp.MAX)
+            tw, fu = float(tt2[0].item()), float(tt2[1].item())
+        depth_overhead = {"seq_only_ms_per_step": tw, "full_ms_per_step": fu, "frac": (fu - tw) / fu,
+                          "pairs_ms": [[round(x, 3), round(y, 3)] for x, y in pairs_ms],
+                          "note": "same kernels, same q/k/v/dO, L = 0; (t_full - t_seq_only) / t_full"}
+
     # ---- end-to-end through the public autograd operator with host buffers -------------
     e2e = None
     if not args.no_e2e and not args.fwd_only and len(units) > 0:
@@ -572,7 +604,7 @@ def main():
             "frac_of_nominal_bf16_peak": value / (2250.0 * world),
             "frac_of_measured_bf16_peak": value / (pk["tflops"] * world),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
-            "clocks": clocks, "remeasured": remeasured,
+            "clocks": clocks, "remeasured": remeasured, "depth_overhead": depth_overhead,
             "validation": {"per_unit_checksum_o_lse": [[round(float(a), 3), round(float(b), 3)] for a, b in cs_all.tolist()]},
         }
         print(json.dumps(line), flush=True)
