@@ -334,3 +334,32 @@ def test_split_depth_merges_into_each_tcgen05_forward(M, mode, T, L, variant):
         assert _cabi.device_status() == 0
     finally:
         lib.moda_b200_debug_set(None, 0)
+
+
+def _random_cases(seed, n):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    for _ in range(n):
+        mode = rng.choice([mo.MODE_CAUSAL, mo.MODE_NONCAUSAL, mo.MODE_CHUNK_VISIBLE])
+        G = rng.choice([1, 2, 4, 8])
+        T = rng.choice([1, 5, 17, 63, 64, 65, 100, 128, 191, 200, 256, 300, 511, 513, 777, 1024, 1500])
+        T = min(T, max(1, 4200 // G))
+        L = rng.choice([0, 1, 2, 3, 5, 8, 11, 16, 24, 32, 33])
+        cases.append((mode, rng.choice([1, 2]), T, rng.choice([1, 2, 3]), L, G, rng.choice(["bf16", "fp16"]),
+                      rng.choice([0, 32, 128]), rng.choice([False, True]), rng.randrange(1 << 30)))
+    return cases
+
+
+@pytest.mark.parametrize("mode,B,T,H,L,G,dt,variant,forced,seed", _random_cases(20251, 32))
+def test_randomised_shapes_d128(M, mode, B, T, H, L, G, dt, variant, forced, seed):
+    """Seeded random draws over mode, batch, length, heads, depth layers, group size, dtype, the
+    forward kernel (bring-up switch) and auto / forced tcgen05 path; forward and backward."""
+    from moda_b200 import _cabi
+    lib = _cabi.load()
+    lib.moda_b200_debug_set(None, variant)
+    try:
+        _run_case(M, mode, B, T, H, 128, L, G, DT[dt], None, seed=seed, path=(M.PATH_TCGEN05 if forced else None))
+        assert _cabi.device_status() == 0
+    finally:
+        lib.moda_b200_debug_set(None, 0)
