@@ -44,6 +44,8 @@ WORKLOADS = {
     "small_chunk_visible_T8192": ("chunk", 1, 8192, 8, 4, 128, 32),
     # sequence-only twin of config 4 (same kernels, L = 0): gives the depth-KV overhead
     "config4_seq_only_twin_T65536": ("chunk", 1, 65536, 8, 4, 128, 0),
+    # the causal, own-position-depth operator at config 4's size (forward target of the north star)
+    "causal_T65536": ("causal", 1, 65536, 8, 4, 128, 32),
 }
 DEFAULT_WORKLOAD = "config4_chunk_visible_T65536"
 CHUNK_ROWS = 64
@@ -362,17 +364,20 @@ def main():
 
     step_flops_total = flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=not args.fwd_only)
 
-    def one_step():
+    def run_ops(tt):
         if args.fwd_only:
             if mode == "chunk":
-                o, lse = M.parallel_moda_chunk_visible_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+                o, lse = M.parallel_moda_chunk_visible_fwd(tt["q"], tt["k"], tt["v"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G)
             elif mode == "fda":
-                o, lse = M.parallel_fda_fwd(t["q"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G)
+                o, lse = M.parallel_fda_fwd(tt["q"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G)
             else:
-                o, lse = M.parallel_moda_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G,
+                o, lse = M.parallel_moda_fwd(tt["q"], tt["k"], tt["v"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G,
                                              is_causal=(mode == "causal"))
             return o, lse, [], M.last_launch_count()
-        return op_fwd_bwd(M, mode, t, G)
+        return op_fwd_bwd(M, mode, tt, G)
+
+    def one_step():
+        return run_ops(t)
 
     if len(units) > 0:
         for _ in range(args.warmup):
@@ -468,7 +473,7 @@ def main():
     # (t_MoDA - t_seq_only) / t_MoDA, the two timed back to back in this process, twin first and
     # full second in alternation so that both see the same package temperature
     depth_overhead = None
-    if (not args.fwd_only and not args.no_twin and mode != "fda" and L > 0 and len(units) > 0):
+    if (not args.no_twin and mode != "fda" and L > 0 and len(units) > 0):
         t_twin = dict(t)
         t_twin["kd"] = None
         t_twin["vd"] = None
@@ -478,7 +483,7 @@ def main():
             torch.cuda.synchronize()
             a.record()
             for _ in range(n_steps):
-                op_fwd_bwd(M, mode, tt, G)
+                run_ops(tt)
             b_.record()
             torch.cuda.synchronize()
             return a.elapsed_time(b_) / n_steps
