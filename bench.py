@@ -53,11 +53,14 @@ CHUNK_ROWS = 64
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel on the default
 # workload, from the ncu captures summarised under profiles/ (None = not captured).
 # The tcgen05 kernels were captured on the T=8192 case (full size exceeds the capture size
-# rule); their DRAM traffic there is 0.97-0.99 x the algorithmic bytes (inputs read once from
+# rule); their DRAM traffic there is 0.96-1.01 x the algorithmic bytes (inputs read once from
 # HBM, tiles re-read from L2), and traffic grows with the units processed, so the full-size
-# figure is the algorithmic bytes of the launch times that ratio.
-NCU_TRAFFIC_BYTES = {"tc_fwd": 0.99 * 9.93e9, "tc_dq": 0.98 * 10.5e9, "tc_dkv": 0.97 * 18.8e9,
-                     "fda_fwd": 17.72e9, "fda_bwd": 35.43e9}
+# figure is the algorithmic bytes of the launch times that ratio.  Algorithmic bytes at config 4:
+# forward q, k, v, depth K/V in, o + lse out = 9.93 GB; dq the same inputs + o, dO in, dq out =
+# 10.5 GB; dk/dv (sequence keys only) q, dO, k, v in, dk, dv out = 1.62 GB; depth gradients depth
+# K/V, q, dO in, d_depth_k/v out = 18.3 GB.
+NCU_TRAFFIC_BYTES = {"tc_fwd": 0.99 * 9.93e9, "tc_dq": 0.98 * 10.5e9, "tc_dkv": 0.96 * 1.62e9,
+                     "tc_depth_grad": 1.01 * 18.3e9, "fda_fwd": 17.72e9, "fda_bwd": 35.43e9}
 
 # share of the backward's 10*D*pairs algorithmic FLOPs attributed to each backward
 # kernel (dq kernel runs 3 of the 7 executed matmuls, dk/dv kernel 4 of 7)
