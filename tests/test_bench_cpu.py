@@ -1,0 +1,56 @@
+"""Host-side checks of bench.py: the algorithmic work figures and the command line contract."""
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_algorithmic_work_of_the_named_configs():
+    b = _bench()
+    # config 4 (chunk-visible, T = 65536, Hq = 32, D = 128, L = 32): forward 35.48, backward 88.69,
+    # together 124.17 TFLOP; sequence-only twin 123.15 TFLOP
+    mode, B, T, Hkv, G, D, L = b.WORKLOADS[b.DEFAULT_WORKLOAD]
+    fwd = b.flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=False)
+    both = b.flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=True)
+    assert abs(fwd / 1e12 - 35.48) < 0.01
+    assert abs(both / 1e12 - 124.17) < 0.01
+    twin = b.flops(*b.WORKLOADS["config4_seq_only_twin_T65536"], fwd=True, bwd=True)
+    assert abs(twin / 1e12 - 123.15) < 0.01
+    # config 2 forward 0.1391 TFLOP; config 3 forward + backward 0.060 TFLOP; config 5 0.056 TFLOP
+    assert abs(b.flops(*b.WORKLOADS["config2_causal_T4096"], fwd=True, bwd=False) / 1e12 - 0.1391) < 1e-3
+    assert abs(b.flops(*b.WORKLOADS["config3_fda_T8192"], fwd=True, bwd=True) / 1e12 - 0.060) < 1e-3
+    assert abs(b.flops(*b.WORKLOADS["config5_deit_noncausal_T197"], fwd=True, bwd=True) / 1e12 - 0.056) < 1e-3
+
+
+def test_chunk_visible_pairs_match_a_direct_count():
+    b = _bench()
+    T, G, L, C = 100, 4, 3, 64
+    cb = C // G
+    direct = 0
+    for t in range(T):
+        direct += (t + 1) + (t - (t // cb) * cb + 1) * L     # sequence keys + depth rows of the chunk so far
+    assert b.pairs("chunk", 1, T, 1, G, L) == direct * G
+
+
+def test_reference_arm_prints_one_json_line_and_other_ranks_stay_silent():
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+                          "--steps", "1", "--warmup", "0"], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip() == ""
+    env = dict(os.environ, RANK="0", WORLD_SIZE="1")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0", "--cpu-sample-T", "512"], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-500:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
