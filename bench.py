@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the MoDA hot path: fwd+bwd TFLOP/s on BASELINE config 4.
+"""Benchmark of the MoDA hot path: fwd+bwd TFLOP/s on benchmark config 4.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \

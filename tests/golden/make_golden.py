@@ -35,7 +35,7 @@ CASES = [
     ("chunk_g4_l2", 15, MODE_CHUNK_VISIBLE, 1, 40, 2, 64, 2, 4, 16, None, True, True),
     ("chunk_g1_l1", 16, MODE_CHUNK_VISIBLE, 1, 150, 1, 64, 1, 1, 64, 0.2, True, True),
     ("fda_g2_l5", 17, MODE_DEPTH_ONLY, 1, 33, 2, 64, 5, 2, 0, None, True, True),
-    # BASELINE config 1: B=1,T=256,H=4,D=64,L=4,G=1, seed 0 (outputs only; inputs by seed)
+    # benchmark config 1: B=1,T=256,H=4,D=64,L=4,G=1, seed 0 (outputs only; inputs by seed)
     ("config1", 0, MODE_CAUSAL, 1, 256, 4, 64, 4, 1, 0, None, False, False),
 ]
 
@@ -87,4 +87,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of a checkout of hustvl/MoDA>")
+    main(sys.argv[1])

@@ -1,4 +1,4 @@
-"""GPU: parity at BASELINE config 4's full sequence length (T = 65536, G = 4, L = 32, D = 128,
+"""GPU: parity at benchmark config 4's full sequence length (T = 65536, G = 4, L = 32, D = 128,
 chunk-visible) through properties that do not need the full O(T^2) oracle:
 
 * sampled query rows (o, lse, dq), sampled depth rows (d_depth_k/v) and the last sequence keys

@@ -55,7 +55,7 @@ def test_oracle_matches_reference_gradients(name):
 
 
 def test_config1_sanity_values():
-    # BASELINE config 1 (B=1,T=256,H=4,D=64,L=4,G=1, seed 0): values recorded from the
+    # benchmark config 1 (B=1,T=256,H=4,D=64,L=4,G=1, seed 0): values recorded from the
     # reference's naive_mixture_of_depth_causal_ref in the build container.
     rec = load_golden("config1")
     assert abs(float(abs(rec["o"]).mean()) - 0.13568142) < 1e-7

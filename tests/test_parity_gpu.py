@@ -109,10 +109,10 @@ def test_no_depth(M, mode):
 
 
 @pytest.mark.parametrize("mode,T,L,G", [
-    (mo.MODE_CAUSAL, 1024, 24, 4),          # BASELINE config 2 shape at reduced T, B, H
-    (mo.MODE_CHUNK_VISIBLE, 1024, 32, 4),   # BASELINE config 4 shape at reduced T, H
+    (mo.MODE_CAUSAL, 1024, 24, 4),          # benchmark config 2 shape at reduced T, B, H
+    (mo.MODE_CHUNK_VISIBLE, 1024, 32, 4),   # benchmark config 4 shape at reduced T, H
     (mo.MODE_CHUNK_VISIBLE, 512, 8, 1),
-    (mo.MODE_DEPTH_ONLY, 512, 32, 1),       # BASELINE config 3 shape at reduced B, T, H
+    (mo.MODE_DEPTH_ONLY, 512, 32, 1),       # benchmark config 3 shape at reduced B, T, H
     (mo.MODE_CAUSAL, 640, 0, 1),
 ])
 def test_config_shapes_reduced_d128(M, mode, T, L, G):
@@ -120,7 +120,7 @@ def test_config_shapes_reduced_d128(M, mode, T, L, G):
 
 
 def test_deit_shape_noncausal(M):
-    # BASELINE config 5 at reduced batch: T=197, H=6, D=64, L=11, non-causal
+    # benchmark config 5 at reduced batch: T=197, H=6, D=64, L=11, non-causal
     _run_case(M, mo.MODE_NONCAUSAL, 3, 197, 6, 64, 11, 1, torch.bfloat16, None, seed=4)
 
 

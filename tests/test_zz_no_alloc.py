@@ -102,7 +102,7 @@ def test_static_scratch_rejects_oversized_problem(built_library):
     """A problem whose scratch does not fit the fixed array is refused before any launch."""
     from moda_b200 import _cabi
     lib = _cabi.load()
-    # BASELINE config 4: 2.1 M query rows x 8 heads of fp32 statistics is far beyond 8 MiB
+    # benchmark config 4: 2.1 M query rows x 8 heads of fp32 statistics is far beyond 8 MiB
     prob = _cabi.Problem(1, 65536, 8, 128, 4, 32, 2, 64, _cabi.DTYPE_BF16, _cabi.PATH_AUTO, 0.088, 0)
     need = ctypes.c_size_t(0)
     assert lib.moda_b200_bwd_workspace_bytes(ctypes.byref(prob), ctypes.byref(need)) == 0
