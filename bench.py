@@ -476,30 +476,33 @@ def main():
     # (t_MoDA - t_seq_only) / t_MoDA, the two timed back to back in this process, twin first and
     # full second in alternation so that both see the same package temperature
     depth_overhead = None
-    if (not args.no_twin and mode != "fda" and L > 0 and len(units) > 0):
-        t_twin = dict(t)
-        t_twin["kd"] = None
-        t_twin["vd"] = None
+    if not args.no_twin and mode != "fda" and L > 0:
+        tw = fu = 0.0
+        pairs_ms = []
+        if len(units) > 0:      # (a rank without units still joins the reduction below)
+            t_twin = dict(t)
+            t_twin["kd"] = None
+            t_twin["vd"] = None
 
-        def timed(tt, n_steps):
-            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            a.record()
-            for _ in range(n_steps):
-                run_ops(tt)
-            b_.record()
-            torch.cuda.synchronize()
-            return a.elapsed_time(b_) / n_steps
+            def timed(tt, n_steps):
+                a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for _ in range(n_steps):
+                    run_ops(tt)
+                b_.record()
+                torch.cuda.synchronize()
+                return a.elapsed_time(b_) / n_steps
 
-        timed(t_twin, 1)
-        pairs_ms = [(timed(t_twin, args.steps), timed(t, args.steps)) for _ in range(2)]
-        tw = sum(x for x, _ in pairs_ms) / len(pairs_ms)
-        fu = sum(y for _, y in pairs_ms) / len(pairs_ms)
+            timed(t_twin, 1)
+            pairs_ms = [(timed(t_twin, args.steps), timed(t, args.steps)) for _ in range(2)]
+            tw = sum(x for x, _ in pairs_ms) / len(pairs_ms)
+            fu = sum(y for _, y in pairs_ms) / len(pairs_ms)
         if world > 1:
             tt2 = torch.tensor([tw, fu], device=device, dtype=torch.float64)
             dist.all_reduce(tt2, op=dist.ReduceOp.MAX)
             tw, fu = float(tt2[0].item()), float(tt2[1].item())
-        depth_overhead = {"seq_only_ms_per_step": tw, "full_ms_per_step": fu, "frac": (fu - tw) / fu,
+        depth_overhead = {"seq_only_ms_per_step": tw, "full_ms_per_step": fu, "frac": ((fu - tw) / fu if fu > 0 else None),
                           "pairs_ms": [[round(x, 3), round(y, 3)] for x, y in pairs_ms],
                           "note": "same kernels, same q/k/v/dO, L = 0; (t_full - t_seq_only) / t_full"}
 
