@@ -57,32 +57,40 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ------------------------------------------------------------------ statistics pass
-// One warp per (b, h, r); a block of 8 warps covers 8 consecutive rows of one (b, h).
+// delta = rowsum(o * dO) from the stored o, and lse, both transposed to [B, H, T_qp] so that the
+// backward kernels fetch 64 rows of one (b, h) with one 256-byte bulk copy.  Eight lanes per row,
+// four rows per warp, 32 consecutive rows of one (b, h) per block iteration; each lane has two
+// 16-byte loads of o and two of dO in flight.
 template <typename T>
 __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params p, float* delta_t, float* lse_t, int T_qp) {
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int64_t groups_per_bh = T_qp / 8;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, sub = lane & 7, grp = lane >> 3;
+  const uint32_t groups_per_bh = (uint32_t)T_qp / 32u;             // T_qp is a multiple of 64
   const int64_t n_groups = (int64_t)p.B * p.H * groups_per_bh;
   for (int64_t gidx = blockIdx.x; gidx < n_groups; gidx += gridDim.x) {
-    const int64_t bh = gidx / groups_per_bh;
-    const int r = (int)(gidx % groups_per_bh) * 8 + w;
-    const int b = (int)(bh / p.H), h = (int)(bh % p.H);
+    const uint32_t bh = (uint32_t)(gidx / groups_per_bh);
+    const int r = (int)((uint32_t)(gidx - (int64_t)bh * groups_per_bh) * 32u) + w * 4 + grp;
+    const int b = (int)(bh / (uint32_t)p.H), h = (int)(bh % (uint32_t)p.H);
     float s = 0.f, l = 0.f;
     if (r < p.T_q) {
       const T* po = reinterpret_cast<const T*>(p.o.ptr) + p.o.off(b, r, h);
       const T* pd = reinterpret_cast<const T*>(p.dout.ptr) + p.dout.off(b, r, h);
-      const uint2 a = *reinterpret_cast<const uint2*>(po + lane * 4);
-      const uint2 d = *reinterpret_cast<const uint2*>(pd + lane * 4);
-      const float2 a0 = Pack<T>::unpack(a.x), a1 = Pack<T>::unpack(a.y);
-      const float2 d0 = Pack<T>::unpack(d.x), d1 = Pack<T>::unpack(d.y);
-      s = a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y;
+      const uint4 a0 = *reinterpret_cast<const uint4*>(po + sub * 8), a1 = *reinterpret_cast<const uint4*>(po + 64 + sub * 8);
+      const uint4 d0 = *reinterpret_cast<const uint4*>(pd + sub * 8), d1 = *reinterpret_cast<const uint4*>(pd + 64 + sub * 8);
+      const uint32_t av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const uint32_t dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      l = p.lse[((int64_t)b * p.T_q + r) * p.H + h];
+      for (int i = 0; i < 8; ++i) {
+        const float2 x = Pack<T>::unpack(av[i]), y = Pack<T>::unpack(dv[i]);
+        s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+      }
+      if (sub == 0) l = p.lse[((int64_t)b * p.T_q + r) * p.H + h];
     }
-    if (lane == 0) {
-      delta_t[bh * T_qp + r] = s;     // rows in [T_q, T_qp) are written as zeros
-      lse_t[bh * T_qp + r] = l;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (sub == 0) {
+      delta_t[(int64_t)bh * T_qp + r] = s;     // rows in [T_q, T_qp) are written as zeros
+      lse_t[(int64_t)bh * T_qp + r] = l;
     }
   }
 }
@@ -1090,8 +1098,8 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_
 
   const bool bf = pr->dtype == MODA_BF16;
   {
-    const int64_t groups = (int64_t)p.B * p.H * (T_qp / 8);
-    const int blocks = (int)(groups < 148 * 32 ? groups : 148 * 32);
+    const int64_t groups = (int64_t)p.B * p.H * (T_qp / 32);
+    const int blocks = (int)(groups < 148 * 16 ? groups : 148 * 16);
     prof::Scope ps(prof::kPreTc, st);
     if (bf) pre_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
     else pre_kernel<__half><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
