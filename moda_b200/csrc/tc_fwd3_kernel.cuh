@@ -280,7 +280,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         tmem_ld32<64>(tmem_S + lane_addr + 64, su);
         tmem_ld32<96>(tmem_S + lane_addr + 96, su);
         tmem_wait_ld();
-        softmax_row128<T, kPolyEvery>(su, masked, c0, lo, hi, c, m_used, l, alpha, grow, pk);
+        softmax_row128<T, kPolyEvery>(su, masked, is_dep && (p.L & 31) == 0, c0, lo, hi, c, m_used, l, alpha, grow, pk);
       }
       tmem_st32<0>(tmem_S + lane_addr + 0, pk);
       tmem_st32<32>(tmem_S + lane_addr + 32, pk);

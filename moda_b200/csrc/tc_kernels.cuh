@@ -209,18 +209,29 @@ __device__ __forceinline__ float2 exp2x2_fma(float2 x) {
 }
 
 // One row's online-softmax step over the 128 scores of a key tile (register bits in su; thread =
-// query row).  Masks columns outside [lo, hi) when `masked`, takes the row maximum, keeps the old
+// query row).  Masks columns outside [lo, hi) when `masked` (`uniform32`: [lo, hi) and the tile are
+// aligned to 32 columns), takes the row maximum, keeps the old
 // reference maximum unless the new one is more than 2^8 larger (lazy rescale: alpha / grow tell
 // the caller to rescale O), and returns P = exp2(s * c - m) as 64 packed 16-bit pairs, with the
 // row sum added to l.  scale > 0 is required (the maximum is taken before scaling).  One pair in
 // kPolyEvery takes its two exponentials on the FMA pipe (exp2x2_fma) instead of the exp2 unit.
 template <typename T, int kPolyEvery>
-__device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, int c0, int lo, int hi, float c,
+__device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, bool uniform32, int c0, int lo, int hi, float c,
                                                float& m_used, float& l, float& alpha, bool& grow, uint32_t (&pk)[64]) {
   float s[128];
 #pragma unroll
   for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
-  if (masked) {
+  if (masked && uniform32) {
+    // depth tile with L a multiple of 32: a row sees whole positions, so each aligned group of 32
+    // columns is visible or not as a whole - four tests instead of 128
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int col = c0 + 32 * g;
+      const bool vis = col >= lo && col < hi;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[32 * g + i] = vis ? s[32 * g + i] : -INFINITY;
+    }
+  } else if (masked) {
 #pragma unroll
     for (int i = 0; i < 128; ++i) {
       const int col = c0 + i;
@@ -485,7 +496,7 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
           for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = __uint_as_float(su[i]);
         }
         // same arithmetic as fwd3_kernel, so that a result does not depend on which of the two ran
-        softmax_row128<T, 4>(su, masked, c0, lo, hi, c, m_used, l, alpha, grow, pk);
+        softmax_row128<T, 4>(su, masked, is_dep && (p.L & 31) == 0, c0, lo, hi, c, m_used, l, alpha, grow, pk);
       }
       if (kPTmem) {
         tmem_st32<0>(tmem_S + lane_addr + 0, pk);
