@@ -44,27 +44,47 @@ WORKLOADS = {
     "small_chunk_visible_T8192": ("chunk", 1, 8192, 8, 4, 128, 32),
     # sequence-only twin of config 4 (same kernels, L = 0): gives the depth-KV overhead
     "config4_seq_only_twin_T65536": ("chunk", 1, 65536, 8, 4, 128, 0),
-    # the causal, own-position-depth operator at config 4's size (forward target of the north star)
+    # the causal, own-position-depth operator at config 4's size
     "causal_T65536": ("causal", 1, 65536, 8, 4, 128, 32),
+    # the one shape the reference publishes a kernel time for (README.md:94; A100, fwd+bwd):
+    # B=1, T=65536, G=8, Hq=64, Hk=8, d=64, L=64, causal own-position depth
+    "published_causal_T65536_d64": ("causal", 1, 65536, 8, 8, 64, 64),
+    # config 4 with D halved and the KV heads doubled (same FLOPs): the nearest shape the reference's
+    # chunk-visible Triton launcher can run (it asserts for D=128: moda_v16.py:598)
+    "config4_d64_twin_T65536": ("chunk", 1, 65536, 16, 4, 64, 32),
 }
+# workloads reported beside the default one (N = 1 only): name -> (what is timed, bound)
+OTHER_WORKLOADS = {
+    "config2_causal_T4096": ("fwd", "tensor"),
+    "config3_fda_T8192": ("fwd+bwd", "hbm"),
+    "config5_deit_noncausal_T197": ("fwd+bwd", "hbm"),
+    "published_causal_T65536_d64": ("fwd+bwd", "tensor"),
+}
+PUBLISHED_A100_MS = {"published_causal_T65536_d64": 1883.026}   # reference README.md:94 (MoDA-Triton, A100)
 DEFAULT_WORKLOAD = "config4_chunk_visible_T65536"
 CHUNK_ROWS = 64
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel on the default
-# workload, from the ncu captures summarised under profiles/ (None = not captured).
-# The tcgen05 kernels were captured on the T=8192 case (full size exceeds the capture size
-# rule); their DRAM traffic there is 0.96-1.01 x the algorithmic bytes (inputs read once from
-# HBM, tiles re-read from L2), and traffic grows with the units processed, so the full-size
-# figure is the algorithmic bytes of the launch times that ratio.  Algorithmic bytes at config 4:
-# forward q, k, v, depth K/V in, o + lse out = 9.93 GB; dq the same inputs + o, dO in, dq out =
-# 10.5 GB; dk/dv (sequence keys only) q, dO, k, v in, dk, dv out = 1.62 GB; depth gradients depth
-# K/V, q, dO in, d_depth_k/v out = 18.3 GB.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel on the default workload,
+# SCALED from the ncu captures summarised under profiles/: the tcgen05 kernels were captured on
+# the T=8192 case (the full size exceeds the capture size rule); their DRAM traffic there is
+# 0.96-1.01 x the algorithmic bytes (inputs read once from HBM, tiles re-read from L2), and
+# traffic grows with the units processed, so the full-size figure is the algorithmic bytes of the
+# launch times that ratio.  Algorithmic bytes at config 4: forward q, k, v, depth K/V in, o + lse
+# out = 9.93 GB; dq the same inputs + o, dO in, dq out = 10.5 GB; dk/dv (sequence keys only) q, dO,
+# k, v in, dk, dv out = 1.62 GB; depth gradients depth K/V, q, dO in, d_depth_k/v out = 18.3 GB.
 NCU_TRAFFIC_BYTES = {"tc_fwd": 0.99 * 9.93e9, "tc_dq": 0.98 * 10.5e9, "tc_dkv": 0.96 * 1.62e9,
                      "tc_depth_grad": 1.01 * 18.3e9, "fda_fwd": 17.72e9, "fda_bwd": 35.43e9}
+NCU_TRAFFIC_SOURCE = {"tc_fwd": "scaled from the T=8192 ncu capture", "tc_dq": "scaled from the T=8192 ncu capture",
+                      "tc_dkv": "scaled from the T=8192 ncu capture", "tc_depth_grad": "scaled from the T=8192 ncu capture",
+                      "fda_fwd": "ncu capture of this workload", "fda_bwd": "ncu capture of this workload"}
 
-# share of the backward's 10*D*pairs algorithmic FLOPs attributed to each backward
-# kernel (dq kernel runs 3 of the 7 executed matmuls, dk/dv kernel 4 of 7)
-BWD_SHARE = {"simt_dq": 3.0 / 7.0, "simt_dkv": 4.0 / 7.0, "tc_dq": 3.0 / 7.0, "tc_dkv": 4.0 / 7.0}
+# Algorithmic matmuls (of 2*D*pairs FLOP each) a kernel OWNS - the outputs it alone produces.  The
+# forward owns S and O (2); of the backward's five (S, dP, dV, dK, dQ) the dq kernel owns dQ, the
+# dk/dv kernel dK and dV; the scores both backward kernels recompute (S, dP) are owned by neither,
+# so the per-kernel figures of a two-kernel backward do not add up to the step's - the whole-step
+# figure in roofline.step is the one that counts every algorithmic FLOP exactly once.
+OWNED_MATMULS = {"simt_fwd": 2, "tc_fwd": 2, "simt_dq": 1, "tc_dq": 1, "simt_dkv": 2, "tc_dkv": 2}
+EXECUTED_MATMULS = {"simt_fwd": 2, "tc_fwd": 2, "simt_dq": 3, "tc_dq": 3, "simt_dkv": 4, "tc_dkv": 4}
 
 
 def pairs(mode, B, T, Hkv, G, L):
@@ -96,10 +116,11 @@ def peaks():
     if os.path.exists(path):
         with open(path) as f:
             m = json.load(f)
+        mhz = (m.get("clocks_under_load") or {}).get("sm_mhz_median")
         return {"tflops": float(m.get("bf16_tflops_sustained", m.get("bf16_tflops"))),
                 "tflops_burst": float(m.get("bf16_tflops")), "hbm_gbs": float(m["hbm_gbs"]),
-                "source": "measured"}
-    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+                "peak_sm_mhz": float(mhz) if mhz else None, "source": "measured"}
+    return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "peak_sm_mhz": 1300.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -311,26 +332,218 @@ def run_reference_arm(args, wl):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------
+# The reference's own Triton kernels on this GPU (a reported baseline, not the target).  They are
+# imported from an install of the unmodified reference package under baseline/_ref (made by
+# baseline/install_reference.py; git-ignored) - never from the product package - in a child
+# process, so that a Triton compile error or an assertion of the reference cannot take the
+# benchmark down with it.
+# ---------------------------------------------------------------------------------------------
+TRITON_WORKLOADS = ["config2_causal_T4096", "config3_fda_T8192", "config5_deit_noncausal_T197",
+                    "config4_chunk_visible_T65536", "config4_d64_twin_T65536", "published_causal_T65536_d64"]
+
+
+def run_triton_baseline_arm(args):
+    """--impl triton_baseline: times the reference's Triton operators (forward + backward through
+    their autograd Functions; forward only for config 2) on seeded inputs of the named shapes and
+    prints one JSON line {"impl": "triton_baseline", "results": [...]}.  A workload the reference
+    cannot run is recorded with its exception text, verbatim."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    out = {"impl": "triton_baseline", "results": []}
+    if not os.path.isdir(os.path.join(ref_dir, "fla")):
+        out["unavailable"] = "no reference install under baseline/_ref (run: python baseline/install_reference.py)"
+        print(json.dumps(out), flush=True)
+        return
+    if not torch.cuda.is_available():
+        out["unavailable"] = "no CUDA device"
+        print(json.dumps(out), flush=True)
+        return
+    sys.path.insert(0, ref_dir)
+    import io
+    import contextlib
+    import warnings
+    try:
+        with warnings.catch_warnings(), contextlib.redirect_stdout(io.StringIO()):
+            warnings.simplefilter("ignore")
+            import triton  # noqa: F401
+            from fla.ops.moda import parallel_moda, parallel_moda_chunk_visible
+            from fla.ops.moda.fda_v12 import parallel_fda
+        out["triton"] = triton.__version__
+    except Exception as exc:  # noqa: BLE001 - the message is the result
+        out["unavailable"] = f"import failed: {type(exc).__name__}: {exc}"[:500]
+        print(json.dumps(out), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    names = [args.workload] if args.workload != DEFAULT_WORKLOAD or args.only_workload else TRITON_WORKLOADS
+    for name in names:
+        mode, B, T, Hkv, G, D, L = WORKLOADS[name]
+        fwd_only = OTHER_WORKLOADS.get(name, ("fwd+bwd",))[0] == "fwd"
+        rec = {"workload": name, "mode": mode, "B": B, "T": T, "Hkv": Hkv, "G": G, "D": D, "L": L,
+               "timed": "fwd" if fwd_only else "fwd+bwd"}
+        try:
+            gen = torch.Generator(device=dev).manual_seed(3)
+            mk = lambda rows: torch.randn(B, rows, Hkv, D, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)  # noqa: E731
+            q = mk(T * G).requires_grad_(not fwd_only)
+            k = v = None
+            if mode != "fda":
+                k, v = mk(T).requires_grad_(not fwd_only), mk(T).requires_grad_(not fwd_only)
+            kd, vd = mk(T * L).requires_grad_(not fwd_only), mk(T * L).requires_grad_(not fwd_only)
+            dout = mk(T * G)
+
+            def step():
+                with contextlib.redirect_stdout(io.StringIO()):      # the reference prints a line per call
+                    if mode == "fda":
+                        o = parallel_fda(q, None, None, cached_k=kd, cached_v=vd, moda_group_num=G, warn_shape=False)
+                    elif mode == "chunk":
+                        o = parallel_moda_chunk_visible(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=G, warn_shape=False)
+                    else:
+                        o = parallel_moda(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=G,
+                                          is_causal=(mode == "causal"), warn_shape=False)
+                    if not fwd_only:
+                        o.backward(dout)
+                        for x in (q, k, v, kd, vd):
+                            if x is not None:
+                                x.grad = None
+
+            t0 = time.perf_counter()
+            step()
+            torch.cuda.synchronize()
+            first = time.perf_counter() - t0              # includes the Triton compile
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record(); step(); ev1.record(); torch.cuda.synchronize()
+            one = ev0.elapsed_time(ev1)
+            n_warm = 3 if one > 50 else 10
+            n_timed = max(5, min(50, int(3000 / max(one, 1e-3))))
+            for _ in range(n_warm):
+                step()
+            torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(n_timed):
+                step()
+            ev1.record()
+            torch.cuda.synchronize()
+            ms = ev0.elapsed_time(ev1) / n_timed
+            fl = flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=not fwd_only)
+            rec.update({"ms": ms, "tflops": fl / (ms * 1e-3) / 1e12, "iters": n_timed, "warmup": n_warm + 2,
+                        "first_call_s": first})
+            if mode == "fda" or name.startswith("config5"):
+                e = 2
+                nq, nkv, nd, nl = B * T * G * Hkv * D * e, (0 if mode == "fda" else B * T * Hkv * D * e), B * T * L * Hkv * D * e, 4 * B * T * G * Hkv
+                by = (2 * nq + 2 * nkv + 2 * nd + nl) + (0 if fwd_only else (4 * nq + 4 * nkv + 4 * nd + 2 * nl))
+                rec["gbs"] = by / (ms * 1e-3) / 1e9
+        except BaseException as exc:  # noqa: BLE001 - AssertionError / OutOfResources text is the result
+            if isinstance(exc, KeyboardInterrupt):
+                raise
+            rec["unavailable"] = f"{type(exc).__name__}: {exc}"[:600]
+        finally:
+            q = k = v = kd = vd = dout = None
+            torch.cuda.empty_cache()
+        out["results"].append(rec)
+    print(json.dumps(out), flush=True)
+
+
+def triton_baseline_in_child(timeout_s):
+    """Runs the --impl triton_baseline leg in a child process; returns its parsed JSON (or the
+    reason it is unavailable)."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "triton_baseline"]
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, env=env)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"did not finish within {timeout_s} s"}
+    for line in reversed(res.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                break
+    return {"unavailable": ("exit %d: " % res.returncode) + (res.stderr.strip().splitlines() or ["no output"])[-1][:400]}
+
+
+def time_workload(M, _cabi, name, device, steps, warmup, pk):
+    """One of the secondary workloads on this GPU: device time per step (CUDA events, inputs
+    resident and larger than L2 except where noted), algorithmic TFLOP/s or GB/s."""
+    mode, B, T, Hkv, G, D, L = WORKLOADS[name]
+    what, bound = OTHER_WORKLOADS[name]
+    fwd_only = what == "fwd"
+    units = range(0, B * Hkv)
+    t = make_shard(mode, T, G, D, L, units, Hkv, seed=WORKLOAD_SEEDS.get(name, 3), device=device)
+    # make_shard lays units along the head axis of a batch-1 tensor; give the batch its own axis back
+    if B > 1:
+        t = {n: (None if x is None else x.view(x.shape[1], B, Hkv, D).permute(1, 0, 2, 3).contiguous()) for n, x in t.items()}
+
+    def run():
+        if fwd_only:
+            return M.parallel_moda_fwd(t["q"], t["k"], t["v"], cached_k=t["kd"], cached_v=t["vd"], moda_group_num=G,
+                                       is_causal=(mode == "causal"))
+        return op_fwd_bwd(M, mode, t, G)
+
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device.index)
+    sampler.start()
+    _cabi.profile_begin()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        run()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    prof = _cabi.profile_end()
+    clocks = sampler.stop()
+    fl = flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=not fwd_only)
+    e = 2
+    nq, nkv, nd, nl = B * T * G * Hkv * D * e, (0 if mode == "fda" else B * T * Hkv * D * e), B * T * L * Hkv * D * e, 4 * B * T * G * Hkv
+    by = (2 * nq + 2 * nkv + 2 * nd + nl) + (0 if fwd_only else (4 * nq + 4 * nkv + 4 * nd + 2 * nl))
+    rec = {"workload": name, "mode": mode, "B": B, "T": T, "Hkv": Hkv, "G": G, "D": D, "L": L, "timed": what,
+           "steps": steps, "warmup": warmup, "ms_per_step": ms, "tflops": fl / (ms * 1e-3) / 1e12,
+           "gbs": by / (ms * 1e-3) / 1e9, "bound": bound,
+           "frac_of_measured_peak": (fl / (ms * 1e-3) / 1e12 / pk["tflops"]) if bound == "tensor" else (by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]),
+           "algorithmic_flops": fl, "algorithmic_bytes": by,
+           "kernels": {k: {"launches": c, "total_ms": round(m, 3)} for k, (c, m) in prof.items()},
+           "clocks": {"sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")},
+           "device_status": _cabi.device_status()}
+    if name in PUBLISHED_A100_MS:
+        rec["reference_published"] = {"ms": PUBLISHED_A100_MS[name], "hardware": "A100", "source": "README.md:94 (MoDA-Triton, fwd+bwd)"}
+    del t
+    torch.cuda.empty_cache()
+    return rec
+
+
+# seeds of the benchmark configurations (N(0,1) inputs from seed 1..4 for configs 2..5)
+WORKLOAD_SEEDS = {"config2_causal_T4096": 1, "config3_fda_T8192": 2, "config4_chunk_visible_T65536": 3,
+                  "config5_deit_noncausal_T197": 4}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton_baseline"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--only-workload", action="store_true", help="triton_baseline: time --workload only, also when it is the default one")
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05"])
     ap.add_argument("--cpu-sample-T", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-twin", action="store_true", help="skip the sequence-only twin (depth-KV overhead) leg")
+    ap.add_argument("--no-other-workloads", action="store_true", help="skip the secondary workloads (configs 2, 3, 5, published shape)")
+    ap.add_argument("--no-triton-baseline", action="store_true", help="skip the reference-Triton-kernels leg")
+    ap.add_argument("--triton-timeout", type=int, default=420)
     ap.add_argument("--fwd-only", action="store_true", help="time forward only (exploration; not the headline)")
-    ap.add_argument("--fwd-variant", type=int, default=0, help="bring-up switch of the forward kernel (exploration)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     mode, B, T, Hkv, G, D, L = wl
 
     if args.impl == "reference":
         run_reference_arm(args, wl)
+        return
+    if args.impl == "triton_baseline":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_triton_baseline_arm(args)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -352,8 +565,6 @@ def main():
     from moda_b200 import _cabi
     from moda_b200.sharding import gather_units, partition_units
     M.set_kernel_path({"auto": M.PATH_AUTO, "simt": M.PATH_SIMT_MMA, "tcgen05": M.PATH_TCGEN05}[args.path])
-    if args.fwd_variant:
-        _cabi.load().moda_b200_debug_set(None, args.fwd_variant)
 
     n_units = B * Hkv
     units = partition_units(n_units, world, rank)
@@ -367,15 +578,17 @@ def main():
 
     step_flops_total = flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=not args.fwd_only)
 
-    def run_ops(tt):
-        if args.fwd_only:
-            if mode == "chunk":
-                o, lse = M.parallel_moda_chunk_visible_fwd(tt["q"], tt["k"], tt["v"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G)
-            elif mode == "fda":
-                o, lse = M.parallel_fda_fwd(tt["q"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G)
-            else:
-                o, lse = M.parallel_moda_fwd(tt["q"], tt["k"], tt["v"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G,
-                                             is_causal=(mode == "causal"))
+    def run_fwd(tt):
+        if mode == "chunk":
+            return M.parallel_moda_chunk_visible_fwd(tt["q"], tt["k"], tt["v"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G)
+        if mode == "fda":
+            return M.parallel_fda_fwd(tt["q"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G)
+        return M.parallel_moda_fwd(tt["q"], tt["k"], tt["v"], cached_k=tt["kd"], cached_v=tt["vd"], moda_group_num=G,
+                                   is_causal=(mode == "causal"))
+
+    def run_ops(tt, fwd_only=args.fwd_only):
+        if fwd_only:
+            o, lse = run_fwd(tt)
             return o, lse, [], M.last_launch_count()
         return op_fwd_bwd(M, mode, tt, G)
 
@@ -431,6 +644,13 @@ def main():
                       "first_ms_per_step": first, "gap_frac_first": gap, "gap_frac": gap2}
     ms_per_step = elapsed_ms / args.steps
     value = step_flops_total / (ms_per_step * 1e-3) / 1e12
+    # sticky status word of the bounded waits: non-zero means some launch gave up and left its
+    # outputs unwritten, i.e. the timing above is of work that was not done
+    dev_status = _cabi.device_status()
+    if world > 1:
+        stt = torch.tensor([dev_status], device=device, dtype=torch.int64)
+        dist.all_reduce(stt, op=dist.ReduceOp.MAX)
+        dev_status = int(stt.item())
 
     # validation gather (untimed): per-unit checksums, identical for every N
     if len(units) > 0 and o is not None:
@@ -439,20 +659,31 @@ def main():
         cs = torch.zeros(0, 2, dtype=torch.float64, device=device)
     cs_all = gather_units(cs, n_units, world, rank)
 
-    # ---- roofline of the dominant kernel (rank 0's shard) -------------------------------
+    # ---- roofline (rank 0's shard) -------------------------------------------------------
     pk = peaks()
+    sm_mhz = (clocks or {}).get("sm_mhz")
+
+    def per_clock(ach, peak):
+        """(achieved / median SM MHz of this run) / (peak / SM MHz the peak was measured at)."""
+        if not sm_mhz or not pk.get("peak_sm_mhz"):
+            return None
+        return (ach / sm_mhz) / (peak / pk["peak_sm_mhz"])
+
     roofline = None
     if prof:
         name, (cnt, tot_ms) = max(prof.items(), key=lambda kv: kv[1][1])
         shard_frac = len(units) / n_units
         p_sh = pairs(mode, B, T, Hkv, G, L) * shard_frac
-        if name in ("simt_fwd", "tc_fwd", "fda_fwd"):
-            alg = 4 * D * p_sh
-        elif name in BWD_SHARE:
-            alg = 10 * D * p_sh * BWD_SHARE[name]
-        else:
-            alg = 10 * D * p_sh
         avg_ms = tot_ms / cnt
+        traffic = NCU_TRAFFIC_BYTES.get(name) if args.workload in (DEFAULT_WORKLOAD, "config3_fda_T8192") and world == 1 else None
+        kernels = {}
+        for k_, (c, m) in prof.items():
+            kernels[k_] = {"launches": c, "total_ms": round(m, 3)}
+            if k_ in EXECUTED_MATMULS and m > 0:
+                kernels[k_]["executed_tflops_incl_recompute"] = round(EXECUTED_MATMULS[k_] * 2 * D * p_sh * c / (m * 1e-3) / 1e12, 1)
+        step_ach = step_flops_total * shard_frac / (ms_per_step * 1e-3) / 1e12
+        step_block = {"achieved": step_ach, "frac": step_ach / pk["tflops"], "frac_per_clock": per_clock(step_ach, pk["tflops"]),
+                      "note": "whole step: every algorithmic FLOP of fwd+bwd counted once / device time of the step"}
         if name in ("fda_fwd", "fda_bwd"):
             # algorithmic bytes of the depth-only kernels (bf16): forward reads q and the depth
             # K/V and writes o + lse; backward reads q, o, dout and the depth K/V, writes dq and
@@ -462,49 +693,59 @@ def main():
             by = per_unit * B * Hkv * shard_frac
             ach = by / (avg_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": name, "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                        "frac": ach / pk["hbm_gbs"], "traffic": (NCU_TRAFFIC_BYTES.get(name) if args.workload in (DEFAULT_WORKLOAD, "config3_fda_T8192") and world == 1 else None), "peak_source": pk["source"],
-                        "avg_launch_ms": avg_ms,
-                        "kernels": {k: {"launches": c, "total_ms": round(m, 3)} for k, (c, m) in prof.items()}}
+                        "frac": ach / pk["hbm_gbs"], "traffic": traffic, "traffic_source": NCU_TRAFFIC_SOURCE.get(name) if traffic else None,
+                        "peak_source": pk["source"], "avg_launch_ms": avg_ms, "kernels": kernels}
         else:
+            owned = OWNED_MATMULS.get(name)
+            alg = (owned * 2 * D * p_sh) if owned is not None else 10 * D * p_sh
             ach = alg / (avg_ms * 1e-3) / 1e12
             roofline = {"bound": "tensor", "kernel": name, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
-                        "frac": ach / pk["tflops"], "traffic": (NCU_TRAFFIC_BYTES.get(name) if args.workload in (DEFAULT_WORKLOAD, "config3_fda_T8192") and world == 1 else None),
-                        "peak_source": pk["source"] + " (sustained cuBLAS bf16)", "avg_launch_ms": avg_ms,
-                        "kernels": {k: {"launches": c, "total_ms": round(m, 3)} for k, (c, m) in prof.items()}}
+                        "frac": ach / pk["tflops"], "frac_per_clock": per_clock(ach, pk["tflops"]),
+                        "owned_algorithmic_matmuls": owned, "traffic": traffic,
+                        "traffic_source": NCU_TRAFFIC_SOURCE.get(name) if traffic else None,
+                        "peak_source": pk["source"] + " (sustained cuBLAS bf16 at %s MHz)" % pk.get("peak_sm_mhz"),
+                        "avg_launch_ms": avg_ms, "step": step_block, "kernels": kernels}
 
     # ---- depth-KV overhead: the same kernels on the same q, k, v, dO with L = 0 ---------------
-    # (t_MoDA - t_seq_only) / t_MoDA, the two timed back to back in this process, twin first and
-    # full second in alternation so that both see the same package temperature
+    # (t_MoDA - t_seq_only) / t_MoDA, forward only and forward+backward, the two timed back to back
+    # in this process, twin first and full second, three alternations so that both see the same
+    # package temperature
     depth_overhead = None
     if not args.no_twin and mode != "fda" and L > 0:
-        tw = fu = 0.0
-        pairs_ms = []
+        res = {"fwd": [0.0, 0.0, []], "fwd_bwd": [0.0, 0.0, []]}
         if len(units) > 0:      # (a rank without units still joins the reduction below)
             t_twin = dict(t)
             t_twin["kd"] = None
             t_twin["vd"] = None
 
-            def timed(tt, n_steps):
+            def timed(tt, n_steps, fwd_only):
                 a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 torch.cuda.synchronize()
                 a.record()
                 for _ in range(n_steps):
-                    run_ops(tt)
+                    run_ops(tt, fwd_only)
                 b_.record()
                 torch.cuda.synchronize()
                 return a.elapsed_time(b_) / n_steps
 
-            timed(t_twin, 1)
-            pairs_ms = [(timed(t_twin, args.steps), timed(t, args.steps)) for _ in range(2)]
-            tw = sum(x for x, _ in pairs_ms) / len(pairs_ms)
-            fu = sum(y for _, y in pairs_ms) / len(pairs_ms)
+            for key, fo in (("fwd", True), ("fwd_bwd", False)):
+                if key == "fwd_bwd" and args.fwd_only:
+                    continue
+                timed(t_twin, 1, fo)
+                prs = [(timed(t_twin, args.steps, fo), timed(t, args.steps, fo)) for _ in range(3)]
+                res[key] = [sum(x for x, _ in prs) / len(prs), sum(y for _, y in prs) / len(prs), prs]
         if world > 1:
-            tt2 = torch.tensor([tw, fu], device=device, dtype=torch.float64)
+            tt2 = torch.tensor([res["fwd"][0], res["fwd"][1], res["fwd_bwd"][0], res["fwd_bwd"][1]], device=device, dtype=torch.float64)
             dist.all_reduce(tt2, op=dist.ReduceOp.MAX)
-            tw, fu = float(tt2[0].item()), float(tt2[1].item())
-        depth_overhead = {"seq_only_ms_per_step": tw, "full_ms_per_step": fu, "frac": ((fu - tw) / fu if fu > 0 else None),
-                          "pairs_ms": [[round(x, 3), round(y, 3)] for x, y in pairs_ms],
-                          "note": "same kernels, same q/k/v/dO, L = 0; (t_full - t_seq_only) / t_full"}
+            res["fwd"][0], res["fwd"][1], res["fwd_bwd"][0], res["fwd_bwd"][1] = [float(x) for x in tt2.tolist()]
+
+        def block(key):
+            tw, fu, prs = res[key]
+            return {"seq_only_ms_per_step": tw, "full_ms_per_step": fu, "frac": ((fu - tw) / fu if fu > 0 else None),
+                    "pairs_ms": [[round(x, 3), round(y, 3)] for x, y in prs]}
+        depth_overhead = dict(block("fwd_bwd"))
+        depth_overhead["forward_only"] = block("fwd")
+        depth_overhead["note"] = "same kernels, same q/k/v/dO, L = 0; (t_full - t_seq_only) / t_full; three alternations"
 
     # ---- end-to-end through the public autograd operator with host buffers -------------
     e2e = None
@@ -576,9 +817,11 @@ def main():
                 tt = torch.tensor([ems], device=device, dtype=torch.float64)
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 ems = float(tt.item())
-            e2e = {"value": step_flops_total / (ems / n_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+            sec = ems / n_e2e * 1e-3
+            e2e = {"value": step_flops_total / sec / 1e12, "unit": "TFLOP/s",
                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": n_e2e,
                    "ms_per_step": ems / n_e2e,
+                   "h2d_gbs_per_rank": h2d / sec / 1e9, "d2h_gbs_per_rank": d2h / sec / 1e9,
                    "note": "per-rank bytes; pinned host buffers; one (batch, KV-head) unit per operator call, "
                            "copies of neighbouring units on their own streams under the kernels"}
             # the pipelined results are the whole-tensor results, unit by unit
@@ -592,6 +835,23 @@ def main():
                    "error": str(exc)[:200]}
     elif world > 1:
         barrier()
+
+    # ---- secondary workloads and the reference's Triton kernels (one GPU, default run only) ----
+    other = triton_ref = None
+    if rank == 0 and world == 1 and args.workload == DEFAULT_WORKLOAD and not args.fwd_only:
+        del t
+        o = lse = None
+        torch.cuda.empty_cache()
+        if not args.no_other_workloads:
+            other = []
+            for name in OTHER_WORKLOADS:
+                try:
+                    other.append(time_workload(M, _cabi, name, device, steps=5, warmup=3, pk=pk))
+                except RuntimeError as exc:
+                    other.append({"workload": name, "error": str(exc)[:300]})
+        if not args.no_triton_baseline:
+            torch.cuda.empty_cache()
+            triton_ref = triton_baseline_in_child(args.triton_timeout)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -616,6 +876,8 @@ def main():
             "frac_of_measured_bf16_peak": value / (pk["tflops"] * world),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
             "clocks": clocks, "remeasured": remeasured, "depth_overhead": depth_overhead,
+            "device_status": dev_status,
+            "other_workloads": other, "reference_triton": triton_ref,
             "validation": {"per_unit_checksum_o_lse": [[round(float(a), 3), round(float(b), 3)] for a, b in cs_all.tolist()]},
         }
         print(json.dumps(line), flush=True)

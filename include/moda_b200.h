@@ -9,7 +9,10 @@
  * Conventions
  *   - Tensors are 4-D [B, T, H, D] with arbitrary element strides for B, T, H and a
  *     contiguous innermost D (moda_tensor4).  Pointers are DEVICE pointers, 16-byte
- *     aligned; strides must be multiples of 8 elements.  Inputs are never written.
+ *     aligned; the stride of every dimension of extent > 1 must be a positive multiple
+ *     of 8 elements (zero or negative strides, as of expanded or flipped views, are
+ *     refused with MODA_ERR_ALIGNMENT; a dimension of extent 1 may carry any stride).
+ *     Inputs are never written.
  *   - Queries are folded the reference's way (moda_v14.py:2839-2852): q is
  *     [B, T_kv*G, H, D]; query row r belongs to base position t = r / G.
  *   - depth_k / depth_v are [B, T_kv*L, H, D]; row t*L + l is layer l at position t
@@ -35,7 +38,7 @@ typedef enum moda_status {
   MODA_ERR_SHAPE = 2,       /* B/T/H/G/L out of range, T_q != T_kv*G ... */
   MODA_ERR_HEAD_DIM = 3,    /* D not in {64, 128} */
   MODA_ERR_DTYPE = 4,       /* dtype not bf16/fp16 */
-  MODA_ERR_ALIGNMENT = 5,   /* pointer not 16-byte aligned or stride not multiple of 8 */
+  MODA_ERR_ALIGNMENT = 5,   /* pointer not 16-byte aligned, or a stride not a positive multiple of 8 */
   MODA_ERR_MODE = 6,        /* unknown mode / mode-argument mismatch */
   MODA_ERR_CHUNK = 7,       /* chunk_rows not a positive multiple of G */
   MODA_ERR_WORKSPACE = 8,   /* workspace NULL or too small */
@@ -55,12 +58,17 @@ typedef enum moda_dtype { MODA_BF16 = 0, MODA_FP16 = 1 } moda_dtype;
 
 /* Kernel path selector (moda_problem.path). */
 typedef enum moda_path {
-  MODA_PATH_AUTO = 0,    /* tcgen05 kernels where they apply (D = 128), otherwise the mma.sync
+  MODA_PATH_AUTO = 0,    /* tcgen05 kernels where they apply (scale > 0), otherwise the mma.sync
                             kernels; the bandwidth kernels for MODA_DEPTH_ONLY and for the
                             own-position depth rows of MODA_CAUSAL / MODA_NONCAUSAL at G = 1
                             (whose partial result the attention kernel merges in its epilogue) */
   MODA_PATH_SIMT_MMA = 1,/* warp-level mma.sync kernels (every shape) */
-  MODA_PATH_TCGEN05 = 2  /* tcgen05/TMEM/TMA kernels; MODA_ERR_UNSUPPORTED if they do not apply */
+  MODA_PATH_TCGEN05 = 2, /* tcgen05/TMEM/TMA kernels; MODA_ERR_UNSUPPORTED if they do not apply */
+  /* As MODA_PATH_TCGEN05, with the forward kernel fixed instead of chosen by grid size: one
+     128-row query tile per CTA (two CTAs per SM), or two query tiles per CTA (one CTA per SM).
+     Both give bit-identical results; the values exist so that each can be tested on any shape. */
+  MODA_PATH_TCGEN05_ONE_TILE = 3,
+  MODA_PATH_TCGEN05_TWO_TILES = 4
 } moda_path;
 
 typedef struct moda_tensor4 {
@@ -140,7 +148,8 @@ int moda_b200_bwd(const moda_problem *prob, const moda_tensor4 *q, const moda_te
  *    exits, which is why it is kept modest.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress, with that device made current) and caches it; make that
- *    first call outside any stream capture.
+ *    first call outside any stream capture.  The cache covers device ordinals 0..63;
+ *    a larger ordinal is refused with MODA_ERR_SHAPE.
  *  - All calls on a device share the one array and it keeps the previous call's
  *    contents.  The backward writes every scratch word before reading it, so nothing
  *    needs clearing between calls; but two calls whose kernels overlap on the GPU
@@ -186,10 +195,14 @@ const char *moda_b200_kernel_name(int kernel_id);
 /*
  * Device-side status of the tcgen05 kernels.  Every wait inside those kernels (on an
  * mbarrier fed by TMA, by the tensor core or by other warps) is bounded; a wait that
- * expires records (1 << 8 | barrier id) here, the CTA releases its TMEM and returns,
- * and the remaining CTAs of the launch return at once.  0 means no wait has expired
- * since the last launch began.  SYNCHRONISES the device.  The reference has no
- * counterpart (Triton kernels do not spin on barriers they could miss).
+ * expires records (1 << 8 | barrier id) in a status word, the CTA releases its TMEM and
+ * returns, and the remaining CTAs of that launch return at once, leaving outputs
+ * unwritten.  The word is sticky: launches never clear it, it keeps the FIRST failure
+ * since it was last read, and this call returns it and resets it to 0.  A caller that
+ * wants to know that its results are valid reads it at its next synchronisation point
+ * (0 = every launch since the previous read ran to completion).  SYNCHRONISES the
+ * device.  The reference has no counterpart (Triton kernels do not spin on barriers
+ * they could miss).
  */
 int moda_b200_device_status(int *status);
 

@@ -5,6 +5,7 @@ plus ``fla.ops.moda.fda_v12.parallel_fda``; see ``moda_b200.ops``.
 """
 from .ops import (  # noqa: F401
     CHUNK_VISIBLE_QUERY_ROWS,
+    fold_qkv,
     last_launch_count,
     moda_attention,
     parallel_fda,
@@ -20,12 +21,13 @@ from .ops import (  # noqa: F401
 )
 from ._cabi import (  # noqa: F401
     MODE_CAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY, MODE_NONCAUSAL,
-    PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05, ModaLibraryError,
+    PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05, PATH_TCGEN05_ONE_TILE, PATH_TCGEN05_TWO_TILES, ModaLibraryError,
+    device_status,
 )
 
 __all__ = [
     "parallel_moda", "parallel_moda_fwd", "parallel_moda_bwd",
     "parallel_moda_chunk_visible", "parallel_moda_chunk_visible_fwd", "parallel_moda_chunk_visible_bwd",
     "parallel_fda", "parallel_fda_fwd", "parallel_fda_bwd",
-    "moda_attention", "set_kernel_path", "last_launch_count",
+    "moda_attention", "fold_qkv", "set_kernel_path", "last_launch_count", "device_status",
 ]

@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libmoda_b200.so")
 MODE_CAUSAL, MODE_NONCAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY = 0, 1, 2, 3
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05 = 0, 1, 2
+PATH_TCGEN05_ONE_TILE, PATH_TCGEN05_TWO_TILES = 3, 4   # tcgen05 with the forward kernel fixed (tests)
 STATIC_SCRATCH_BYTES = 8 << 20   # MODA_B200_STATIC_SCRATCH_BYTES
 
 # every symbol include/moda_b200.h declares
@@ -142,7 +143,11 @@ def profile_end() -> dict:
 
 
 def device_status() -> int:
-    """Status word of the tcgen05 kernels' bounded waits (0 = none expired); synchronises."""
+    """Sticky status word of the tcgen05 kernels' bounded waits; synchronises.
+
+    0 = every launch since the previous read ran to completion.  Non-zero = the first wait that
+    expired since then ((1 << 8) | barrier id): that launch returned early and left outputs
+    unwritten.  Reading resets the word, so callers poll it at their next synchronisation point."""
     v = ctypes.c_int(0)
     check(load().moda_b200_device_status(ctypes.byref(v)), "moda_b200_device_status")
     return int(v.value)

@@ -12,7 +12,6 @@
 #ifndef MODA_NO_TCGEN05
 #include "tc_kernels.cuh"
 #include "tc_bwd_kernels.cuh"
-#include "tc_fwd2_kernel.cuh"
 #include "tc_fwd3_kernel.cuh"
 #endif
 
@@ -25,11 +24,29 @@ thread_local int g_last_cuda_error = 0;
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int check_tensor(const moda_tensor4* t, bool required) {
+// A tensor of extents [B, T, H, D].  A dimension of extent 1 may carry any stride (its index is
+// always 0); every other stride must be a positive multiple of 8 elements.  Zero or negative
+// strides (expanded / flipped views) are refused: the TMA tensor maps cannot express them and a
+// gradient written through one would alias.
+int check_tensor(const moda_tensor4* t, bool required, int64_t B, int64_t T, int64_t H) {
   if (t == nullptr || t->data == nullptr) return required ? MODA_ERR_NULL : MODA_OK;
   if (!aligned16(t->data)) return MODA_ERR_ALIGNMENT;
-  if ((t->stride_b % 8) || (t->stride_t % 8) || (t->stride_h % 8)) return MODA_ERR_ALIGNMENT;
+  const int64_t ext[3] = {B, T, H}, str[3] = {t->stride_b, t->stride_t, t->stride_h};
+  for (int i = 0; i < 3; ++i)
+    if (ext[i] > 1 && (str[i] <= 0 || (str[i] % 8) != 0)) return MODA_ERR_ALIGNMENT;
   return MODA_OK;
+}
+
+// Multiprocessor count of a device (queried once per device).
+int sm_count(int device) {
+  static std::mutex mu;
+  static int cached[64] = {0};
+  std::lock_guard<std::mutex> lk(mu);
+  if (device >= 0 && device < 64 && cached[device] > 0) return cached[device];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) return 0;
+  if (device >= 0 && device < 64) cached[device] = n;
+  return n;
 }
 
 View to_view(const moda_tensor4* t) {
@@ -51,7 +68,7 @@ int check_problem(const moda_problem* pr) {
   if (pr->mode == MODA_CHUNK_VISIBLE) {
     if (pr->chunk_rows < 1 || pr->chunk_rows % pr->G != 0) return MODA_ERR_CHUNK;
   }
-  if (pr->path < MODA_PATH_AUTO || pr->path > MODA_PATH_TCGEN05) return MODA_ERR_MODE;
+  if (pr->path < MODA_PATH_AUTO || pr->path > MODA_PATH_TCGEN05_TWO_TILES) return MODA_ERR_MODE;
   if (!(pr->scale == pr->scale)) return MODA_ERR_SHAPE;  // NaN scale
   return MODA_OK;
 }
@@ -90,10 +107,10 @@ int simt_fwd(const Params& p, cudaStream_t st) {
 }
 
 template <typename T, int D>
-int simt_delta(const Params& p, cudaStream_t st) {
+int simt_delta(const Params& p, int n_sm, cudaStream_t st) {
   const int64_t rows = (int64_t)p.B * p.T_q * p.H;
-  int blocks = (int)((rows + 7) / 8);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  const int64_t want = (rows + 7) / 8, cap = (int64_t)n_sm * 16;
+  const int blocks = (int)(want < cap ? want : cap);
   {
     prof::Scope ps(prof::kDelta, st);
     simt::delta_kernel<T, D><<<blocks, 256, 0, st>>>(p);
@@ -104,8 +121,8 @@ int simt_delta(const Params& p, cudaStream_t st) {
 }
 
 template <typename T, int D>
-int simt_bwd(const Params& p, cudaStream_t st) {
-  if (int rc = simt_delta<T, D>(p, st)) return rc;
+int simt_bwd(const Params& p, int n_sm, cudaStream_t st) {
+  if (int rc = simt_delta<T, D>(p, n_sm, st)) return rc;
   {
     auto kern = simt::dq_kernel<T, D>;
     constexpr size_t smem = simt::dq_smem<T, D>();
@@ -140,13 +157,13 @@ int simt_fwd_d(const Params& p, int D, cudaStream_t st) {
   return D == 64 ? simt_fwd<T, 64>(p, st) : simt_fwd<T, 128>(p, st);
 }
 template <typename T>
-int simt_bwd_d(const Params& p, int D, cudaStream_t st) {
-  return D == 64 ? simt_bwd<T, 64>(p, st) : simt_bwd<T, 128>(p, st);
+int simt_bwd_d(const Params& p, int D, int n_sm, cudaStream_t st) {
+  return D == 64 ? simt_bwd<T, 64>(p, n_sm, st) : simt_bwd<T, 128>(p, n_sm, st);
 }
 
 // ----------------------------------------------------------------- depth-only (FDA) bandwidth path
 bool use_fda(const moda_problem* pr, bool is_bwd) {
-  if (pr->mode != MODA_DEPTH_ONLY || pr->path == MODA_PATH_SIMT_MMA || pr->path == MODA_PATH_TCGEN05) return false;
+  if (pr->mode != MODA_DEPTH_ONLY || pr->path != MODA_PATH_AUTO) return false;
   return !is_bwd || fda::bwd_supported(pr->G, pr->D);
 }
 
@@ -158,7 +175,7 @@ bool use_fda(const moda_problem* pr, bool is_bwd) {
 // spans 128 positions and has to multiply against 128 L depth columns of which each row uses L
 // (L extra key tiles per query tile; at T = 197, L = 11 that is 11 tiles beside 2 sequence
 // tiles).  With G = 4 the tile spans 32 positions, the extra tiles are a small share of the
-// sequence tiles, and one launch is faster (measured at T = 4096, L = 24: 0.30 ms against 0.45).
+// sequence tiles, and one launch is faster.
 bool split_depth(const moda_problem* pr, bool is_bwd) {
   if (pr->path != MODA_PATH_AUTO || pr->L <= 0 || pr->G != 1) return false;
   if (pr->mode != MODA_CAUSAL && pr->mode != MODA_NONCAUSAL) return false;
@@ -173,10 +190,10 @@ Params sequence_part(const Params& p) {
 }
 
 template <typename T, int D>
-int fda_fwd(const Params& p, cudaStream_t st) {
+int fda_fwd(const Params& p, int n_sm, cudaStream_t st) {
   const int64_t units = (int64_t)p.B * p.T_kv * p.H;
-  int blocks = (int)((units + 7) / 8);
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  const int64_t want = (units + 7) / 8, cap = (int64_t)n_sm * 32;
+  const int blocks = (int)(want < cap ? want : cap);
   {
     prof::Scope ps(prof::kFdaFwd, st);
     fda::fwd_kernel<T, D><<<blocks, 256, 0, st>>>(p);
@@ -187,10 +204,10 @@ int fda_fwd(const Params& p, cudaStream_t st) {
 }
 
 template <typename T, int D>
-int fda_bwd(const Params& p, cudaStream_t st) {
+int fda_bwd(const Params& p, int n_sm, cudaStream_t st) {
   const int64_t units = (int64_t)p.B * p.T_kv * p.H;
-  int blocks = (int)((units + 3) / 4);
-  if (blocks > 148 * 64) blocks = 148 * 64;
+  const int64_t want = (units + 3) / 4, cap = (int64_t)n_sm * 64;
+  const int blocks = (int)(want < cap ? want : cap);
   {
     prof::Scope ps(prof::kFdaBwd, st);
     if (p.G == 1) fda::bwd_kernel<T, D, 1><<<blocks, 128, 0, st>>>(p);
@@ -203,9 +220,9 @@ int fda_bwd(const Params& p, cudaStream_t st) {
 }
 
 template <typename T>
-int fda_dispatch(const Params& p, int D, bool is_bwd, cudaStream_t st) {
-  if (is_bwd) return D == 64 ? fda_bwd<T, 64>(p, st) : fda_bwd<T, 128>(p, st);
-  return D == 64 ? fda_fwd<T, 64>(p, st) : fda_fwd<T, 128>(p, st);
+int fda_dispatch(const Params& p, int D, bool is_bwd, int n_sm, cudaStream_t st) {
+  if (is_bwd) return D == 64 ? fda_bwd<T, 64>(p, n_sm, st) : fda_bwd<T, 128>(p, n_sm, st);
+  return D == 64 ? fda_fwd<T, 64>(p, n_sm, st) : fda_fwd<T, 128>(p, n_sm, st);
 }
 
 int resolve_path(const moda_problem* pr, bool is_bwd) {
@@ -215,23 +232,19 @@ int resolve_path(const moda_problem* pr, bool is_bwd) {
   const bool ok = false;
 #endif
   if (pr->path == MODA_PATH_SIMT_MMA) return MODA_PATH_SIMT_MMA;
-  if (pr->path == MODA_PATH_TCGEN05) return ok ? MODA_PATH_TCGEN05 : -MODA_ERR_UNSUPPORTED;
+  if (pr->path >= MODA_PATH_TCGEN05) return ok ? MODA_PATH_TCGEN05 : -MODA_ERR_UNSUPPORTED;
   return ok ? MODA_PATH_TCGEN05 : MODA_PATH_SIMT_MMA;
 }
 
 #ifndef MODA_NO_TCGEN05
-int tc_forward(const Params& p, const moda_problem* prob, cudaStream_t st) {
-  // Three forwards exist.  tc::fwd3 (two 128-row query tiles per CTA, one CTA per SM, one MMA warp
-  // ordering the work of both tiles) is the fastest once its grid fills the GPU: config 4 forward
-  // 33.1 ms against 35.2 ms.  tc::fwd (one query tile per CTA, two CTAs per SM) has twice as many,
-  // smaller CTAs and serves the small problems.  tc::fwd2 (Q in TMEM, column-split softmax) is
-  // kept selectable: 36.8 ms.  Bring-up switch bits force one of them: 32, 128, 64.
-  const int variant = tc::debug_state().variant;
-  if (variant & 64) return tc::fwd2(p, prob, st, &g_last_launches, &g_last_cuda_error);
-  bool two_tiles = (variant & 128) != 0;
-  if (!(variant & (32 | 128))) {
-    int n_sm = 0;
-    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, prob->device) != cudaSuccess) n_sm = 0;
+int tc_forward(const Params& p, const moda_problem* prob, int n_sm, cudaStream_t st) {
+  // Two forwards.  tc::fwd3 (two 128-row query tiles per CTA, one CTA per SM, one MMA warp
+  // ordering the work of both tiles) is the faster one once its grid fills the GPU; tc::fwd
+  // (one query tile per CTA, two CTAs per SM) has twice as many, smaller CTAs and serves the
+  // small problems.  Both use the same softmax arithmetic, so a result does not depend on the
+  // choice.  MODA_PATH_TCGEN05_ONE_TILE / _TWO_TILES force one of them.
+  bool two_tiles = prob->path == MODA_PATH_TCGEN05_TWO_TILES;
+  if (prob->path != MODA_PATH_TCGEN05_ONE_TILE && prob->path != MODA_PATH_TCGEN05_TWO_TILES) {
     const int64_t n_cta = (int64_t)((p.T_q + 255) / 256) * p.H * p.B;
     two_tiles = n_sm > 0 && n_cta >= n_sm;
   }
@@ -272,12 +285,13 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (int rc = check_problem(prob)) return rc;
   const bool need_seq = prob->mode != MODA_DEPTH_ONLY;
   const bool need_dep = prob->L > 0;
-  if (int rc = check_tensor(q, true)) return rc;
-  if (int rc = check_tensor(k, need_seq)) return rc;
-  if (int rc = check_tensor(v, need_seq)) return rc;
-  if (int rc = check_tensor(depth_k, need_dep)) return rc;
-  if (int rc = check_tensor(depth_v, need_dep)) return rc;
-  if (int rc = check_tensor(o, true)) return rc;
+  const int64_t Tq = (int64_t)prob->T_kv * prob->G, Tk = prob->T_kv, Td = (int64_t)prob->T_kv * prob->L;
+  if (int rc = check_tensor(q, true, prob->B, Tq, prob->H)) return rc;
+  if (int rc = check_tensor(k, need_seq, prob->B, Tk, prob->H)) return rc;
+  if (int rc = check_tensor(v, need_seq, prob->B, Tk, prob->H)) return rc;
+  if (int rc = check_tensor(depth_k, need_dep, prob->B, Td, prob->H)) return rc;
+  if (int rc = check_tensor(depth_v, need_dep, prob->B, Td, prob->H)) return rc;
+  if (int rc = check_tensor(o, true, prob->B, Tq, prob->H)) return rc;
   if (lse == nullptr) return MODA_ERR_NULL;
   const int path = resolve_path(prob, false);
   if (path < 0) return -path;
@@ -292,23 +306,18 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (!guard.ok) return cuda_fail(guard.err);
   g_last_launches = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int n_sm = sm_count(prob->device);
+  if (n_sm <= 0) return cuda_fail(cudaErrorInvalidDevice);
   if (use_fda(prob, false))
-    return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, st)
-                                    : fda_dispatch<__half>(p, prob->D, false, st);
+    return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, n_sm, st)
+                                    : fda_dispatch<__half>(p, prob->D, false, n_sm, st);
   if (split_depth(prob, false)) {
-    if (int rc = prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, st)
-                                          : fda_dispatch<__half>(p, prob->D, false, st)) return rc;
+    if (int rc = prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, false, n_sm, st)
+                                          : fda_dispatch<__half>(p, prob->D, false, n_sm, st)) return rc;
     p = sequence_part(p);
-#ifndef MODA_NO_TCGEN05
-    if (path == MODA_PATH_TCGEN05) return tc_forward(p, prob, st);
-#endif
-    return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)
-                                    : simt_fwd_d<__half>(p, prob->D, st);
   }
 #ifndef MODA_NO_TCGEN05
-  if (path == MODA_PATH_TCGEN05) {
-    return tc_forward(p, prob, st);
-  }
+  if (path == MODA_PATH_TCGEN05) return tc_forward(p, prob, n_sm, st);
 #endif
   return prob->dtype == MODA_BF16 ? simt_fwd_d<__nv_bfloat16>(p, prob->D, st)
                                   : simt_fwd_d<__half>(p, prob->D, st);
@@ -334,18 +343,20 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (int rc = check_problem(prob)) return rc;
   const bool need_seq = prob->mode != MODA_DEPTH_ONLY;
   const bool need_dep = prob->L > 0;
-  if (int rc = check_tensor(q, true)) return rc;
-  if (int rc = check_tensor(k, need_seq)) return rc;
-  if (int rc = check_tensor(v, need_seq)) return rc;
-  if (int rc = check_tensor(depth_k, need_dep)) return rc;
-  if (int rc = check_tensor(depth_v, need_dep)) return rc;
-  if (int rc = check_tensor(o, true)) return rc;
-  if (int rc = check_tensor(dout, true)) return rc;
-  if (int rc = check_tensor(dq, true)) return rc;
-  if (int rc = check_tensor(dk, need_seq)) return rc;
-  if (int rc = check_tensor(dv, need_seq)) return rc;
-  if (int rc = check_tensor(d_depth_k, need_dep)) return rc;
-  if (int rc = check_tensor(d_depth_v, need_dep)) return rc;
+  const int64_t Tq = (int64_t)prob->T_kv * prob->G, Tk = prob->T_kv, Td = (int64_t)prob->T_kv * prob->L;
+  const int Bn = prob->B, Hn = prob->H;
+  if (int rc = check_tensor(q, true, Bn, Tq, Hn)) return rc;
+  if (int rc = check_tensor(k, need_seq, Bn, Tk, Hn)) return rc;
+  if (int rc = check_tensor(v, need_seq, Bn, Tk, Hn)) return rc;
+  if (int rc = check_tensor(depth_k, need_dep, Bn, Td, Hn)) return rc;
+  if (int rc = check_tensor(depth_v, need_dep, Bn, Td, Hn)) return rc;
+  if (int rc = check_tensor(o, true, Bn, Tq, Hn)) return rc;
+  if (int rc = check_tensor(dout, true, Bn, Tq, Hn)) return rc;
+  if (int rc = check_tensor(dq, true, Bn, Tq, Hn)) return rc;
+  if (int rc = check_tensor(dk, need_seq, Bn, Tk, Hn)) return rc;
+  if (int rc = check_tensor(dv, need_seq, Bn, Tk, Hn)) return rc;
+  if (int rc = check_tensor(d_depth_k, need_dep, Bn, Td, Hn)) return rc;
+  if (int rc = check_tensor(d_depth_v, need_dep, Bn, Td, Hn)) return rc;
   if (lse == nullptr) return MODA_ERR_NULL;
   size_t need = 0;
   if (int rc = moda_b200_bwd_workspace_bytes(prob, &need)) return rc;
@@ -368,22 +379,24 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (!guard.ok) return cuda_fail(guard.err);
   g_last_launches = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int n_sm = sm_count(prob->device);
+  if (n_sm <= 0) return cuda_fail(cudaErrorInvalidDevice);
   if (use_fda(prob, true))
-    return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, st)
-                                    : fda_dispatch<__half>(p, prob->D, true, st);
+    return prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, n_sm, st)
+                                    : fda_dispatch<__half>(p, prob->D, true, n_sm, st);
   if (split_depth(prob, true)) {   // depth rows' dq share, d_depth_k, d_depth_v; then the sequence part
-    if (int rc = prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, st)
-                                          : fda_dispatch<__half>(p, prob->D, true, st)) return rc;
+    if (int rc = prob->dtype == MODA_BF16 ? fda_dispatch<__nv_bfloat16>(p, prob->D, true, n_sm, st)
+                                          : fda_dispatch<__half>(p, prob->D, true, n_sm, st)) return rc;
     p = sequence_part(p);
   }
 #ifndef MODA_NO_TCGEN05
   if (path == MODA_PATH_TCGEN05) {
     void* extra = reinterpret_cast<unsigned char*>(workspace) + delta_bytes(prob);
-    return tc::bwd(p, prob, extra, st, &g_last_launches, &g_last_cuda_error);
+    return tc::bwd(p, prob, extra, n_sm, st, &g_last_launches, &g_last_cuda_error);
   }
 #endif
-  return prob->dtype == MODA_BF16 ? simt_bwd_d<__nv_bfloat16>(p, prob->D, st)
-                                  : simt_bwd_d<__half>(p, prob->D, st);
+  return prob->dtype == MODA_BF16 ? simt_bwd_d<__nv_bfloat16>(p, prob->D, n_sm, st)
+                                  : simt_bwd_d<__half>(p, prob->D, n_sm, st);
 }
 
 int moda_b200_profile_begin(void) {
@@ -432,17 +445,6 @@ int moda_b200_device_status(int* status) {
   *status = v;
 #else
   *status = 0;
-#endif
-  return MODA_OK;
-}
-
-// Bring-up aid, not part of the public header: `dump` (device, 128*128 floats, may be NULL)
-// receives the raw S tile of the first key tile of CTA (0,0,0) of the tcgen05 forward;
-// variant 1 routes P through shared memory instead of TMEM.
-int moda_b200_debug_set(void* dump, int variant) {
-#ifndef MODA_NO_TCGEN05
-  tc::debug_state().dump = reinterpret_cast<float*>(dump);
-  tc::debug_state().variant = variant;
 #endif
   return MODA_OK;
 }

@@ -1,4 +1,4 @@
-// tcgen05 / TMEM / TMA backward kernels of MoDA for sm_100a (D = 128, bf16 or fp16).
+// tcgen05 / TMEM / TMA backward kernels of MoDA for sm_100a (D = 64 or 128, bf16 or fp16).
 //
 // Like the reference (moda_v14.py:1470-1842) the backward is a row-statistics pass, a
 // query-parallel dq kernel and a key-parallel dk/dv kernel; every output row has one
@@ -34,9 +34,9 @@ namespace tc {
 constexpr int kStep = 64;                      // keys (dq) or query rows (dkv) per pipeline step
 constexpr int kDqRing = 6;                     // dq: ring of {K, V} step tiles
 constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delta} step tiles
-constexpr uint32_t kStepTile = 64 * 128 * 2;   // one [64 x 128] 16-bit tile (two 8 KB boxes)
-constexpr uint32_t kStepHalf = kStepTile / 2;
-constexpr uint32_t kDkvSlot = 2 * kStepTile + 512;
+constexpr uint32_t kStepHalf = 64 * 64 * 2;    // one TMA box of a step tile: [64 rows x 64 elements]
+template <int D> __host__ __device__ constexpr uint32_t step_tile() { return (uint32_t)(D / 64) * kStepHalf; }   // [64 x D] 16-bit tile
+constexpr uint32_t kScoreTile = 128 * 64 * 2;  // [128 x 64] 16-bit tile of dS, P^T or dS^T (K-major, 128 B per row)
 constexpr int kDqThreads = 352;                // 8 softmax warps + score-MMA, TMA and update-MMA warps
 
 struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
@@ -60,8 +60,8 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // delta = rowsum(o * dO) from the stored o, and lse, both transposed to [B, H, T_qp] so that the
 // backward kernels fetch 64 rows of one (b, h) with one 256-byte bulk copy.  Eight lanes per row,
 // four rows per warp, 32 consecutive rows of one (b, h) per block iteration; each lane has two
-// 16-byte loads of o and two of dO in flight.
-template <typename T>
+// 16-byte loads of o and two of dO in flight (one of each for D = 64).
+template <typename T, int D>
 __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params p, float* delta_t, float* lse_t, int T_qp) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, sub = lane & 7, grp = lane >> 3;
   const uint32_t groups_per_bh = (uint32_t)T_qp / 32u;             // T_qp is a multiple of 64
@@ -74,14 +74,21 @@ __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params
     if (r < p.T_q) {
       const T* po = reinterpret_cast<const T*>(p.o.ptr) + p.o.off(b, r, h);
       const T* pd = reinterpret_cast<const T*>(p.dout.ptr) + p.dout.off(b, r, h);
-      const uint4 a0 = *reinterpret_cast<const uint4*>(po + sub * 8), a1 = *reinterpret_cast<const uint4*>(po + 64 + sub * 8);
-      const uint4 d0 = *reinterpret_cast<const uint4*>(pd + sub * 8), d1 = *reinterpret_cast<const uint4*>(pd + 64 + sub * 8);
-      const uint32_t av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      const uint32_t dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+      uint4 a4[D / 64], d4[D / 64];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float2 x = Pack<T>::unpack(av[i]), y = Pack<T>::unpack(dv[i]);
-        s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+      for (int i = 0; i < D / 64; ++i) {
+        a4[i] = *reinterpret_cast<const uint4*>(po + 64 * i + sub * 8);
+        d4[i] = *reinterpret_cast<const uint4*>(pd + 64 * i + sub * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < D / 64; ++i) {
+        const uint32_t av[4] = {a4[i].x, a4[i].y, a4[i].z, a4[i].w};
+        const uint32_t dv[4] = {d4[i].x, d4[i].y, d4[i].z, d4[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = Pack<T>::unpack(av[j]), y = Pack<T>::unpack(dv[j]);
+          s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+        }
       }
       if (sub == 0) l = p.lse[((int64_t)b * p.T_q + r) * p.H + h];
     }
@@ -117,27 +124,28 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 // ============================================================================ dq
 // grid (ceil(T_q/128), H, B), 352 threads.  TMEM (512 columns):
 //   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32);
-//   [256, 384) dQ (fp32);  [384, 448) Q (16-bit A operand);  [448, 512) dO (16-bit A operand).
-// Shared memory: ring of kDqRing x {K step tile, V step tile} (32 KB per slot), then two
+//   [256, 256+D) dQ (fp32);  [384, 384+D/2) Q (16-bit A operand);  [448, 448+D/2) dO (16-bit A operand).
+// Shared memory: ring of kDqRing x {K step tile, V step tile} ([64 x D] each), then two
 // [128 x 64] dS tiles (K-major, 128-byte swizzle).  A softmax warpgroup releases its TMEM stage
 // as soon as it has the scores in registers, so the next-but-one score MMAs overlap its math;
 // dS reaches the update MMA through shared memory.
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kDqThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
           const float* lse_t, int T_qp) {
   constexpr int R = kDqRing;
   constexpr BwdBars B_(R);
+  constexpr uint32_t kStepTile = step_tile<D>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {   // the 128-byte swizzle needs 1024-byte aligned tiles
-    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    if (threadIdx.x == 0) record_failure(2 << 8);
     return;
   }
   const uint32_t sRing = base;
-  const uint32_t ds_off = R * 2 * kStepTile;            // two dS tiles of kStepTile bytes
+  const uint32_t ds_off = R * 2 * kStepTile;            // two dS tiles of kScoreTile bytes
   const uint32_t sDS = base + ds_off;
-  const uint32_t ctl_off = ds_off + 2 * kStepTile;
+  const uint32_t ctl_off = ds_off + 2 * kScoreTile;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
@@ -206,10 +214,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         if (elect_one()) {
           mbar_expect_tx(bar, 2 * kStepTile);
-          tma_load_4d(dst, mk, bar, 0, h, row, b);
-          tma_load_4d(dst + kStepHalf, mk, bar, 64, h, row, b);
-          tma_load_4d(dst + kStepTile, mv, bar, 0, h, row, b);
-          tma_load_4d(dst + kStepTile + kStepHalf, mv, bar, 64, h, row, b);
+          tma_load_tile<D>(dst, mk, bar, kStepHalf, h, row, b);
+          tma_load_tile<D>(dst + kStepTile, mv, bar, kStepHalf, h, row, b);
         }
         __syncwarp();
         issued = i + 1;
@@ -237,7 +243,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
+          for (int kk = 0; kk < D / 16; ++kk) {
             mma_ts(tS, tmem_Q + kk * 8, desc_add(dk, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
             mma_ts(tP, tmem_dO + kk * 8, desc_add(dv, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           }
@@ -251,13 +257,13 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major.  A warp of
     // its own, so that an update never waits behind the issue of the next scores.
     if (n > 0) {
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      constexpr uint32_t idesc_t = instr_desc(fmt, D, true);
       bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
         if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
         tc_fence_after();
         const uint32_t slot = j % R;
-        const uint64_t da = desc_kmajor(sDS + (j & 1) * kStepTile);
+        const uint64_t da = desc_kmajor(sDS + (j & 1) * kScoreTile);
         const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
         if (elect_one()) {
 #pragma unroll
@@ -277,22 +283,22 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     const int r = r0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     {   // stage this thread's Q row (warpgroup 0) or dO row (warpgroup 1) into TMEM as an A operand
-      uint32_t regs[64];
+      uint32_t regs[D / 2];
       if (r < p.T_q) {
         const View& src = (wg == 0) ? p.q : p.dout;
         const uint4* g4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(src.ptr) + src.off(b, r, h));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < D / 8; ++i) {
           const uint4 v4 = g4[i];
           regs[4 * i] = v4.x; regs[4 * i + 1] = v4.y; regs[4 * i + 2] = v4.z; regs[4 * i + 3] = v4.w;
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) regs[i] = 0u;
+        for (int i = 0; i < D / 2; ++i) regs[i] = 0u;
       }
       const uint32_t dst = ((wg == 0) ? tmem_Q : tmem_dO) + lane_addr;
       tmem_st32<0>(dst, regs);
-      tmem_st32<32>(dst + 32, regs);
+      if constexpr (D == 128) tmem_st32<D / 2 - 32>(dst + 32, regs);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars + 8 * B_.res);
@@ -346,7 +352,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         if (!ok) break;
       }
       {   // row of the K-major, 128B-swizzled [128 x 64] tile: 16-byte chunk c lives at chunk c ^ (row & 7)
-        unsigned char* prow = smem_raw + ds_off + (i & 1) * kStepTile + row * 128;
+        unsigned char* prow = smem_raw + ds_off + (i & 1) * kScoreTile + row * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch)
           *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
@@ -359,7 +365,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       tc_fence_after();
       T* gdq = reinterpret_cast<T*>(p.dq.ptr) + p.dq.off(b, r, h);
 #pragma unroll
-      for (int q4 = 2 * wg; q4 < 2 * wg + 2; ++q4) {   // each warpgroup stores half of the row
+      for (int q4 = (D / 64) * wg; q4 < (D / 64) * (wg + 1); ++q4) {   // each warpgroup stores half of the row
         uint32_t ov[32];
         tmem_ld32<0>(tmem_dQ + lane_addr + q4 * 32, ov);
         tmem_wait_ld();
@@ -384,24 +390,25 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 // =========================================================================== dk / dv
 // grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 352 threads; key tiles of 128.
 // TMEM (512 columns): [0, 64) S^T and [64, 128) dP^T (one fp32 score stage);
-//   [128, 256) dV; [256, 384) dK; [384, 448) K and [448, 512) V rows as 16-bit A operands.
+//   [128, 128+D) dV; [256, 256+D) dK; [384, 384+D/2) K and [448, 448+D/2) V rows as 16-bit A operands.
 // Shared memory: ring of kDkvRing x {Q step tile, dO step tile}; two {P^T, dS^T} tile pairs
 // ([128 keys x 64 rows], K-major, 128-byte swizzle), one per softmax warpgroup; the ring of
 // {64 lse, 64 delta}.  A warpgroup releases the score stage as soon as the scores are in its
 // registers, so the next step's score MMAs overlap its math; P^T and dS^T reach the update
 // MMAs through shared memory.
-constexpr uint32_t kDkvPairBytes = 2 * kStepTile;   // P^T tile + dS^T tile
+constexpr uint32_t kDkvPairBytes = 2 * kScoreTile;   // P^T tile + dS^T tile
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kDqThreads, 1)
 dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
            const float* lse_t, int T_qp, int n_seq_key_tiles) {
   constexpr int R = kDkvRing;
   constexpr BwdBars B_(R);
+  constexpr uint32_t kStepTile = step_tile<D>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {
-    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    if (threadIdx.x == 0) record_failure(2 << 8);
     return;
   }
   const uint32_t sRing = base;
@@ -479,10 +486,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         const uint32_t st = sStat + slot * 512;
         if (elect_one()) {
           mbar_expect_tx(bar, 2 * kStepTile + 512);
-          tma_load_4d(dst, &maps.q, bar, 0, h, row, b);
-          tma_load_4d(dst + kStepHalf, &maps.q, bar, 64, h, row, b);
-          tma_load_4d(dst + kStepTile, &maps.dout, bar, 0, h, row, b);
-          tma_load_4d(dst + kStepTile + kStepHalf, &maps.dout, bar, 64, h, row, b);
+          tma_load_tile<D>(dst, &maps.q, bar, kStepHalf, h, row, b);
+          tma_load_tile<D>(dst + kStepTile, &maps.dout, bar, kStepHalf, h, row, b);
           bulk_load(st, lse_t + stat_base + row, 256, bar);
           bulk_load(st + 256, delta_t + stat_base + row, 256, bar);
         }
@@ -511,7 +516,7 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         const uint64_t dq = desc_kmajor(sQ), ddo = desc_kmajor(sQ + kStepTile);
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
+          for (int kk = 0; kk < D / 16; ++kk) {
             mma_ts(tmem_S, tmem_K + kk * 8, desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
             mma_ts(tmem_P, tmem_V + kk * 8, desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           }
@@ -525,14 +530,14 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     // dV += P^T(j) dO(j) and dK += dS^T(j) Q(j): A = tiles written by warpgroup j&1, B = the
     // step tiles read MN-major.
     if (n > 0) {
-      constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+      constexpr uint32_t idesc_t = instr_desc(fmt, D, true);
       bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
         if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
         tc_fence_after();
         const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
         const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);
-        const uint64_t dpt = desc_kmajor(sPT + (j & 1) * kDkvPairBytes), dst = desc_kmajor(sPT + (j & 1) * kDkvPairBytes + kStepTile);
+        const uint64_t dpt = desc_kmajor(sPT + (j & 1) * kDkvPairBytes), dst = desc_kmajor(sPT + (j & 1) * kDkvPairBytes + kScoreTile);
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
@@ -553,22 +558,22 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     const int key = c0 + row;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     {   // stage this thread's K row (warpgroup 0) or V row (warpgroup 1) into TMEM as an A operand
-      uint32_t regs[64];
+      uint32_t regs[D / 2];
       if (key < n_keys) {
         const View& src = (wg == 0) ? (is_dep ? p.kd : p.k) : (is_dep ? p.vd : p.v);
         const uint4* g4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(src.ptr) + src.off(b, key, h));
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < D / 8; ++i) {
           const uint4 v4 = g4[i];
           regs[4 * i] = v4.x; regs[4 * i + 1] = v4.y; regs[4 * i + 2] = v4.z; regs[4 * i + 3] = v4.w;
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) regs[i] = 0u;
+        for (int i = 0; i < D / 2; ++i) regs[i] = 0u;
       }
       const uint32_t dst = ((wg == 0) ? tmem_K : tmem_V) + lane_addr;
       tmem_st32<0>(dst, regs);
-      tmem_st32<32>(dst + 32, regs);
+      if constexpr (D == 128) tmem_st32<D / 2 - 32>(dst + 32, regs);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bars + 8 * B_.res);
@@ -641,7 +646,7 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         for (int ch = 0; ch < 8; ++ch) {
           const uint32_t o = (uint32_t)((ch ^ (row & 7)) << 4);
           *reinterpret_cast<uint4*>(prow + o) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
-          *reinterpret_cast<uint4*>(prow + kStepTile + o) = make_uint4(pd[4 * ch], pd[4 * ch + 1], pd[4 * ch + 2], pd[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(prow + kScoreTile + o) = make_uint4(pd[4 * ch], pd[4 * ch + 1], pd[4 * ch + 2], pd[4 * ch + 3]);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -655,7 +660,7 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;      // warpgroup 0 stores dV, warpgroup 1 dK
       const float mul = (wg == 0) ? 1.f : p.scale;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < D / 32; ++q4) {
         uint32_t ov32[32];
         tmem_ld32<0>(tsrc + lane_addr + q4 * 32, ov32);
         tmem_wait_ld();
@@ -713,10 +718,10 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
 // grid (min(blocks, SMs)), 320 threads.  TMEM (512 columns): stage s at [128 s, 128 s + 64)
 // S^T / P^T and [128 s + 64, 128 s + 128) dP^T / dS^T (the packed 16-bit P^T / dS^T of query
 // columns 32 g .. + 31 sit in the first 16 columns of that group's 32 fp32 columns);
-// [256,384) dVd, [384,512) dKd.
+// [256,256+D) dVd, [384,384+D) dKd.
 enum DgBar : int { kDgRes = 0, kDgFull0 = 1, kDgEmpty0 = 3, kDgS0 = 5, kDgP0 = 7, kDgU = 9, kDgE = 10, kDgQFree = 11, kDgCount = 12 };
-constexpr uint32_t kDgOutOff = 2 * kStepTile + 1024 + 2 * 2 * kTileBytes;      // {dVd tile, dKd tile} staging
-constexpr uint32_t kDgSmem = kDgOutOff + 2 * kTileBytes + 128;
+template <int D> __host__ __device__ constexpr uint32_t dg_out_off() { return 2 * step_tile<D>() + 1024 + 2 * 2 * tile_bytes<D>(); }   // {dVd tile, dKd tile} staging
+template <int D> __host__ __device__ constexpr uint32_t dg_smem() { return dg_out_off<D>() + 2 * tile_bytes<D>() + 128; }
 struct DgOutMaps { CUtensorMap dkd, dvd; };                                     // 32-row boxes
 constexpr int kDgThreads = 320;                                                 // 8 softmax/store warps, MMA warp, TMA warp
 
@@ -737,20 +742,21 @@ __device__ __forceinline__ DgBlock dg_block(const Params& p, int idx, int n_xb, 
   return k;
 }
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kDgThreads, 1)
 depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps,
                   const __grid_constant__ DgOutMaps omaps, const float* delta_t, const float* lse_t, int T_qp) {
+  constexpr uint32_t kStepTile = step_tile<D>(), kTile = tile_bytes<D>(), kDgOutOff = dg_out_off<D>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {
-    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    if (threadIdx.x == 0) record_failure(2 << 8);
     return;
   }
   const uint32_t sQ = base, sDO = base + kStepTile, sStat = base + 2 * kStepTile;
   const uint32_t sKV = base + 2 * kStepTile + 1024;          // 2 x {Kd tile, Vd tile}
   const uint32_t sOut = base + kDgOutOff;
-  const uint32_t ctl_off = kDgOutOff + 2 * kTileBytes;
+  const uint32_t ctl_off = kDgOutOff + 2 * kTile;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 104);
@@ -807,13 +813,11 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
         const uint32_t slot = gi & 1;
         if (gi >= 2 && !mbar_wait(bars + 8 * (kDgEmpty0 + slot), ((gi >> 1) - 1) & 1, abort_flag, kDgEmpty0 + slot)) return false;
         const int row = k.k_lo + i * kBN;
-        const uint32_t dst = sKV + slot * 2 * kTileBytes, bar = bars + 8 * (kDgFull0 + slot);
+        const uint32_t dst = sKV + slot * 2 * kTile, bar = bars + 8 * (kDgFull0 + slot);
         if (elect_one()) {
-          mbar_expect_tx(bar, 2 * kTileBytes);
-          tma_load_4d(dst, &maps.kd, bar, 0, k.h, row, k.b);
-          tma_load_4d(dst + kHalfBytes, &maps.kd, bar, 64, k.h, row, k.b);
-          tma_load_4d(dst + kTileBytes, &maps.vd, bar, 0, k.h, row, k.b);
-          tma_load_4d(dst + kTileBytes + kHalfBytes, &maps.vd, bar, 64, k.h, row, k.b);
+          mbar_expect_tx(bar, 2 * kTile);
+          tma_load_tile<D>(dst, &maps.kd, bar, kHalfBytes, k.h, row, k.b);
+          tma_load_tile<D>(dst + kTile, &maps.vd, bar, kHalfBytes, k.h, row, k.b);
         }
         __syncwarp();
         issued = gi + 1;
@@ -827,10 +831,8 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
       if (kb >= 1 && !(ok = mbar_wait(bars + 8 * kDgQFree, (kb - 1) & 1, abort_flag, kDgQFree))) break;
       if (elect_one()) {
         mbar_expect_tx(bars + 8 * kDgRes, 2 * kStepTile + 512);
-        tma_load_4d(sQ, &maps.q, bars + 8 * kDgRes, 0, k.h, k.q0, k.b);
-        tma_load_4d(sQ + kStepHalf, &maps.q, bars + 8 * kDgRes, 64, k.h, k.q0, k.b);
-        tma_load_4d(sDO, &maps.dout, bars + 8 * kDgRes, 0, k.h, k.q0, k.b);
-        tma_load_4d(sDO + kStepHalf, &maps.dout, bars + 8 * kDgRes, 64, k.h, k.q0, k.b);
+        tma_load_tile<D>(sQ, &maps.q, bars + 8 * kDgRes, kStepHalf, k.h, k.q0, k.b);
+        tma_load_tile<D>(sDO, &maps.dout, bars + 8 * kDgRes, kStepHalf, k.h, k.q0, k.b);
         bulk_load(sStat, lse_t + k.stat_base + k.q0, 256, bars + 8 * kDgRes);
         bulk_load(sStat + 256, delta_t + k.stat_base + k.q0, 256, bars + 8 * kDgRes);
       }
@@ -849,7 +851,7 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
   } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA warp
     constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-    constexpr uint32_t idesc_t = instr_desc(fmt, 128, true);
+    constexpr uint32_t idesc_t = instr_desc(fmt, D, true);
     const uint64_t dq_k = desc_kmajor(sQ), ddo_k = desc_kmajor(sDO);
     const uint64_t dq_mn = desc_mnmajor(sQ, kStepHalf), ddo_mn = desc_mnmajor(sDO, kStepHalf);
     // scores of tile gj into stage gj & 1; the updates that read that stage last (tile gj - 2) were
@@ -858,11 +860,11 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
       const uint32_t slot = gj & 1;
       if (!mbar_wait(bars + 8 * (kDgFull0 + slot), (gj >> 1) & 1, abort_flag, kDgFull0 + slot)) return false;
       tc_fence_after();
-      const uint64_t dK = desc_kmajor(sKV + slot * 2 * kTileBytes), dV = desc_kmajor(sKV + slot * 2 * kTileBytes + kTileBytes);
+      const uint64_t dK = desc_kmajor(sKV + slot * 2 * kTile), dV = desc_kmajor(sKV + slot * 2 * kTile + kTile);
       const uint32_t tS = tmem + slot * 128, tP = tS + 64;
       if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int kk = 0; kk < D / 16; ++kk) {
           mma_ss(tS, desc_add(dK, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(dq_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           mma_ss(tP, desc_add(dV, (kk >> 2) * kHalfBytes + (kk & 3) * 32), desc_add(ddo_k, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
         }
@@ -980,25 +982,27 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
           __syncwarp();
           // staging = the TMA box layout: two [128 rows x 128 B] halves per tensor, 16-byte chunk c of
           // row r at chunk c ^ (r & 7)
-          unsigned char* orow = smem_raw + kDgOutOff + wg * kTileBytes + row * 128;
-          uint32_t ov[128];
+          unsigned char* orow = smem_raw + kDgOutOff + wg * kTile + row * 128;
+          uint32_t ov[D];
           tmem_ld32<0>(tacc, ov);
           tmem_ld32<32>(tacc + 32, ov);
-          tmem_ld32<64>(tacc + 64, ov);
-          tmem_ld32<96>(tacc + 96, ov);
+          if constexpr (D == 128) {
+            tmem_ld32<D - 64>(tacc + 64, ov);
+            tmem_ld32<D - 32>(tacc + 96, ov);
+          }
           tmem_wait_ld();
           tc_fence_before();
           mbar_arrive(bars + 8 * kDgE);                      // accumulator values are in registers
 #pragma unroll
-          for (int ch = 0; ch < 16; ++ch)
+          for (int ch = 0; ch < D / 8; ++ch)
             *reinterpret_cast<uint4*>(orow + (ch >> 3) * kHalfBytes + (((ch & 7) ^ (row & 7)) << 4)) = pack8_scaled<T>(ov + ch * 8, f);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
-            const uint32_t src = sOut + wg * kTileBytes + wq * 32 * 128;
+            const uint32_t src = sOut + wg * kTile + wq * 32 * 128;
             const CUtensorMap* om = wg ? &omaps.dkd : &omaps.dvd;
-            tma_store_4d(om, src, 0, k.h, key0, k.b);
-            tma_store_4d(om, src + kHalfBytes, 64, k.h, key0, k.b);
+#pragma unroll
+            for (int bx = 0; bx < D / 64; ++bx) tma_store_4d(om, src + bx * kHalfBytes, 64 * bx, k.h, key0, k.b);
             bulk_commit();
           }
           __syncwarp();
@@ -1007,7 +1011,7 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
           const bool valid = key < k.k_hi;
           T* gout = wg ? reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(k.b, key, k.h) : reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(k.b, key, k.h);
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
+          for (int q4 = 0; q4 < D / 32; ++q4) {
             uint32_t ov[32];
             tmem_ld32<0>(tacc + q4 * 32, ov);
             tmem_wait_ld();
@@ -1042,23 +1046,10 @@ inline bool depth_grad_applies(const Params& p, const moda_problem* pr) {
 }
 
 // ------------------------------------------------------------------ host side
-inline bool make_map_rows(CUtensorMap* m, const View& v, int dtype, int B, int64_t T, int H, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr || v.ptr == nullptr) return false;
-  auto fix = [](int64_t s) { return (cuuint64_t)((s > 0 ? s : 8) * 2); };
-  cuuint64_t dims[4] = {128, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
-  cuuint64_t strides[3] = {fix(v.sh), fix(v.st), fix(v.sb)};
-  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(m, dtype == MODA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, v.ptr,
-            dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 inline int padded_rows(int T_q) { return (T_q + 63) / 64 * 64 + 64; }
 
 inline bool bwd_supported(const moda_problem* pr) {
-  return pr->D == 128 && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
+  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
 }
 
 inline size_t bwd_extra_workspace_bytes(const moda_problem* pr) {
@@ -1067,99 +1058,97 @@ inline size_t bwd_extra_workspace_bytes(const moda_problem* pr) {
   return 2 * ((n + 255) & ~(size_t)255);
 }
 
-inline int bwd(const Params& p, const moda_problem* pr, void* extra, cudaStream_t st, int* launches, int* cuda_err) {
+struct BwdMaps { DqMaps dq; DkvMaps dkv; DgOutMaps out; };
+
+template <typename T, int D>
+inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, float* delta_t, float* lse_t, int T_qp, bool dg,
+                              int n_sm, cudaStream_t st, int* launches) {
+  cudaError_t e;
+  {
+    const int64_t groups = (int64_t)p.B * p.H * (T_qp / 32);
+    const int64_t cap = (int64_t)n_sm * 16;
+    const int blocks = (int)(groups < cap ? groups : cap);
+    prof::Scope ps(prof::kPreTc, st);
+    pre_kernel<T, D><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
+  }
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  *launches += 1;
+  {
+    auto kern = dq_kernel<T, D>;
+    const size_t smem = kDqRing * 2 * (size_t)step_tile<D>() + 2 * (size_t)kScoreTile + kCtlBytes;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
+    prof::Scope ps(prof::kDqTc, st);
+    kern<<<grid, kDqThreads, smem, st>>>(p, m.dq, delta_t, lse_t, T_qp);
+  }
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  *launches += 1;
+  {
+    auto kern = dkv_kernel<T, D>;
+    const size_t smem = kDkvRing * (2 * (size_t)step_tile<D>() + 512) + 2 * (size_t)kDkvPairBytes + kCtlBytes;
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    const int n_seq = (p.T_kv + kBN - 1) / kBN;
+    const int n_dep = dg ? 0 : (int)(((int64_t)p.T_kv * p.L + kBN - 1) / kBN);
+    dim3 grid(n_seq + n_dep, p.H, p.B);
+    prof::Scope ps(prof::kDkvTc, st);
+    kern<<<grid, kDqThreads, smem, st>>>(p, m.dkv, delta_t, lse_t, T_qp, n_seq);
+  }
+  if ((e = cudaGetLastError()) != cudaSuccess) return e;
+  *launches += 1;
+  if (dg) {
+    auto kern = depth_grad_kernel<T, D>;
+    constexpr uint32_t smem = dg_smem<D>();
+    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+    const int64_t n_blocks = (int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B;
+    dim3 grid((unsigned)(n_blocks < n_sm ? n_blocks : n_sm));
+    {
+      prof::Scope ps(prof::kDepthGradTc, st);
+      kern<<<grid, kDgThreads, smem, st>>>(p, m.dkv, m.out, delta_t, lse_t, T_qp);
+    }
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    *launches += 1;
+  }
+  return cudaSuccess;
+}
+
+inline int bwd(const Params& p, const moda_problem* pr, void* extra, int n_sm, cudaStream_t st, int* launches, int* cuda_err) {
   const int T_qp = padded_rows(p.T_q);
   const size_t n = (((size_t)p.B * p.H * T_qp * sizeof(float)) + 255) & ~(size_t)255;
   float* delta_t = reinterpret_cast<float*>(extra);
   float* lse_t = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(extra) + n);
   const int64_t TL = (int64_t)p.T_kv * p.L;
   const bool dep = p.L > 0;
+  const int D = pr->D, dt = pr->dtype;
 
-  DqMaps dqm; DkvMaps dkm;
-  memset(&dqm, 0, sizeof(dqm)); memset(&dkm, 0, sizeof(dkm));
-  bool ok = make_map_rows(&dqm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 64) &&
-            make_map_rows(&dqm.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 64) &&
-            make_map_rows(&dkm.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 128) &&
-            make_map_rows(&dkm.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 128) &&
-            make_map_rows(&dkm.q, p.q, pr->dtype, p.B, p.T_q, p.H, 64) &&
-            make_map_rows(&dkm.dout, p.dout, pr->dtype, p.B, p.T_q, p.H, 64);
+  BwdMaps m;
+  memset(&m, 0, sizeof(m));
+  bool ok = make_map_rows(&m.dq.k, p.k, dt, p.B, p.T_kv, p.H, D, 64) &&
+            make_map_rows(&m.dq.v, p.v, dt, p.B, p.T_kv, p.H, D, 64) &&
+            make_map_rows(&m.dkv.k, p.k, dt, p.B, p.T_kv, p.H, D, 128) &&
+            make_map_rows(&m.dkv.v, p.v, dt, p.B, p.T_kv, p.H, D, 128) &&
+            make_map_rows(&m.dkv.q, p.q, dt, p.B, p.T_q, p.H, D, 64) &&
+            make_map_rows(&m.dkv.dout, p.dout, dt, p.B, p.T_q, p.H, D, 64);
   if (ok && dep) {
-    ok = make_map_rows(&dqm.kd, p.kd, pr->dtype, p.B, TL, p.H, 64) && make_map_rows(&dqm.vd, p.vd, pr->dtype, p.B, TL, p.H, 64) &&
-         make_map_rows(&dkm.kd, p.kd, pr->dtype, p.B, TL, p.H, 128) && make_map_rows(&dkm.vd, p.vd, pr->dtype, p.B, TL, p.H, 128);
+    ok = make_map_rows(&m.dq.kd, p.kd, dt, p.B, TL, p.H, D, 64) && make_map_rows(&m.dq.vd, p.vd, dt, p.B, TL, p.H, D, 64) &&
+         make_map_rows(&m.dkv.kd, p.kd, dt, p.B, TL, p.H, D, 128) && make_map_rows(&m.dkv.vd, p.vd, dt, p.B, TL, p.H, D, 128);
   } else if (ok) {
-    dqm.kd = dqm.k; dqm.vd = dqm.v; dkm.kd = dkm.k; dkm.vd = dkm.v;
+    m.dq.kd = m.dq.k; m.dq.vd = m.dq.v; m.dkv.kd = m.dkv.k; m.dkv.vd = m.dkv.v;
   }
   if (!ok) return MODA_ERR_UNSUPPORTED;
+  const bool dg = depth_grad_applies(p, pr);
+  if (dg && !(make_map_rows(&m.out.dkd, p.dkd, dt, p.B, TL, p.H, D, 32) && make_map_rows(&m.out.dvd, p.dvd, dt, p.B, TL, p.H, D, 32)))
+    return MODA_ERR_UNSUPPORTED;
+  if ((int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B > 0x7fffffff || n_sm <= 0) return MODA_ERR_UNSUPPORTED;
 
-  void* status_addr = nullptr;
-  cudaError_t e = cudaGetSymbolAddress(&status_addr, g_tc_status);
-  if (e == cudaSuccess) e = cudaMemsetAsync(status_addr, 0, sizeof(int), st);
+  cudaError_t e = clear_launch_status(st);
+  if (e == cudaSuccess) {
+    const bool bf = dt == MODA_BF16;
+    if (D == 128) e = bf ? launch_bwd<__nv_bfloat16, 128>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches)
+                         : launch_bwd<__half, 128>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches);
+    else e = bf ? launch_bwd<__nv_bfloat16, 64>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches)
+                : launch_bwd<__half, 64>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches);
+  }
   if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
-
-  const bool bf = pr->dtype == MODA_BF16;
-  {
-    const int64_t groups = (int64_t)p.B * p.H * (T_qp / 32);
-    const int blocks = (int)(groups < 148 * 16 ? groups : 148 * 16);
-    prof::Scope ps(prof::kPreTc, st);
-    if (bf) pre_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
-    else pre_kernel<__half><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
-  }
-  if ((e = cudaGetLastError()) != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
-  *launches += 1;
-  {
-    const size_t smem = kDqRing * 2 * (size_t)kStepTile + 2 * (size_t)kStepTile + kCtlBytes;
-    dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
-    auto launch = [&](auto kern) -> cudaError_t {
-      cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (er != cudaSuccess) return er;
-      prof::Scope ps(prof::kDqTc, st);
-      kern<<<grid, kDqThreads, smem, st>>>(p, dqm, delta_t, lse_t, T_qp);
-      return cudaGetLastError();
-    };
-    e = bf ? launch(dq_kernel<__nv_bfloat16>) : launch(dq_kernel<__half>);
-    if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
-    *launches += 1;
-  }
-  {
-    const size_t smem = kDkvRing * (size_t)kDkvSlot + 2 * (size_t)kDkvPairBytes + kCtlBytes;
-    const bool dg = depth_grad_applies(p, pr);
-    DgOutMaps om;
-    if (dg && !(make_map_rows(&om.dkd, p.dkd, pr->dtype, p.B, TL, p.H, 32) && make_map_rows(&om.dvd, p.dvd, pr->dtype, p.B, TL, p.H, 32)))
-      return MODA_ERR_UNSUPPORTED;
-    const int n_seq = (p.T_kv + kBN - 1) / kBN;
-    const int n_dep = dg ? 0 : (int)((TL + kBN - 1) / kBN);
-    dim3 grid(n_seq + n_dep, p.H, p.B);
-    auto launch = [&](auto kern) -> cudaError_t {
-      cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (er != cudaSuccess) return er;
-      prof::Scope ps(prof::kDkvTc, st);
-      kern<<<grid, kDqThreads, smem, st>>>(p, dkm, delta_t, lse_t, T_qp, n_seq);
-      return cudaGetLastError();
-    };
-    e = bf ? launch(dkv_kernel<__nv_bfloat16>) : launch(dkv_kernel<__half>);
-    if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
-    *launches += 1;
-    if (dg) {
-      int dev = 0, n_sm = 0;
-      if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) {
-        *cuda_err = (int)cudaGetLastError();
-        return MODA_ERR_CUDA;
-      }
-      const int64_t n_blocks = (int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B;
-      if (n_blocks > 0x7fffffff) return MODA_ERR_UNSUPPORTED;
-      dim3 ggrid((unsigned)(n_blocks < n_sm ? n_blocks : n_sm));
-      auto glaunch = [&](auto kern) -> cudaError_t {
-        cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDgSmem);
-        if (er != cudaSuccess) return er;
-        prof::Scope ps(prof::kDepthGradTc, st);
-        kern<<<ggrid, kDgThreads, kDgSmem, st>>>(p, dkm, om, delta_t, lse_t, T_qp);
-        return cudaGetLastError();
-      };
-      e = bf ? glaunch(depth_grad_kernel<__nv_bfloat16>) : glaunch(depth_grad_kernel<__half>);
-      if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
-      *launches += 1;
-    }
-  }
   return MODA_OK;
 }
 

@@ -1,4 +1,4 @@
-// tcgen05 / TMEM / TMA forward of MoDA, two query tiles per CTA (D = 128, bf16 or fp16).
+// tcgen05 / TMEM / TMA forward of MoDA, two query tiles per CTA (D = 64 or 128, bf16 or fp16).
 //
 // One CTA per SM owns 256 folded query rows of one (batch, KV head): two tiles of 128 rows, each
 // with its own softmax warpgroup (thread = row = TMEM lane), its own score block S_a and its own
@@ -17,10 +17,10 @@
 // different rows, so a depth step belongs to one query tile).
 //
 //   warp 9 (TMA)   Q_0, Q_1 once; ring of two {K tile, V tile} slots.
-//   warp 8 (MMA)   S_a = Q_a K^T (SS, M128 N128), O_a += P_a V (TS: P_a packed over S_a in TMEM).
+//   warp 8 (MMA)   S_a = Q_a K^T (SS, M128 N128), O_a += P_a V (TS, N = D: P_a packed over S_a in TMEM).
 //   warps 0-3 / 4-7  softmax of query tile 0 / 1, lazy O rescale, epilogue.
 //
-// TMEM (512 columns): S_0 [0,128), S_1 [128,256), O_0 [256,384), O_1 [384,512).  Every wait is
+// TMEM (512 columns): S_0 [0,128), S_1 [128,256), O_0 [256,256+D), O_1 [384,384+D).  Every wait is
 // bounded, as in the other tcgen05 kernels.
 #pragma once
 #include "tc_bwd_kernels.cuh"
@@ -32,7 +32,7 @@ constexpr int kF3Threads = 320;
 // barriers: q, full[2], empty[2], s[2], p[2], done
 struct F3Bars { static constexpr int q = 0, full0 = 1, empty0 = 3, s0 = 5, p0 = 7, done = 9, count = 10; };
 static_assert(F3Bars::count <= kMaxBars, "control block too small");
-constexpr uint32_t kF3Smem = 2 * kTileBytes + 2 * 2 * kTileBytes + kCtlBytes;
+template <int D> __host__ __device__ constexpr uint32_t f3_smem() { return 6 * tile_bytes<D>() + kCtlBytes; }   // Q_0, Q_1, two {K, V} slots
 
 struct Fwd3Maps { CUtensorMap q, k, v, kd, vd; };        // 128-row boxes
 
@@ -68,19 +68,20 @@ __device__ __forceinline__ void f3_step(const F3Plan& pl, int s, int& part, bool
   row = pl.w[a].dep_c0 + d * kBN;
 }
 
-template <typename T, int kPolyEvery>
+template <typename T, int D, int kPolyEvery>
 __global__ void __launch_bounds__(kF3Threads, 1)
 fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps maps) {
   using B_ = F3Bars;
+  constexpr uint32_t kTile = tile_bytes<D>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   if (base & 1023u) {
-    if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, (2 << 8));
+    if (threadIdx.x == 0) record_failure(2 << 8);
     return;
   }
-  const uint32_t sQ = base;                              // Q_a at sQ + a * kTileBytes
-  const uint32_t sRing = base + 2 * kTileBytes;          // slot: {K tile, V tile}
-  const uint32_t ctl_off = 6 * kTileBytes;
+  const uint32_t sQ = base;                              // Q_a at sQ + a * kTile
+  const uint32_t sRing = base + 2 * kTile;               // slot: {K tile, V tile}
+  const uint32_t ctl_off = 6 * kTile;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
@@ -126,13 +127,9 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
     if (pl.n > 0) {
       if (elect_one()) {
         prefetch_map(&maps.q); prefetch_map(&maps.k); prefetch_map(&maps.v);
-        mbar_expect_tx(bars + 8 * B_::q, (two ? 2u : 1u) * kTileBytes);
-        tma_load_4d(sQ, &maps.q, bars + 8 * B_::q, 0, h, r0, b);
-        tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * B_::q, 64, h, r0, b);
-        if (two) {
-          tma_load_4d(sQ + kTileBytes, &maps.q, bars + 8 * B_::q, 0, h, r0 + kBM, b);
-          tma_load_4d(sQ + kTileBytes + kHalfBytes, &maps.q, bars + 8 * B_::q, 64, h, r0 + kBM, b);
-        }
+        mbar_expect_tx(bars + 8 * B_::q, (two ? 2u : 1u) * kTile);
+        tma_load_tile<D>(sQ, &maps.q, bars + 8 * B_::q, kHalfBytes, h, r0, b);
+        if (two) tma_load_tile<D>(sQ + kTile, &maps.q, bars + 8 * B_::q, kHalfBytes, h, r0 + kBM, b);
       }
       __syncwarp();
       bool ok = true;
@@ -142,15 +139,13 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         if (s >= 2 && !(ok = mbar_wait(bars + 8 * (B_::empty0 + slot), ((s >> 1) - 1) & 1, abort_flag, B_::empty0 + slot))) break;
         int part, row; bool dep;
         f3_step(pl, s, part, dep, row);
-        const uint32_t dst = sRing + slot * 2 * kTileBytes, bar = bars + 8 * (B_::full0 + slot);
+        const uint32_t dst = sRing + slot * 2 * kTile, bar = bars + 8 * (B_::full0 + slot);
         const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         if (elect_one()) {
-          mbar_expect_tx(bar, 2 * kTileBytes);
-          tma_load_4d(dst, mk, bar, 0, h, row, b);
-          tma_load_4d(dst + kHalfBytes, mk, bar, 64, h, row, b);
-          tma_load_4d(dst + kTileBytes, mv, bar, 0, h, row, b);
-          tma_load_4d(dst + kTileBytes + kHalfBytes, mv, bar, 64, h, row, b);
+          mbar_expect_tx(bar, 2 * kTile);
+          tma_load_tile<D>(dst, mk, bar, kHalfBytes, h, row, b);
+          tma_load_tile<D>(dst + kTile, mv, bar, kHalfBytes, h, row, b);
         }
         __syncwarp();
         issued = s + 1;
@@ -165,7 +160,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
     // ---------------------------------------------------------------- MMA warp
     if (pl.n > 0) {
       constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
-      constexpr uint32_t idesc_pv = instr_desc(fmt, 128, true);
+      constexpr uint32_t idesc_pv = instr_desc(fmt, D, true);
       int qk_cnt[2] = {0, 0}, pv_cnt[2] = {0, 0};     // steps tile a has taken part in so far
       bool ok = mbar_wait(bars + 8 * B_::q, 0, abort_flag, B_::q);
       // S_a = Q_a K(s)^T
@@ -173,10 +168,10 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         const uint32_t slot = s & 1;
         if (!mbar_wait(bars + 8 * (B_::full0 + slot), (s >> 1) & 1, abort_flag, B_::full0 + slot)) return false;
         tc_fence_after();
-        const uint32_t sK = sRing + slot * 2 * kTileBytes, sQa = sQ + a * kTileBytes, tS = tmem + a * 128;
+        const uint32_t sK = sRing + slot * 2 * kTile, sQa = sQ + a * kTile, tS = tmem + a * 128;
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
+          for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
             mma_ss(tS, smem_desc_sw128(sQa + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
           }
@@ -191,7 +186,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         if (!mbar_wait(bars + 8 * (B_::p0 + a), pv_cnt[a] & 1, abort_flag, B_::p0 + a)) return false;
         tc_fence_after();
         const uint32_t slot = s & 1;
-        const uint32_t sV = sRing + slot * 2 * kTileBytes + kTileBytes, tS = tmem + a * 128, tO = tmem + 256 + a * 128;
+        const uint32_t sV = sRing + slot * 2 * kTile + kTile, tS = tmem + a * 128, tO = tmem + 256 + a * 128;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
@@ -288,7 +283,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       // this tile's previous step finished before these scores were produced (issue order)
       if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 0; q4 < D / 32; ++q4) {
           uint32_t ov[32];
           tmem_ld32<0>(tmem_O + lane_addr + q4 * 32, ov);
           tmem_wait_ld();
@@ -312,7 +307,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       if (merge) merge_partials(m_used, l, p.lse[lse_idx], inv, w_dep, lse_out);
       T* go = reinterpret_cast<T*>(p.o.ptr) + p.o.off(b, r, h);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < D / 32; ++q4) {
         uint32_t ov[32];
         tmem_ld32<0>(tmem_O + lane_addr + q4 * 32, ov);
         tmem_wait_ld();
@@ -335,36 +330,29 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
   }
 }
 
-inline int fwd3(const Params& p, const moda_problem* pr, cudaStream_t st, int* launches, int* cuda_err) {
-  Fwd3Maps maps;
-  memset(&maps, 0, sizeof(maps));
-  const int64_t TL = (int64_t)p.T_kv * p.L;
-  bool ok = make_map_rows(&maps.q, p.q, pr->dtype, p.B, p.T_q, p.H, 128) &&
-            make_map_rows(&maps.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 128) &&
-            make_map_rows(&maps.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 128);
-  if (ok && p.L > 0) {
-    ok = make_map_rows(&maps.kd, p.kd, pr->dtype, p.B, TL, p.H, 128) && make_map_rows(&maps.vd, p.vd, pr->dtype, p.B, TL, p.H, 128);
-  } else if (ok) {
-    maps.kd = maps.k; maps.vd = maps.v;   // never dereferenced (no depth steps)
-  }
-  if (!ok) return MODA_ERR_UNSUPPORTED;
-  void* status_addr = nullptr;
-  cudaError_t e = cudaGetSymbolAddress(&status_addr, g_tc_status);
-  if (e == cudaSuccess) e = cudaMemsetAsync(status_addr, 0, sizeof(int), st);
-  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+template <typename T, int D>
+inline cudaError_t launch_fwd3(const Params& p, const Fwd3Maps& maps, cudaStream_t st) {
+  // one pair of exponentials in four goes to the FMA pipe (exp2x2_fma); none, one in eight and
+  // one in two were all slower
+  auto kern = fwd3_kernel<T, D, 4>;
+  constexpr uint32_t smem = f3_smem<D>();
+  cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (er != cudaSuccess) return er;
   dim3 grid((p.T_q + 2 * kBM - 1) / (2 * kBM), p.H, p.B);
-  auto launch = [&](auto kern) -> cudaError_t {
-    cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kF3Smem);
-    if (er != cudaSuccess) return er;
-    prof::Scope ps(prof::kFwdTc, st);
-    kern<<<grid, kF3Threads, kF3Smem, st>>>(p, maps);
-    return cudaGetLastError();
-  };
-  // One pair of exponentials in four on the FMA pipe: measured on config 4 (forward only) 33.5 ms,
-  // against 34.1 ms with none, 33.7 ms with one in eight and 36.2 ms with one in two.  Rounding P
-  // to 16 bits with integer adds and a byte permute instead of the conversion instruction was
-  // also measured: 33.0 ms against 32.2 ms.
-  e = (pr->dtype == MODA_BF16) ? launch(fwd3_kernel<__nv_bfloat16, 4>) : launch(fwd3_kernel<__half, 4>);
+  prof::Scope ps(prof::kFwdTc, st);
+  kern<<<grid, kF3Threads, smem, st>>>(p, maps);
+  return cudaGetLastError();
+}
+
+inline int fwd3(const Params& p, const moda_problem* pr, cudaStream_t st, int* launches, int* cuda_err) {
+  FwdMaps fm;
+  if (!make_fwd_maps(&fm, p, pr)) return MODA_ERR_UNSUPPORTED;
+  Fwd3Maps maps{fm.q, fm.k, fm.v, fm.kd, fm.vd};
+  cudaError_t e = clear_launch_status(st);
+  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+  const bool bf = pr->dtype == MODA_BF16;
+  if (pr->D == 128) e = bf ? launch_fwd3<__nv_bfloat16, 128>(p, maps, st) : launch_fwd3<__half, 128>(p, maps, st);
+  else e = bf ? launch_fwd3<__nv_bfloat16, 64>(p, maps, st) : launch_fwd3<__half, 64>(p, maps, st);
   if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
   *launches += 1;
   return MODA_OK;

@@ -1,4 +1,4 @@
-// tcgen05 / TMEM / TMA MoDA kernels for sm_100a (D = 128, bf16 or fp16).
+// tcgen05 / TMEM / TMA MoDA kernels for sm_100a (head dim D = 64 or 128, bf16 or fp16).
 //
 // Forward.  One CTA owns 128 folded query rows of one (batch, KV head) and walks the
 // key tiles they can see: sequence K/V first, then the depth K/V window of the tile
@@ -8,8 +8,8 @@
 //   warp 5           : TMA loads (128B-swizzled [128 x 64] boxes) of Q once and of each K and
 //                      V tile into single-stage buffers, refilled as soon as the MMA that read
 //                      them has completed.
-//   warp 4           : issues S = Q K^T and O += P V as tcgen05.mma (M=128, N=128, K=16 steps)
-//                      with fp32 accumulators in TMEM.
+//   warp 4           : issues S = Q K^T (M=128, N=128) and O += P V (M=128, N=D) as tcgen05.mma
+//                      in K=16 steps with fp32 accumulators in TMEM.
 //   warps 0-3        : softmax.  Thread = query row = TMEM lane.  tcgen05.ld of the S
 //                      row, visibility mask on masked tiles only, online softmax in
 //                      base 2 with lazy rescaling of O (O is touched only when a row
@@ -18,7 +18,8 @@
 //                      TMEM.
 //
 // TMEM (256 columns per CTA): [0,128) S (fp32) / P (16-bit, first 64 columns),
-// [128,256) O (fp32).  Shared memory: Q, K, V tiles of 32 KB each.
+// [128,128+D) O (fp32).  Shared memory: Q, K, V tiles of [128 x D] 16-bit values each, stored
+// as D/64 boxes of [128 rows x 64 elements] (one 128-byte swizzle atom per row).
 //
 // Every mbarrier wait is bounded: on expiry the CTA records an error in a device
 // status word, drains its outstanding TMA loads (bounded again), frees its TMEM and
@@ -39,12 +40,26 @@ namespace tc {
 constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr uint32_t kWaitHintNs = 20000;        // one try_wait may sleep this long (ns)
+#ifdef MODA_WAIT_TEST
+constexpr uint32_t kWaitTries = 50;            // wait-expiry test build: give up after about 1 ms
+#else
 constexpr uint32_t kWaitTries = 10000;         // tries per wait before giving up (<= 0.2 s)
-constexpr uint32_t kTileBytes = 128 * 128 * 2; // one [128 x 128] 16-bit tile
-constexpr uint32_t kHalfBytes = kTileBytes / 2;
+#endif
+constexpr uint32_t kHalfBytes = 128 * 64 * 2;  // one TMA box: [128 rows x 64 elements] of 16 bits
+constexpr uint32_t kTileBytes = 2 * kHalfBytes; // a [128 x 128] 16-bit tile (two boxes)
+template <int D> __host__ __device__ constexpr uint32_t tile_bytes() { return (uint32_t)(D / 64) * kHalfBytes; }   // [128 x D]
 
-// 0 = ok; otherwise (code << 8) | barrier id of the first wait that expired.
+// 0 = ok; otherwise (code << 8) | barrier id of the first wait that expired.  g_tc_status is the
+// abort flag of the launch in flight: it is cleared when a launch is enqueued and lets the CTAs
+// that start after a failure return at once.  g_tc_sticky keeps the first failure of any launch
+// until the host reads it (moda_b200_device_status), so that a later call cannot erase it.
 __device__ int g_tc_status;
+__device__ int g_tc_sticky;
+
+__device__ __forceinline__ void record_failure(int code) {
+  atomicCAS(&g_tc_status, 0, code);
+  atomicCAS(&g_tc_sticky, 0, code);
+}
 
 struct FwdMaps { CUtensorMap q, k, v, kd, vd; };
 
@@ -88,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (*abort_flag != 0) return false;
   }
   *abort_flag = 1;
-  atomicCAS(&g_tc_status, 0, (1 << 8) | bar_id);
+  record_failure((1 << 8) | bar_id);
   return false;
 }
 
@@ -315,20 +330,27 @@ __device__ __forceinline__ Walk make_walk(const Params& p, int r0) {
   return w;
 }
 
+// Loads a [rows x D] tile as D/64 boxes; the caller has armed `bar` with the byte count.
+template <int D>
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t box_bytes,
+                                              int h, int row, int b) {
+#pragma unroll
+  for (int bx = 0; bx < D / 64; ++bx) tma_load_4d(dst + bx * box_bytes, map, bar, 64 * bx, h, row, b);
+}
+
 // ======================================================================= forward
-// grid (ceil(T_q/128), H, B); 192 threads (4 softmax warps, MMA warp, TMA warp).  kPTmem: P is handed to the PV MMA through
-// TMEM (production).  kPTmem = false stages P through a swizzled shared-memory tile
-// instead (one CTA per SM; kept as a cross-check of the TMEM operand layout).
-template <typename T, bool kPTmem>
-__global__ void __launch_bounds__(192, kPTmem ? 2 : 1)
-fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps maps, float* dbg) {
+// grid (ceil(T_q/128), H, B); 192 threads (4 softmax warps, MMA warp, TMA warp); two CTAs per SM.
+template <typename T, int D>
+__global__ void __launch_bounds__(192, 2)
+fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps maps) {
+  constexpr uint32_t kTile = tile_bytes<D>();
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   unsigned char* gbase = smem_raw + (base - raw_u32);
-  const uint32_t sQ = base, sK = base + kTileBytes, sV = base + 2 * kTileBytes, sP = base + 3 * kTileBytes;
-  const uint32_t ctl = base + (kPTmem ? 3 : 4) * kTileBytes;
-  unsigned char* gctl = gbase + (kPTmem ? 3 : 4) * kTileBytes;
+  const uint32_t sQ = base, sK = base + kTile, sV = base + 2 * kTile;
+  const uint32_t ctl = base + 3 * kTile;
+  unsigned char* gctl = gbase + 3 * kTile;
   const uint32_t bars = ctl;                                    // kBarCount x 8 bytes
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 64);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gctl + 72);
@@ -383,18 +405,16 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         const uint32_t dst = is_k ? sK : sV;
         const uint32_t bar = bars + 8 * (is_k ? kBarK : kBarV);
         if (elect_one()) {
-          mbar_expect_tx(bar, kTileBytes);
-          tma_load_4d(dst, m, bar, 0, h, row, b);
-          tma_load_4d(dst + kHalfBytes, m, bar, 64, h, row, b);
+          mbar_expect_tx(bar, kTile);
+          tma_load_tile<D>(dst, m, bar, kHalfBytes, h, row, b);
         }
         __syncwarp();
         if (is_k) { pend_k = true; pend_k_par = i & 1; } else { pend_v = true; pend_v_par = i & 1; }
       };
       if (elect_one()) {
         prefetch_map(&maps.q); prefetch_map(&maps.k); prefetch_map(&maps.v);
-        mbar_expect_tx(bars + 8 * kBarQ, kTileBytes);
-        tma_load_4d(sQ, &maps.q, bars + 8 * kBarQ, 0, h, r0, b);
-        tma_load_4d(sQ + kHalfBytes, &maps.q, bars + 8 * kBarQ, 64, h, r0, b);
+        mbar_expect_tx(bars + 8 * kBarQ, kTile);
+        tma_load_tile<D>(sQ, &maps.q, bars + 8 * kBarQ, kHalfBytes, h, r0, b);
       }
       __syncwarp();
       load_kv(0, true);
@@ -406,17 +426,18 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         if (!(ok = mbar_wait(bars + 8 * kBarVFree, j & 1, abort_flag, kBarVFree))) break;
         load_kv(j + 1, false);
       }
-      if (!ok) {   // give up: let loads in flight land before the CTA's shared memory is released
-        mbar_wait(bars + 8 * kBarQ, 0, drain_flag, kBarQ);
-        if (pend_k) mbar_wait(bars + 8 * kBarK, pend_k_par, drain_flag, kBarK);
-        if (pend_v) mbar_wait(bars + 8 * kBarV, pend_v_par, drain_flag, kBarV);
-      }
+      // Every load this warp issued must have landed before the CTA's shared memory is released,
+      // whether the walk completed (the last tiles are about to be consumed anyway) or a wait gave
+      // up somewhere in the CTA: wait (bounded) for the latest Q, K and V loads.
+      mbar_wait(bars + 8 * kBarQ, 0, drain_flag, kBarQ);
+      if (pend_k) mbar_wait(bars + 8 * kBarK, pend_k_par, drain_flag, kBarK);
+      if (pend_v) mbar_wait(bars + 8 * kBarV, pend_v_par, drain_flag, kBarV);
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------- MMA warp
     if (n_tiles > 0) {
       constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
-      constexpr uint32_t idesc_pv = instr_desc(fmt, 128, true);
+      constexpr uint32_t idesc_pv = instr_desc(fmt, D, true);
       bool ok = mbar_wait(bars + 8 * kBarQ, 0, abort_flag, kBarQ);
       for (int j = 0; ok && j < n_tiles; ++j) {
         const uint32_t par = j & 1;
@@ -424,7 +445,7 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
+          for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
             mma_ss(tmem_S, smem_desc_sw128(sQ + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
           }
@@ -437,16 +458,9 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t bdesc = smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024);
-            const uint32_t acc = (j > 0 || kk > 0) ? 1u : 0u;
-            if (kPTmem) {
-              mma_ts(tmem_O, tmem_S + kk * 8, bdesc, idesc_pv, acc);
-            } else {
-              const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-              mma_ss(tmem_O, smem_desc_sw128(sP + off, 16, 1024), bdesc, idesc_pv, acc);
-            }
-          }
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem_O, tmem_S + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv,
+                   (j > 0 || kk > 0) ? 1u : 0u);
           tc_commit(bars + 8 * kBarO);
           tc_commit(bars + 8 * kBarVFree);
         }
@@ -491,31 +505,15 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         tmem_ld32<64>(tmem_S + lane_addr + 64, su);
         tmem_ld32<96>(tmem_S + lane_addr + 96, su);
         tmem_wait_ld();
-        if (dbg != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-#pragma unroll
-          for (int i = 0; i < 128; ++i) dbg[row * 128 + i] = __uint_as_float(su[i]);
-        }
         // same arithmetic as fwd3_kernel, so that a result does not depend on which of the two ran
         softmax_row128<T, 4>(su, masked, is_dep && (p.L & 31) == 0, c0, lo, hi, c, m_used, l, alpha, grow, pk);
       }
-      if (kPTmem) {
-        tmem_st32<0>(tmem_S + lane_addr + 0, pk);
-        tmem_st32<32>(tmem_S + lane_addr + 32, pk);
-      } else {
-        // K-major, 128B-swizzled [128 rows][64 keys] x 2 blocks: 16-byte chunk cidx of a row
-        // lives at chunk (cidx ^ (row & 7))
-        unsigned char* prow = gbase + 3 * kTileBytes + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
-          const int blk = ch >> 3, cidx = ch & 7;
-          uint4 v4 = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-          *reinterpret_cast<uint4*>(prow + blk * kHalfBytes + ((cidx ^ (row & 7)) << 4)) = v4;
-        }
-      }
+      tmem_st32<0>(tmem_S + lane_addr + 0, pk);
+      tmem_st32<32>(tmem_S + lane_addr + 32, pk);
       // rescale O (TMEM round trip) only when some row of this warp moved its maximum
       if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
+        for (int q4 = 0; q4 < D / 32; ++q4) {
           uint32_t ov[32];
           tmem_ld32<0>(tmem_O + lane_addr + q4 * 32, ov);
           tmem_wait_ld();
@@ -524,14 +522,14 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
           tmem_st32<0>(tmem_O + lane_addr + q4 * 32, ov);
         }
       }
-      if (kPTmem) {
-        tmem_wait_st();
-      } else {
-        tmem_wait_st();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      }
+      tmem_wait_st();
       tc_fence_before();
+#ifndef MODA_WAIT_TEST
       mbar_arrive(bars + 8 * kBarP);
+#endif
+      // (the wait-expiry test build withholds this arrival: the MMA warp's bounded wait on the
+      // P-ready barrier, which no TMA load targets, then runs out and the CTA leaves through the
+      // teardown path)
     }
 
     if (ok && n_tiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * kBarO, (n_tiles - 1) & 1, abort_flag, kBarO));
@@ -543,7 +541,7 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
       if (merge) merge_partials(m_used, l, p.lse[lse_idx], inv, w_dep, lse_out);
       T* go = reinterpret_cast<T*>(p.o.ptr) + p.o.off(b, r, h);
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q4 = 0; q4 < D / 32; ++q4) {
         uint32_t ov[32];
         tmem_ld32<0>(tmem_O + lane_addr + q4 * 32, ov);
         tmem_wait_ld();
@@ -584,71 +582,92 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [B, T, H, D] view -> 4-D tensor map (D, H, T, B), box [64, 1, 128, 1], 128B swizzle, zero fill.
-inline bool make_map(CUtensorMap* m, const View& v, int dtype, int B, int64_t T, int H, int D) {
+// [B, T, H, D] view -> 4-D tensor map (D, H, T, B), box [64, 1, box_rows, 1], 128B swizzle, zero
+// fill.  A dimension of extent 1 may carry any stride (it is never multiplied by a non-zero
+// index) and gets a placeholder TMA accepts; every other stride must be a positive multiple of
+// 8 elements, which the entry points have checked.
+inline bool make_map_rows(CUtensorMap* m, const View& v, int dtype, int B, int64_t T, int H, int D, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr || v.ptr == nullptr) return false;
-  // a size-1 dimension may carry any stride; TMA still wants a positive multiple of 16 bytes
-  auto fix = [](int64_t s) { return (cuuint64_t)((s > 0 ? s : 8) * 2); };
+  bool bad = false;
+  auto stride = [&bad](int64_t s, int64_t extent) -> cuuint64_t {
+    if (extent <= 1) return (cuuint64_t)16;
+    if (s <= 0) { bad = true; return (cuuint64_t)16; }
+    return (cuuint64_t)(s * 2);
+  };
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
-  cuuint64_t strides[3] = {fix(v.sh), fix(v.st), fix(v.sb)};
-  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint64_t strides[3] = {stride(v.sh, H), stride(v.st, T), stride(v.sb, B)};
+  if (bad) return false;
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult rc = fn(m, dtype == MODA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                   v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS;
+  return fn(m, dtype == MODA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, v.ptr,
+            dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 inline bool fwd_supported(const moda_problem* pr) {
-  return pr->D == 128 && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && pr->T_kv * (int64_t)pr->G >= 1;
+  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
 }
 
-// debugging aids (set through moda_b200_debug_set): variant 1 routes P through shared memory
-struct DebugState { float* dump = nullptr; int variant = 0; };
-inline DebugState& debug_state() { static DebugState s; return s; }
-
-inline int fwd(const Params& p, const moda_problem* pr, cudaStream_t st, int* launches, int* cuda_err) {
-  FwdMaps maps;
-  memset(&maps, 0, sizeof(maps));
-  const int64_t TL = (int64_t)p.T_kv * p.L;
-  bool ok = make_map(&maps.q, p.q, pr->dtype, p.B, p.T_q, p.H, 128) &&
-            make_map(&maps.k, p.k, pr->dtype, p.B, p.T_kv, p.H, 128) &&
-            make_map(&maps.v, p.v, pr->dtype, p.B, p.T_kv, p.H, 128);
-  if (ok && p.L > 0) {
-    ok = make_map(&maps.kd, p.kd, pr->dtype, p.B, TL, p.H, 128) && make_map(&maps.vd, p.vd, pr->dtype, p.B, TL, p.H, 128);
-  } else if (ok) {
-    maps.kd = maps.k; maps.vd = maps.v;   // never dereferenced (no depth tiles)
-  }
-  if (!ok) return MODA_ERR_UNSUPPORTED;
-
+// Clears the abort flag of the launch about to be enqueued (the sticky word is left alone).
+inline cudaError_t clear_launch_status(cudaStream_t st) {
   void* status_addr = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&status_addr, g_tc_status);
   if (e == cudaSuccess) e = cudaMemsetAsync(status_addr, 0, sizeof(int), st);
-  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+  return e;
+}
 
-  const bool p_tmem = debug_state().variant != 1;
-  const size_t smem = (p_tmem ? 3 : 4) * (size_t)kTileBytes + 1024 + 128;
+inline bool make_fwd_maps(FwdMaps* maps, const Params& p, const moda_problem* pr) {
+  memset(maps, 0, sizeof(*maps));
+  const int64_t TL = (int64_t)p.T_kv * p.L;
+  const int D = pr->D;
+  bool ok = make_map_rows(&maps->q, p.q, pr->dtype, p.B, p.T_q, p.H, D, 128) &&
+            make_map_rows(&maps->k, p.k, pr->dtype, p.B, p.T_kv, p.H, D, 128) &&
+            make_map_rows(&maps->v, p.v, pr->dtype, p.B, p.T_kv, p.H, D, 128);
+  if (ok && p.L > 0) {
+    ok = make_map_rows(&maps->kd, p.kd, pr->dtype, p.B, TL, p.H, D, 128) &&
+         make_map_rows(&maps->vd, p.vd, pr->dtype, p.B, TL, p.H, D, 128);
+  } else if (ok) {
+    maps->kd = maps->k; maps->vd = maps->v;   // never dereferenced (no depth tiles)
+  }
+  return ok;
+}
+
+template <typename T, int D>
+inline cudaError_t launch_fwd(const Params& p, const FwdMaps& maps, cudaStream_t st) {
+  auto kern = fwd_kernel<T, D>;
+  const size_t smem = 3 * (size_t)tile_bytes<D>() + 1024 + 128;
+  cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (er != cudaSuccess) return er;
   dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
-  auto launch = [&](auto kern) -> cudaError_t {
-    cudaError_t er = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (er != cudaSuccess) return er;
-    prof::Scope ps(prof::kFwdTc, st);
-    kern<<<grid, 192, smem, st>>>(p, maps, debug_state().dump);
-    return cudaGetLastError();
-  };
-  if (pr->dtype == MODA_BF16) e = p_tmem ? launch(fwd_kernel<__nv_bfloat16, true>) : launch(fwd_kernel<__nv_bfloat16, false>);
-  else e = p_tmem ? launch(fwd_kernel<__half, true>) : launch(fwd_kernel<__half, false>);
+  prof::Scope ps(prof::kFwdTc, st);
+  kern<<<grid, 192, smem, st>>>(p, maps);
+  return cudaGetLastError();
+}
+
+inline int fwd(const Params& p, const moda_problem* pr, cudaStream_t st, int* launches, int* cuda_err) {
+  FwdMaps maps;
+  if (!make_fwd_maps(&maps, p, pr)) return MODA_ERR_UNSUPPORTED;
+  cudaError_t e = clear_launch_status(st);
+  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
+  const bool bf = pr->dtype == MODA_BF16;
+  if (pr->D == 128) e = bf ? launch_fwd<__nv_bfloat16, 128>(p, maps, st) : launch_fwd<__half, 128>(p, maps, st);
+  else e = bf ? launch_fwd<__nv_bfloat16, 64>(p, maps, st) : launch_fwd<__half, 64>(p, maps, st);
   if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
   *launches += 1;
   return MODA_OK;
 }
 
-// Reads (and synchronises on) the device status word of the tcgen05 kernels.
+// Reads the sticky status word of the tcgen05 kernels (synchronises) and clears it when set.
 inline int read_status(int* out) {
   int v = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_sticky, sizeof(int));
   if (e != cudaSuccess) return (int)e;
+  if (v != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_tc_sticky, &zero, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+  }
   *out = v;
   return 0;
 }

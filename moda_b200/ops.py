@@ -14,9 +14,16 @@ form, which is a view of the folded call (query head ``hq = g*Hkv + h`` uses KV 
 Tensors must live on a CUDA device; every call launches on the current stream of
 ``q.device`` and does not synchronise.  Unlike the reference, strided (e.g.
 head-sliced) inputs are consumed in place when their innermost stride is 1 and the
-other strides are multiples of 8 elements; otherwise they are copied like the
-reference's ``@contiguous`` (fla/utils.py:130-161).  The tile-tuning keywords
-(``customized_*``, ``group_bs`` ...) are accepted and ignored.
+stride of every other dimension of size > 1 is a positive multiple of 8 elements;
+otherwise (odd strides, expanded or flipped views) they are copied like the
+reference's ``@contiguous`` (fla/utils.py:130-161).  The tile-tuning arguments
+(``customized_*``, ``group_bs`` ...) sit in the reference's positions and are ignored:
+the library has one fixed sm_100a configuration per kernel.
+
+The tcgen05 kernels bound every wait; a wait that expires makes its launch return early
+with outputs unwritten and records the fact in a sticky device word.  Nothing here
+synchronises to look at it: a caller that needs the guarantee reads
+``moda_b200.device_status()`` (0 = fine; resets on read) at its next synchronisation point.
 """
 from __future__ import annotations
 
@@ -48,9 +55,12 @@ def set_kernel_path(path: int) -> int:
 
 
 def _usable(x: torch.Tensor) -> torch.Tensor:
-    if x.stride(-1) == 1 and all(s % 8 == 0 for s in x.stride()[:-1]) and x.data_ptr() % 16 == 0:
-        return x
-    return x.contiguous()
+    """``x`` itself when the library can consume its layout in place, else a contiguous copy."""
+    ok = x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+    for size, stride in zip(x.shape[:-1], x.stride()[:-1]):
+        if size > 1 and (stride <= 0 or stride % 8 != 0):   # expanded (0) and odd strides are copied
+            ok = False
+    return x if ok else x.contiguous()
 
 
 def _t4(x: Optional[torch.Tensor]) -> Optional[Tensor4]:
@@ -264,7 +274,9 @@ def parallel_fda(q, k=None, v=None, g=None, cached_k=None, cached_v=None, scale=
 
 # ---- low-level forms (no autograd), same returns as the reference ------------------
 def parallel_moda_fwd(q, k, v, g_cumsum=None, scale=None, cu_seqlens=None, cached_k=None,
-                      cached_v=None, moda_group_num=1, is_causal=True, **_tile_knobs):
+                      cached_v=None, moda_group_num=1, is_causal=True, customized_BT=None,
+                      customized_BS=None, customized_BK=None, customized_BV=None,
+                      customized_num_warps=None):
     """(o, lse) — reference: moda_v14.py:381-522."""
     assert g_cumsum is None and cu_seqlens is None
     scale = q.shape[-1] ** -0.5 if scale is None else scale
@@ -273,7 +285,10 @@ def parallel_moda_fwd(q, k, v, g_cumsum=None, scale=None, cu_seqlens=None, cache
 
 
 def parallel_moda_bwd(q, k, v, o, g_cumsum, lse, do, scale=None, chunk_size=128, cu_seqlens=None,
-                      cached_k=None, cached_v=None, moda_group_num=1, is_causal=True, **_tile_knobs):
+                      cached_k=None, cached_v=None, moda_group_num=1, is_causal=True,
+                      customized_BT=None, customized_BS=None, customized_BK=None, customized_BV=None,
+                      customized_num_warps=None, group_bs=None, group_warps=None, depth_bs=None,
+                      depth_warps=None):
     """(dq, dk, dv, dg_cumsum=None, d_cached_k, d_cached_v) — reference: moda_v14.py:1470-1842.
     ``chunk_size`` is unused, as in the reference."""
     assert g_cumsum is None and cu_seqlens is None
@@ -284,7 +299,9 @@ def parallel_moda_bwd(q, k, v, o, g_cumsum, lse, do, scale=None, chunk_size=128,
 
 
 def parallel_moda_chunk_visible_fwd(q, k, v, g_cumsum=None, scale=None, cu_seqlens=None,
-                                    cached_k=None, cached_v=None, moda_group_num=1, **_tile_knobs):
+                                    cached_k=None, cached_v=None, moda_group_num=1,
+                                    customized_BT=None, customized_BS=None, customized_BK=None,
+                                    customized_BV=None, customized_num_warps=None):
     """(o, lse) — reference: moda_v16.py:498-633."""
     assert g_cumsum is None and cu_seqlens is None
     scale = q.shape[-1] ** -0.5 if scale is None else scale
@@ -293,7 +310,8 @@ def parallel_moda_chunk_visible_fwd(q, k, v, g_cumsum=None, scale=None, cu_seqle
 
 def parallel_moda_chunk_visible_bwd(q, k, v, o, g_cumsum, lse, do, scale=None, chunk_size=128,
                                     cu_seqlens=None, cached_k=None, cached_v=None,
-                                    moda_group_num=1, **_tile_knobs):
+                                    moda_group_num=1, customized_BT=None, customized_BS=None,
+                                    customized_BK=None, customized_BV=None, customized_num_warps=None):
     """(dq, dk, dv, None, d_cached_k, d_cached_v) — reference: moda_v16.py:2099-2343."""
     assert g_cumsum is None and cu_seqlens is None
     scale = q.shape[-1] ** -0.5 if scale is None else scale
@@ -303,21 +321,47 @@ def parallel_moda_chunk_visible_bwd(q, k, v, o, g_cumsum, lse, do, scale=None, c
 
 
 def parallel_fda_fwd(q, g_cumsum=None, scale=None, cu_seqlens=None, cached_k=None, cached_v=None,
-                     moda_group_num=1, **_tile_knobs):
+                     moda_group_num=1, customized_BT=None, customized_BS=None, customized_BK=None,
+                     customized_BV=None, customized_num_warps=None):
     """(o, lse) — reference: fda_v12.py:261-400."""
     assert g_cumsum is None and cu_seqlens is None
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     return _forward(q, None, None, cached_k, cached_v, scale, moda_group_num, MODE_DEPTH_ONLY)
 
 
-def parallel_fda_bwd(q, o, g_cumsum, lse, do, scale=None, cu_seqlens=None, cached_k=None,
-                     cached_v=None, moda_group_num=1, **_tile_knobs):
-    """(dq, dg_cumsum=None, d_cached_k, d_cached_v) — reference: fda_v12.py:881-1135."""
+def parallel_fda_bwd(q, o, g_cumsum, lse, do, scale=None, chunk_size=128, cu_seqlens=None,
+                     cached_k=None, cached_v=None, moda_group_num=1, customized_BT=None,
+                     customized_BS=None, customized_BK=None, customized_BV=None,
+                     customized_num_warps=None, group_bs=None, group_warps=None, depth_bs=None,
+                     depth_warps=None):
+    """(dq, dg_cumsum=None, d_cached_k, d_cached_v) — reference: fda_v12.py:881-1135.
+    ``chunk_size`` is unused, as in the reference."""
     assert g_cumsum is None and cu_seqlens is None
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     dq, _, _, dkd, dvd = _backward(q, None, None, cached_k, cached_v, o, lse, do, scale,
                                    moda_group_num, MODE_DEPTH_ONLY)
     return dq, None, dkd, dvd
+
+
+# ---- projection outputs -> operator inputs, without copies --------------------------
+def fold_qkv(q_proj, kv_proj, num_kv_heads: int, groups: int):
+    """Views of a block's projection outputs in the operator's layouts — no copy, no kernel.
+
+    ``q_proj [B, N, groups*num_kv_heads*D]`` (output of the query ``Linear``) and
+    ``kv_proj [B, N, 2*num_kv_heads*D]`` (output of the fused key/value ``Linear``) become
+    ``q [B, N*groups, num_kv_heads, D]`` (GQA folded into time, query head ``g*Hkv + h`` on KV
+    head ``h``), ``k`` and ``v [B, N, num_kv_heads, D]``, exactly as the reference's caller forms
+    them (vision_tasks/deit/models.py:244-253).  There ``k = kv[:, :, 0]`` and ``v = kv[:, :, 1]``
+    are strided views that the reference operator then copies (``@contiguous``,
+    fla/utils.py:139-140); this library reads them through their strides, so the projection's
+    epilogue already writes the layout the kernels consume and nothing is left to fuse.
+    """
+    B, N, C = q_proj.shape
+    D = C // (groups * num_kv_heads)
+    assert C == groups * num_kv_heads * D and kv_proj.shape == (B, N, 2 * num_kv_heads * D)
+    q = q_proj.reshape(B, N, groups, num_kv_heads, D).reshape(B, N * groups, num_kv_heads, D)
+    kv = kv_proj.reshape(B, N, 2, num_kv_heads, D)
+    return q, kv[:, :, 0], kv[:, :, 1]
 
 
 # ---- unfolded convenience form -----------------------------------------------------

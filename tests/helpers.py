@@ -11,7 +11,8 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TOL_O_MAX_ABS = 2e-2
 TOL_LSE_MAX_ABS = 1e-3
 TOL_GRAD_REL_L2 = 5e-2
-TOL_GRAD_MAX_ABS = 1e-2   # only for gradients whose oracle value is ~0
+TOL_GRAD_MAX_ABS = 1e-2   # only for gradients whose oracle value is numerically zero
+GRAD_ZERO_RMS = 1e-3      # an oracle gradient with rms below this has no meaningful relative error
 
 
 def golden_names():
@@ -40,3 +41,17 @@ def rel_l2(a, b):
 
 def t(x):
     return None if x is None else torch.from_numpy(np.asarray(x))
+
+
+def check_grad(name, got, ref):
+    """Gradient rule of the GPU parity tests: relative L2 error <= 5e-2.  Only where the oracle
+    gradient is numerically zero (rms < 1e-3: e.g. dq of a query with one visible key, whose
+    softmax is the constant 1) is the rule max-abs <= 1e-2 instead, as in the reference's own
+    test (tests/ops/test_moda.py:84-92) - and there the absolute bound is asserted."""
+    rms = ref.double().pow(2).mean().sqrt().item() if ref.numel() else 0.0
+    if rms < GRAD_ZERO_RMS:
+        ea = max_abs(got, ref) if ref.numel() else 0.0
+        assert ea <= TOL_GRAD_MAX_ABS, f"{name}: oracle gradient ~0 (rms {rms:.2e}), max-abs {ea}"
+    else:
+        e = rel_l2(got, ref)
+        assert e <= TOL_GRAD_REL_L2, f"{name}: rel-L2 {e} (oracle rms {rms:.2e})"

@@ -54,3 +54,28 @@ def test_reference_arm_prints_one_json_line_and_other_ranks_stay_silent():
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["value"] > 0
     assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
+
+
+def test_triton_baseline_arm_reports_unavailable_without_a_gpu():
+    """The reference-Triton leg never raises: without a CUDA device (or without the reference
+    install) it prints one JSON line that says why it has no numbers."""
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "triton_baseline"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-500:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "triton_baseline"
+    import torch
+    if not torch.cuda.is_available():
+        assert "unavailable" in line and line["results"] == []
+
+
+def test_kernel_attribution_tables_cover_the_same_kernels():
+    b = _bench()
+    assert set(b.OWNED_MATMULS) == set(b.EXECUTED_MATMULS)
+    # the forward owns both of its matmuls; a two-kernel backward owns three of the five algorithmic ones
+    assert b.OWNED_MATMULS["tc_fwd"] == 2 and b.OWNED_MATMULS["tc_dq"] + b.OWNED_MATMULS["tc_dkv"] == 3
+    for name in b.OTHER_WORKLOADS:
+        assert name in b.WORKLOADS
+    # the published shape: 14 * d * Hq * (T (T + 1) / 2 + T L) FLOP
+    fl = b.flops(*b.WORKLOADS["published_causal_T65536_d64"], fwd=True, bwd=True)
+    assert abs(fl - 14 * 64 * 64 * (65536 * 65537 // 2 + 65536 * 64)) < 1

@@ -72,8 +72,19 @@ def test_null_and_alignment_are_rejected_before_any_launch(lib):
     assert f(r(p), r(good), r(good), r(good), r(good), r(good), r(good), None, None) == 1     # lse NULL
     assert f(r(p), r(odd), r(good), r(good), r(good), r(good), r(good), 0x2000, None) == 5
     assert f(r(p), r(good), r(bad_stride), r(good), r(good), r(good), r(good), 0x2000, None) == 5
-    pt = _prob(path=2, D=64)     # tcgen05 path forced on a problem it may not take -> unsupported or ok
-    assert lib.moda_b200_resolve_path(r(pt), 0) in (2, -10)
+    # a zero or negative stride on a dimension of extent > 1 (expanded / flipped view) is refused;
+    # on a dimension of extent 1 (here the batch) the stride is irrelevant
+    zero_h = Tensor4(0x1000, 64 * 2 * 64, 2 * 64, 0)
+    neg_t = Tensor4(0x1000, 64 * 2 * 64, -2 * 64, 64)
+    any_b = Tensor4(0x1000, 0, 2 * 64, 64)
+    assert f(r(p), r(good), r(zero_h), r(good), r(good), r(good), r(good), 0x2000, None) == 5
+    assert f(r(p), r(good), r(good), r(neg_t), r(good), r(good), r(good), 0x2000, None) == 5
+    p2 = _prob(B=2)
+    assert f(r(p2), r(good), r(any_b), r(good), r(good), r(good), r(good), 0x2000, None) == 5
+    assert lib.moda_b200_resolve_path(r(_prob(path=2, D=64)), 0) == 2          # tcgen05 kernels take D = 64 and 128
+    assert lib.moda_b200_resolve_path(r(_prob(path=4, D=128)), 1) == 2
+    assert lib.moda_b200_resolve_path(r(_prob(path=2, scale=-1.0)), 0) == -10  # ... but only a positive scale
+    assert lib.moda_b200_resolve_path(r(_prob(path=0, scale=-1.0)), 0) == 1
 
 
 def test_workspace_size_and_bwd_rejects_small_workspace(lib):
@@ -116,6 +127,31 @@ def test_python_wrappers_mirror_reference_assertions(built_library):
             M.parallel_moda(torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16),
                             torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16),
                             torch.zeros(1, 2, 4, 64, dtype=torch.bfloat16))
+
+
+def test_fold_qkv_returns_views_of_the_projection_outputs(built_library):
+    """The projection outputs are consumed in place: q is a reshape, k and v are strided views of
+    the fused key/value projection (the layout vision_tasks/deit/models.py:244-253 builds), and the
+    library's layout rule accepts all three without a copy."""
+    import moda_b200 as M
+    from moda_b200 import ops
+    B, N, Hkv, G, D = 2, 197, 6, 1, 64
+    qp = torch.randn(B, N, G * Hkv * D).to(torch.bfloat16)
+    kvp = torch.randn(B, N, 2 * Hkv * D).to(torch.bfloat16)
+    q, k, v = M.fold_qkv(qp, kvp, Hkv, G)
+    assert q.shape == (B, N * G, Hkv, D) and k.shape == v.shape == (B, N, Hkv, D)
+    assert q.data_ptr() == qp.data_ptr() and k.data_ptr() == kvp.data_ptr()
+    assert v.data_ptr() == kvp.data_ptr() + Hkv * D * 2 and not k.is_contiguous()
+    for x in (q, k, v):
+        assert ops._usable(x) is x
+    assert torch.equal(k, kvp.view(B, N, 2, Hkv, D)[:, :, 0])
+    # G > 1: query head g*Hkv + h sits at folded row n*G + g of KV head h
+    qp2 = torch.randn(1, 5, 3 * 2 * D)
+    q2, _, _ = M.fold_qkv(qp2, torch.randn(1, 5, 2 * 2 * D), 2, 3)
+    assert torch.equal(q2[0, 4 * 3 + 1, 1], qp2[0, 4].view(3, 2, D)[1, 1])
+    # an expanded view is not usable in place
+    e = torch.zeros(1, 8, 2, 64).expand(3, -1, -1, -1)
+    assert ops._usable(e) is not e
 
 
 def test_product_package_does_not_import_the_oracle():

@@ -20,7 +20,7 @@ import pytest
 import torch
 
 from oracle import moda_oracle as mo
-from tests.helpers import TOL_GRAD_MAX_ABS, TOL_GRAD_REL_L2, max_abs, rel_l2
+from tests.helpers import check_grad
 
 pytestmark = pytest.mark.gpu
 
@@ -74,18 +74,26 @@ def test_static_scratch_backward_matches_workspace_backward(built_library, mode,
     g_a, g_b = grads_like(), grads_like()
     stream = torch.cuda.current_stream().cuda_stream
     ins = [_t4(x) for x in (q, k, v, kd, vd, o)]
-    torch.cuda.synchronize()
-    mem_before = torch.cuda.memory_allocated()
-
     rc = lib.moda_b200_bwd(ctypes.byref(prob), *ins, lse.data_ptr(), _t4(dout), *[_t4(g) for g in g_ws],
                            ws.data_ptr(), ws.numel(), stream)
     assert rc == 0, _cabi.status_string(rc)
+    # a first static-scratch call outside the measured window: it resolves the array's address and
+    # lets the driver finish any lazy loading of the kernels involved
+    rc = lib.moda_b200_bwd_static_scratch(ctypes.byref(prob), *ins, lse.data_ptr(), _t4(dout),
+                                          *[_t4(g) for g in g_b], stream)
+    assert rc == 0, _cabi.status_string(rc)
+    torch.cuda.synchronize()
+    # torch's counter sees only torch's caching allocator; the driver's free-memory figure also sees
+    # a cudaMalloc made inside the library
+    mem_before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]
     for dst in (g_a, g_b):   # two calls in a row share the static array
         rc = lib.moda_b200_bwd_static_scratch(ctypes.byref(prob), *ins, lse.data_ptr(), _t4(dout),
                                               *[_t4(g) for g in dst], stream)
         assert rc == 0, _cabi.status_string(rc)
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == mem_before
+    assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was allocated during the static-scratch calls"
     assert _cabi.device_status() == 0
 
     for name, gw, ga, gb, gr in zip(("dq", "dk", "dv", "d_depth_k", "d_depth_v"), g_ws, g_a, g_b, ref[2:]):
@@ -94,8 +102,7 @@ def test_static_scratch_backward_matches_workspace_backward(built_library, mode,
         assert not torch.isnan(ga.float()).any() and not torch.isnan(gb.float()).any(), name
         assert torch.equal(ga, gw), f"{name}: first static-scratch call differs from the workspace call"
         assert torch.equal(gb, gw), f"{name}: second static-scratch call differs from the workspace call"
-        e, ea = rel_l2(ga.float().cpu(), gr), max_abs(ga.float().cpu(), gr)
-        assert e <= TOL_GRAD_REL_L2 or ea <= TOL_GRAD_MAX_ABS, f"{name} rel-L2 {e}"
+        check_grad(name, ga.float().cpu(), gr)
 
 
 def test_static_scratch_rejects_oversized_problem(built_library):
