@@ -59,6 +59,7 @@ OTHER_WORKLOADS = {
     "config3_fda_T8192": ("fwd+bwd", "hbm"),
     "config5_deit_noncausal_T197": ("fwd+bwd", "hbm"),
     "published_causal_T65536_d64": ("fwd+bwd", "tensor"),
+    "config4_d64_twin_T65536": ("fwd+bwd", "tensor"),      # the shape the reference's Triton leg is timed on
 }
 PUBLISHED_A100_MS = {"published_causal_T65536_d64": 1883.026}   # reference README.md:94 (MoDA-Triton, A100)
 DEFAULT_WORKLOAD = "config4_chunk_visible_T65536"
@@ -339,8 +340,23 @@ def run_reference_arm(args, wl):
 # process, so that a Triton compile error or an assertion of the reference cannot take the
 # benchmark down with it.
 # ---------------------------------------------------------------------------------------------
-TRITON_WORKLOADS = ["config2_causal_T4096", "config3_fda_T8192", "config5_deit_noncausal_T197",
-                    "config4_chunk_visible_T65536", "config4_d64_twin_T65536", "published_causal_T65536_d64"]
+TRITON_WORKLOADS = ["config4_chunk_visible_T65536", "config4_d64_twin_T65536"]
+# Workloads whose reference launchers are NOT run on this GPU.  parallel_moda (moda_v14.py) and
+# parallel_fda (fda_v12.py) pick their tiles by device name; a B200 matches none of the names and
+# gets the generic large-shared-memory branch (BT=128, BS=64, 8 warps: moda_v14.py:423-427,
+# fda_v12.py:304-308), which the reference never ran on its own GPUs (they are all forced to 64-wide
+# tiles, moda_v14.py:452-471).  On config 2 that branch ended in "CUDA error: an illegal memory
+# access was encountered" on a B200 (Triton 3.6, first call, inputs valid by the reference's own
+# assertions), so code taking that branch is not launched again; the chunk-visible operator
+# hard-codes the 64-wide tiles on every GPU (moda_v16.py:581-585) and is the one that is timed.
+TRITON_NOT_RUN = {
+    "config2_causal_T4096": "faulted: CUDA error: an illegal memory access was encountered (parallel_moda forward, "
+                            "generic-GPU tile branch BT=128/BS=64/8 warps, first call on a B200); not run again",
+    "config3_fda_T8192": "not run: parallel_fda takes the same untested generic-GPU tile branch (fda_v12.py:304-308) "
+                         "whose parallel_moda twin faulted on this GPU",
+    "config5_deit_noncausal_T197": "not run: parallel_moda, same launcher branch as the call that faulted",
+    "published_causal_T65536_d64": "not run: parallel_moda, same launcher branch as the call that faulted",
+}
 
 
 def run_triton_baseline_arm(args):
@@ -375,7 +391,13 @@ def run_triton_baseline_arm(args):
         return
     dev = torch.device("cuda", 0)
     names = [args.workload] if args.workload != DEFAULT_WORKLOAD or args.only_workload else TRITON_WORKLOADS
+    out["not_run"] = TRITON_NOT_RUN
+    names = [n for n in names if n not in TRITON_NOT_RUN]
+    context_lost = False
     for name in names:
+        if context_lost:
+            out["results"].append({"workload": name, "unavailable": "not run: an earlier workload left the CUDA context unusable"})
+            continue
         mode, B, T, Hkv, G, D, L = WORKLOADS[name]
         fwd_only = OTHER_WORKLOADS.get(name, ("fwd+bwd",))[0] == "fwd"
         rec = {"workload": name, "mode": mode, "B": B, "T": T, "Hkv": Hkv, "G": G, "D": D, "L": L,
@@ -435,8 +457,9 @@ def run_triton_baseline_arm(args):
             if isinstance(exc, KeyboardInterrupt):
                 raise
             rec["unavailable"] = f"{type(exc).__name__}: {exc}"[:600]
-        finally:
-            q = k = v = kd = vd = dout = None
+            context_lost = "CUDA error" in str(exc)
+        q = k = v = kd = vd = dout = None
+        if not context_lost:
             torch.cuda.empty_cache()
         out["results"].append(rec)
     print(json.dumps(out), flush=True)
