@@ -37,7 +37,8 @@ constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delt
 constexpr uint32_t kStepHalf = 64 * 64 * 2;    // one TMA box of a step tile: [64 rows x 64 elements]
 template <int D> __host__ __device__ constexpr uint32_t step_tile() { return (uint32_t)(D / 64) * kStepHalf; }   // [64 x D] 16-bit tile
 constexpr uint32_t kScoreTile = 128 * 64 * 2;  // [128 x 64] 16-bit tile of dS, P^T or dS^T (K-major, 128 B per row)
-constexpr int kDkvThreads = 352;               // dk/dv: 8 softmax warps + score-MMA, TMA and update-MMA warps
+constexpr int kDqThreads = 352;                // 8 softmax warps + score-MMA, TMA and update-MMA warps
+constexpr int kDkvThreads = kDqThreads;
 
 struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
 struct DkvMaps { CUtensorMap k, v, kd, vd, q, dout; };     // k, v, kd, vd: 128-row boxes; q, dout 64-row
@@ -122,20 +123,13 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_s
 __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { return d + (uint64_t)(byte_off >> 4); }
 
 // ============================================================================ dq
-// grid (ceil(T_q/128), H, B), 320 threads.  TMEM (512 columns):
-//   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32); the softmax warps write
-//   dS (16-bit) over the first 32 columns of the stage's S block;
+// grid (ceil(T_q/128), H, B), 352 threads.  TMEM (512 columns):
+//   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32);
 //   [256, 256+D) dQ (fp32);  [384, 384+D/2) Q (16-bit A operand);  [448, 448+D/2) dO (16-bit A operand).
-// Shared memory: ring of kDqRing x {K step tile, V step tile} ([64 x D] each).
-// One MMA warp issues everything, in the order
-//     scores(0), scores(1), update(0), scores(2), update(1), scores(3), ...
-// The tensor pipe executes the MMAs of one thread in issue order, so scores(j+2) may overwrite the
-// stage update(j) reads its dS from without a wait in between, and every operand of every MMA but
-// the K / V step tile comes from TMEM: the update dQ += dS K (A = dS in TMEM, B = K tile read
-// MN-major) runs at the rate of the forward's P V instead of the shared-memory rate an A operand
-// staged in shared memory gave it.
-constexpr int kDqThreads = 320;                // 8 softmax warps, MMA warp, TMA warp
-
+// Shared memory: ring of kDqRing x {K step tile, V step tile} ([64 x D] each), then two
+// [128 x 64] dS tiles (K-major, 128-byte swizzle).  A softmax warpgroup releases its TMEM stage
+// as soon as it has the scores in registers, so the next-but-one score MMAs overlap its math;
+// dS reaches the update MMA through shared memory.
 template <typename T, int D>
 __global__ void __launch_bounds__(kDqThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
@@ -150,7 +144,9 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     return;
   }
   const uint32_t sRing = base;
-  const uint32_t ctl_off = R * 2 * kStepTile;
+  const uint32_t ds_off = R * 2 * kStepTile;            // two dS tiles of kScoreTile bytes
+  const uint32_t sDS = base + ds_off;
+  const uint32_t ctl_off = ds_off + 2 * kScoreTile;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
@@ -183,7 +179,10 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     mbar_init(bars + 8 * B_.res, 256);
     mbar_init(bars + 8 * B_.done, 1);
     for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128);
+      mbar_init(bars + 8 * (B_.r0 + i), 128); mbar_init(bars + 8 * (B_.t0 + i), 1);
+    }
     *abort_flag = 0;
     *drain_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -228,16 +227,17 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       }
     }
   } else if (warp == 8) {
-    // ---------------------------------------------------------------- MMA warp
+    // ---------------------------------------------------------------- score-MMA warp
+    // S(i) = Q K(i)^T and dP(i) = dO V(i)^T into TMEM stage i&1, as soon as the warpgroup that
+    // owned the stage has the previous scores in registers and the step tiles have landed.
     if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
-      constexpr uint32_t idesc_t = instr_desc(fmt, D, true);
       bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // Q, dO are in TMEM
       tc_fence_after();
-      // S(i) = Q K(i)^T and dP(i) = dO V(i)^T into TMEM stage i & 1
-      auto scores = [&](int i) -> bool {
+      for (int i = 0; ok && i < n; ++i) {
         const uint32_t slot = i % R;
-        if (!mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot)) return false;
+        if (i >= 2 && !(ok = mbar_wait(bars + 8 * (B_.r0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.r0 + (i & 1)))) break;
+        if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
         tc_fence_after();
         const uint32_t sK = sRing + slot * 2 * kStepTile;
         const uint64_t dk = desc_kmajor(sK), dv = desc_kmajor(sK + kStepTile);
@@ -251,26 +251,30 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
           tc_commit(bars + 8 * (B_.s0 + (i & 1)));
         }
         __syncwarp();
-        return true;
-      };
-      if (ok) ok = scores(0);
-      if (ok && n > 1) ok = scores(1);
+      }
+    }
+  } else if (warp == 10) {
+    // ---------------------------------------------------------------- update-MMA warp
+    // dQ += dS(j) K(j): A = dS tile in shared memory, B = K step tile read MN-major.  A warp of
+    // its own, so that an update never waits behind the issue of the next scores.
+    if (n > 0) {
+      constexpr uint32_t idesc_t = instr_desc(fmt, D, true);
+      bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
-        // dQ += dS(j) K(j): A = dS, written by the softmax warps over stage j & 1
         if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
         tc_fence_after();
         const uint32_t slot = j % R;
+        const uint64_t da = desc_kmajor(sDS + (j & 1) * kScoreTile);
         const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
-        const uint32_t tA = tmem + (j & 1) * 128;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ts(tmem_dQ, tA + kk * 8, desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
           tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
+          tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // dS tile j&1 may be rewritten
           if (j == n - 1) tc_commit(bars + 8 * B_.done);
         }
         __syncwarp();
-        if (j + 2 < n) ok = scores(j + 2);
       }
     }
   } else {
@@ -325,6 +329,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       tmem_ld32<0>(tS + 64, du);
       tmem_ld32<32>(tS + 96, du);
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: stage is free
       // straight-line passes over the 64 columns (no branches inside, so the scheduler can
       // overlap the exp2 latency of one column with the arithmetic of the others)
       float pr[64];
@@ -342,10 +348,17 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       for (int jj = 0; jj < 32; ++jj)
         pk[jj] = Pack<T>::pack(pr[2 * jj] * (__uint_as_float(du[2 * jj]) - dl_r),
                                pr[2 * jj + 1] * (__uint_as_float(du[2 * jj + 1]) - dl_r));
-      // dS as the 16-bit A operand of the update, over the scores this thread has just read
-      tmem_st32<0>(tS, pk);
-      tmem_wait_st();
-      tc_fence_before();
+      if (i >= 2) {   // the update of step i-2 must have finished reading this dS tile
+        ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
+        if (!ok) break;
+      }
+      {   // row of the K-major, 128B-swizzled [128 x 64] tile: 16-byte chunk c lives at chunk c ^ (row & 7)
+        unsigned char* prow = smem_raw + ds_off + (i & 1) * kScoreTile + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
@@ -1063,7 +1076,7 @@ inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, float* delta_t,
   *launches += 1;
   {
     auto kern = dq_kernel<T, D>;
-    const size_t smem = kDqRing * 2 * (size_t)step_tile<D>() + kCtlBytes;
+    const size_t smem = kDqRing * 2 * (size_t)step_tile<D>() + 2 * (size_t)kScoreTile + kCtlBytes;
     if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
     dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
     prof::Scope ps(prof::kDqTc, st);
