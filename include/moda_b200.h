@@ -17,6 +17,9 @@
  *     [B, T_kv*G, H, D]; query row r belongs to base position t = r / G.
  *   - depth_k / depth_v are [B, T_kv*L, H, D]; row t*L + l is layer l at position t
  *     (moda_v14.py:1944-1945).  L == 0 means "no depth KV" (pass NULL tensors).
+ *     With moda_problem.depth_rows_per_pos = Lmax > L they are instead the first L layers
+ *     of an in-place layer cache [B, T_kv, Lmax, H, D] (row t*Lmax + l), see
+ *     moda_b200_depth_append; the depth gradients use the same layout as the inputs.
  *   - lse is fp32 [B, T_kv*G, H] contiguous, in base-2 units (moda_v14.py:372-374).
  *   - Every call is asynchronous on `stream` (a cudaStream_t), never synchronises,
  *     never allocates device memory, and returns a moda_status (0 = success).
@@ -92,6 +95,13 @@ typedef struct moda_problem {
   int32_t path;       /* moda_path                                                 */
   float scale;        /* softmax scale (reference default D**-0.5)                 */
   int32_t device;     /* CUDA device ordinal the pointers live on                  */
+  int32_t depth_rows_per_pos;     /* memory rows per position of depth_k/v and d_depth_k/v: 0 or L
+                                     = packed [B, T_kv*L, H, D]; Lmax > L = in-place layer cache
+                                     [B, T_kv, Lmax, H, D] of which the first L layers are valid   */
+  int32_t accumulate_depth_grads; /* backward: non-zero adds d_depth_k/v to what the buffers hold
+                                     (a gradient cache several layers share) instead of overwriting;
+                                     each depth row has one owning thread block, so the result does
+                                     not depend on scheduling                                       */
 } moda_problem;
 
 /*
@@ -168,6 +178,19 @@ int moda_b200_bwd_static_scratch(const moda_problem *prob, const moda_tensor4 *q
                                  const moda_tensor4 *dk, const moda_tensor4 *dv,
                                  const moda_tensor4 *d_depth_k, const moda_tensor4 *d_depth_v,
                                  void *stream);
+
+/*
+ * In-place depth-KV cache: copies one layer's k and v ([B, T_kv, H, D], any supported strides)
+ * into slot `layer` of the caches cache_k / cache_v, given as [B, T_kv*Lmax, H, D] tensors with
+ * Lmax = prob->depth_rows_per_pos (row t*Lmax + layer).  Later layers pass the same cache
+ * tensors as depth_k / depth_v with L = number of layers appended so far.  Replaces the reference
+ * caller's rebuild of the depth cache before every layer (torch.stack + reshape + contiguous over
+ * all earlier layers: vision_tasks/deit/models.py:361-375).  Uses B, T_kv, H, D, dtype, device
+ * and depth_rows_per_pos of `prob`; 0 <= layer < Lmax.
+ */
+int moda_b200_depth_append(const moda_problem *prob, const moda_tensor4 *k, const moda_tensor4 *v,
+                           const moda_tensor4 *cache_k, const moda_tensor4 *cache_v, int32_t layer,
+                           void *stream);
 
 /*
  * Validation only (no launch): the status moda_b200_fwd / moda_b200_bwd would return

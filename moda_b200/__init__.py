@@ -19,6 +19,7 @@ from .ops import (  # noqa: F401
     parallel_moda_fwd,
     set_kernel_path,
 )
+from .depth_cache import DepthKVCache  # noqa: F401
 from ._cabi import (  # noqa: F401
     MODE_CAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY, MODE_NONCAUSAL,
     PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05, PATH_TCGEN05_ONE_TILE, PATH_TCGEN05_TWO_TILES, ModaLibraryError,
@@ -29,5 +30,5 @@ __all__ = [
     "parallel_moda", "parallel_moda_fwd", "parallel_moda_bwd",
     "parallel_moda_chunk_visible", "parallel_moda_chunk_visible_fwd", "parallel_moda_chunk_visible_bwd",
     "parallel_fda", "parallel_fda_fwd", "parallel_fda_bwd",
-    "moda_attention", "fold_qkv", "set_kernel_path", "last_launch_count", "device_status",
+    "moda_attention", "fold_qkv", "DepthKVCache", "set_kernel_path", "last_launch_count", "device_status",
 ]

@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "moda_b200_bwd_workspace_bytes",
     "moda_b200_bwd",
     "moda_b200_bwd_static_scratch",
+    "moda_b200_depth_append",
     "moda_b200_check_problem",
     "moda_b200_resolve_path",
     "moda_b200_profile_begin",
@@ -61,6 +62,8 @@ class Problem(ctypes.Structure):
         ("path", ctypes.c_int32),
         ("scale", ctypes.c_float),
         ("device", ctypes.c_int32),
+        ("depth_rows_per_pos", ctypes.c_int32),      # 0 / L: packed depth KV; Lmax > L: in-place layer cache
+        ("accumulate_depth_grads", ctypes.c_int32),  # backward adds the depth gradients instead of overwriting
     ]
 
 
@@ -94,6 +97,8 @@ def load() -> ctypes.CDLL:
     lib.moda_b200_bwd.restype = ctypes.c_int
     lib.moda_b200_bwd_static_scratch.argtypes = [P] + [T] * 6 + [V] + [T] * 6 + [V]
     lib.moda_b200_bwd_static_scratch.restype = ctypes.c_int
+    lib.moda_b200_depth_append.argtypes = [P, T, T, T, T, ctypes.c_int32, V]
+    lib.moda_b200_depth_append.restype = ctypes.c_int
     lib.moda_b200_check_problem.argtypes = [P]
     lib.moda_b200_check_problem.restype = ctypes.c_int
     lib.moda_b200_resolve_path.argtypes = [P, ctypes.c_int]

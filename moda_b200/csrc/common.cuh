@@ -34,7 +34,19 @@ struct Params {
   // backward: dq = the depth rows' share) and this launch, run with L = 0, folds its sequence
   // part into it in the epilogue.
   int merge_depth;
+  // Depth rows per position IN MEMORY.  Ls == L: the packed [B, T*L, H, D] layout (row t*L + l).
+  // Ls > L: rows (t, l), l < L, of an in-place cache [B, T, Ls, H, D] written layer by layer,
+  // i.e. depth row c = t*L + l of the operator lives at memory row t*Ls + l; the depth gradients
+  // use the same layout.  acc_depth: add d_depth_k / d_depth_v to what the buffers hold instead of
+  // overwriting (every depth row has one owning thread block, so this stays deterministic).
+  int Ls;
+  int acc_depth;
 };
+
+// Memory row of depth row c (see Params::Ls).
+__host__ __device__ __forceinline__ int64_t dep_mem_row(const Params& p, int64_t c) {
+  return (p.Ls == p.L) ? c : (c / p.L) * p.Ls + (c % p.L);
+}
 
 // ---------------------------------------------------------------------------
 // Visibility.  A query row r (base position t = r / G) sees

@@ -19,6 +19,13 @@ template <typename T> __device__ __forceinline__ void unpack8(const uint4& u, fl
   const float2 a = Pack<T>::unpack(u.x), b = Pack<T>::unpack(u.y), c = Pack<T>::unpack(u.z), d = Pack<T>::unpack(u.w);
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
+// f += the eight stored 16-bit values of u
+template <typename T> __device__ __forceinline__ void add8(float (&f)[8], const uint4& u) {
+  float g[8];
+  unpack8<T>(u, g);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] += g[e];
+}
 template <typename T> __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return make_uint4(Pack<T>::pack(f[0], f[1]), Pack<T>::pack(f[2], f[3]), Pack<T>::pack(f[4], f[5]), Pack<T>::pack(f[6], f[7]));
 }
@@ -69,8 +76,8 @@ __global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Par
   for (int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < n_units; unit += wstride) {
     int b, t, h;
     decode_unit(unit, p.H, p.T_kv, b, t, h);
-    const T* kb = reinterpret_cast<const T*>(p.kd.ptr) + p.kd.off(b, (int64_t)t * p.L, h);
-    const T* vb = reinterpret_cast<const T*>(p.vd.ptr) + p.vd.off(b, (int64_t)t * p.L, h);
+    const T* kb = reinterpret_cast<const T*>(p.kd.ptr) + p.kd.off(b, (int64_t)t * p.Ls, h);
+    const T* vb = reinterpret_cast<const T*>(p.vd.ptr) + p.vd.off(b, (int64_t)t * p.Ls, h);
     for (int g = 0; g < p.G; ++g) {
       const int r = t * p.G + g;
       float qf[CH][8];
@@ -182,10 +189,10 @@ __global__ void __launch_bounds__(128, (G == 1) ? 3 : 2) bwd_kernel(const __grid
   for (int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < n_units; unit += wstride) {
     int b, t, h;
     decode_unit(unit, p.H, p.T_kv, b, t, h);
-    const T* kb = reinterpret_cast<const T*>(p.kd.ptr) + p.kd.off(b, (int64_t)t * p.L, h);
-    const T* vb = reinterpret_cast<const T*>(p.vd.ptr) + p.vd.off(b, (int64_t)t * p.L, h);
-    T* dkb = reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, (int64_t)t * p.L, h);
-    T* dvb = reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(b, (int64_t)t * p.L, h);
+    const T* kb = reinterpret_cast<const T*>(p.kd.ptr) + p.kd.off(b, (int64_t)t * p.Ls, h);
+    const T* vb = reinterpret_cast<const T*>(p.vd.ptr) + p.vd.off(b, (int64_t)t * p.Ls, h);
+    T* dkb = reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(b, (int64_t)t * p.Ls, h);
+    T* dvb = reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(b, (int64_t)t * p.Ls, h);
 
     uint4 qraw[G][CH], doraw[G][CH];
     float lse_g[G], delta_g[G];
@@ -264,8 +271,14 @@ __global__ void __launch_bounds__(128, (G == 1) ? 3 : 2) bwd_kernel(const __grid
           for (int c = 0; c < CH; ++c) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) dkr[c][e] *= p.scale;
-            *reinterpret_cast<uint4*>(dkb + (int64_t)key * p.dkd.st + (sub + 8 * c) * 8) = pack8<T>(dkr[c]);
-            *reinterpret_cast<uint4*>(dvb + (int64_t)key * p.dvd.st + (sub + 8 * c) * 8) = pack8<T>(dvr[c]);
+            uint4* gk4 = reinterpret_cast<uint4*>(dkb + (int64_t)key * p.dkd.st + (sub + 8 * c) * 8);
+            uint4* gv4 = reinterpret_cast<uint4*>(dvb + (int64_t)key * p.dvd.st + (sub + 8 * c) * 8);
+            if (p.acc_depth) {   // gradient cache shared by several layers: add to what earlier calls left
+              add8<T>(dkr[c], *gk4);
+              add8<T>(dvr[c], *gv4);
+            }
+            *gk4 = pack8<T>(dkr[c]);
+            *gv4 = pack8<T>(dvr[c]);
           }
         }
       }

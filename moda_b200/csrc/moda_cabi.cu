@@ -9,6 +9,7 @@
 #include "profiler.cuh"
 #include "simt_mma_kernels.cuh"
 #include "fda_kernels.cuh"
+#include "depth_cache_kernels.cuh"
 #ifndef MODA_NO_TCGEN05
 #include "tc_kernels.cuh"
 #include "tc_bwd_kernels.cuh"
@@ -70,6 +71,8 @@ int check_problem(const moda_problem* pr) {
   }
   if (pr->path < MODA_PATH_AUTO || pr->path > MODA_PATH_TCGEN05_TWO_TILES) return MODA_ERR_MODE;
   if (!(pr->scale == pr->scale)) return MODA_ERR_SHAPE;  // NaN scale
+  if (pr->depth_rows_per_pos < 0 || (pr->depth_rows_per_pos > 0 && pr->depth_rows_per_pos < pr->L)) return MODA_ERR_SHAPE;
+  if ((int64_t)pr->T_kv * pr->depth_rows_per_pos > (int64_t)1 << 30) return MODA_ERR_SHAPE;
   return MODA_OK;
 }
 
@@ -79,6 +82,8 @@ void fill_common(Params& p, const moda_problem* pr) {
   p.Cb = (pr->mode == MODA_CHUNK_VISIBLE) ? pr->chunk_rows / pr->G : 1;
   p.scale = pr->scale;
   p.scale_log2 = pr->scale * 1.4426950216f;
+  p.Ls = (pr->depth_rows_per_pos > pr->L) ? pr->depth_rows_per_pos : pr->L;
+  p.acc_depth = pr->accumulate_depth_grads != 0;
 }
 
 int cuda_fail(cudaError_t e) { g_last_cuda_error = (int)e; return MODA_ERR_CUDA; }
@@ -285,7 +290,8 @@ int moda_b200_fwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (int rc = check_problem(prob)) return rc;
   const bool need_seq = prob->mode != MODA_DEPTH_ONLY;
   const bool need_dep = prob->L > 0;
-  const int64_t Tq = (int64_t)prob->T_kv * prob->G, Tk = prob->T_kv, Td = (int64_t)prob->T_kv * prob->L;
+  const int64_t Tq = (int64_t)prob->T_kv * prob->G, Tk = prob->T_kv;
+  const int64_t Td = (int64_t)prob->T_kv * (prob->depth_rows_per_pos > prob->L ? prob->depth_rows_per_pos : prob->L);
   if (int rc = check_tensor(q, true, prob->B, Tq, prob->H)) return rc;
   if (int rc = check_tensor(k, need_seq, prob->B, Tk, prob->H)) return rc;
   if (int rc = check_tensor(v, need_seq, prob->B, Tk, prob->H)) return rc;
@@ -343,7 +349,8 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
   if (int rc = check_problem(prob)) return rc;
   const bool need_seq = prob->mode != MODA_DEPTH_ONLY;
   const bool need_dep = prob->L > 0;
-  const int64_t Tq = (int64_t)prob->T_kv * prob->G, Tk = prob->T_kv, Td = (int64_t)prob->T_kv * prob->L;
+  const int64_t Tq = (int64_t)prob->T_kv * prob->G, Tk = prob->T_kv;
+  const int64_t Td = (int64_t)prob->T_kv * (prob->depth_rows_per_pos > prob->L ? prob->depth_rows_per_pos : prob->L);
   const int Bn = prob->B, Hn = prob->H;
   if (int rc = check_tensor(q, true, Bn, Tq, Hn)) return rc;
   if (int rc = check_tensor(k, need_seq, Bn, Tk, Hn)) return rc;
@@ -397,6 +404,41 @@ int moda_b200_bwd(const moda_problem* prob, const moda_tensor4* q, const moda_te
 #endif
   return prob->dtype == MODA_BF16 ? simt_bwd_d<__nv_bfloat16>(p, prob->D, n_sm, st)
                                   : simt_bwd_d<__half>(p, prob->D, n_sm, st);
+}
+
+int moda_b200_depth_append(const moda_problem* prob, const moda_tensor4* k, const moda_tensor4* v,
+                           const moda_tensor4* cache_k, const moda_tensor4* cache_v, int32_t layer, void* stream) {
+  if (prob == nullptr) return MODA_ERR_NULL;
+  if (prob->B < 1 || prob->T_kv < 1 || prob->H < 1 || prob->B > 65535 || prob->H > 65535) return MODA_ERR_SHAPE;
+  if (prob->D != 64 && prob->D != 128) return MODA_ERR_HEAD_DIM;
+  if (prob->dtype != MODA_BF16 && prob->dtype != MODA_FP16) return MODA_ERR_DTYPE;
+  const int Lmax = prob->depth_rows_per_pos;
+  if (Lmax < 1 || layer < 0 || layer >= Lmax || (int64_t)prob->T_kv * Lmax > (int64_t)1 << 30) return MODA_ERR_SHAPE;
+  if (int rc = check_tensor(k, true, prob->B, prob->T_kv, prob->H)) return rc;
+  if (int rc = check_tensor(v, true, prob->B, prob->T_kv, prob->H)) return rc;
+  if (int rc = check_tensor(cache_k, true, prob->B, (int64_t)prob->T_kv * Lmax, prob->H)) return rc;
+  if (int rc = check_tensor(cache_v, true, prob->B, (int64_t)prob->T_kv * Lmax, prob->H)) return rc;
+  DeviceGuard guard(prob->device);
+  if (!guard.ok) return cuda_fail(guard.err);
+  g_last_launches = 0;
+  const int n_sm = sm_count(prob->device);
+  if (n_sm <= 0) return cuda_fail(cudaErrorInvalidDevice);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t n = (int64_t)prob->B * prob->T_kv * prob->H * (prob->D / 8);
+  const int64_t want = (n + 255) / 256, cap = (int64_t)n_sm * 16;
+  const int blocks = (int)(want < cap ? want : cap);
+  {
+    prof::Scope ps(prof::kDepthAppend, st);
+    if (prob->D == 128)
+      cache::append_kernel<16><<<blocks, 256, 0, st>>>(to_view(k), to_view(v), to_view(cache_k), to_view(cache_v),
+                                                      prob->B, prob->T_kv, prob->H, Lmax, layer);
+    else
+      cache::append_kernel<8><<<blocks, 256, 0, st>>>(to_view(k), to_view(v), to_view(cache_k), to_view(cache_v),
+                                                     prob->B, prob->T_kv, prob->H, Lmax, layer);
+  }
+  MODA_CUDA(cudaGetLastError());
+  g_last_launches += 1;
+  return MODA_OK;
 }
 
 int moda_b200_profile_begin(void) {

@@ -10,11 +10,12 @@ namespace moda {
 namespace prof {
 
 enum KernelId : int {
-  kFwdSimt = 0, kDelta, kDqSimt, kDkvSimt, kFwdTc, kPreTc, kDqTc, kDkvTc, kFdaFwd, kFdaBwd, kDepthGradTc, kCount
+  kFwdSimt = 0, kDelta, kDqSimt, kDkvSimt, kFwdTc, kPreTc, kDqTc, kDkvTc, kFdaFwd, kFdaBwd, kDepthGradTc, kDepthAppend, kCount
 };
 inline const char* kernel_name(int id) {
   static const char* const names[kCount] = {"simt_fwd", "delta", "simt_dq", "simt_dkv", "tc_fwd",
-                                            "tc_bwd_pre", "tc_dq", "tc_dkv", "fda_fwd", "fda_bwd", "tc_depth_grad"};
+                                            "tc_bwd_pre", "tc_dq", "tc_dkv", "fda_fwd", "fda_bwd", "tc_depth_grad",
+                                            "depth_append"};
   return (id >= 0 && id < kCount) ? names[id] : "unknown";
 }
 

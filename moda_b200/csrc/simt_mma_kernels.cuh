@@ -54,16 +54,19 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // distinct banks).  Loaded with 16-byte cp.async; rows outside [0, nrows) are zeroed.
 template <typename T, int D> struct Tile {
   static constexpr int LD = D + 8;
+  // L, Ls: rows come in groups of L that sit Ls rows apart in memory (the depth K/V of an in-place
+  // layer cache, Params::Ls); L == Ls is the plain contiguous case.
   template <int ROWS, int NT>
   static __device__ __forceinline__ void load(T* s, const T* g, int64_t row_stride, int64_t row0,
-                                              int64_t nrows, int tid) {
+                                              int64_t nrows, int tid, int L = 1, int Ls = 1) {
     constexpr int CH = D / 8;
     for (int i = tid; i < ROWS * CH; i += NT) {
       const int r = i / CH, c = i % CH;
       T* dst = s + r * LD + c * 8;
       const int64_t row = row0 + r;
       if (row >= 0 && row < nrows) {
-        cp_async16(smem_u32(dst), g + row * row_stride + c * 8);
+        const int64_t mrow = (L == Ls) ? row : (row / L) * Ls + (row % L);
+        cp_async16(smem_u32(dst), g + mrow * row_stride + c * 8);
       } else {
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
@@ -140,8 +143,8 @@ __global__ void __launch_bounds__(128) fwd_kernel(const __grid_constant__ Params
     } else {
       const int64_t c0 = walk.dep_c0 + (int64_t)(i - walk.n_seq_tiles) * BN;
       const int64_t n = (int64_t)p.T_kv * p.L;
-      TL::template load<BN, NT>(sK + st * BN * LD, gkd, p.kd.st, c0, n, tid);
-      TL::template load<BN, NT>(sV + st * BN * LD, gvd, p.vd.st, c0, n, tid);
+      TL::template load<BN, NT>(sK + st * BN * LD, gkd, p.kd.st, c0, n, tid, p.L, p.Ls);
+      TL::template load<BN, NT>(sV + st * BN * LD, gvd, p.vd.st, c0, n, tid, p.L, p.Ls);
     }
   };
 
@@ -360,8 +363,8 @@ __global__ void __launch_bounds__(128) dq_kernel(const __grid_constant__ Params 
     } else {
       const int64_t c0 = walk.dep_c0 + (int64_t)(i - walk.n_seq_tiles) * BN;
       const int64_t n = (int64_t)p.T_kv * p.L;
-      TL::template load<BN, NT>(sK + st * BN * LD, gkd, p.kd.st, c0, n, tid);
-      TL::template load<BN, NT>(sV + st * BN * LD, gvd, p.vd.st, c0, n, tid);
+      TL::template load<BN, NT>(sK + st * BN * LD, gkd, p.kd.st, c0, n, tid, p.L, p.Ls);
+      TL::template load<BN, NT>(sV + st * BN * LD, gvd, p.vd.st, c0, n, tid, p.L, p.Ls);
     }
   };
 
@@ -562,8 +565,9 @@ __global__ void __launch_bounds__(128) dkv_kernel(const __grid_constant__ Params
     }
   };
 
-  TL::template load<BN, NT>(sK, gk, kv_k.st, c0, n_keys, tid);
-  TL::template load<BN, NT>(sV, gv, kv_v.st, c0, n_keys, tid);
+  const int grpL = is_dep ? p.L : 1, grpLs = is_dep ? p.Ls : 1;   // memory layout of the key rows
+  TL::template load<BN, NT>(sK, gk, kv_k.st, c0, n_keys, tid, grpL, grpLs);
+  TL::template load<BN, NT>(sV, gv, kv_v.st, c0, n_keys, tid, grpL, grpLs);
   if (n_steps > 0) issue(0);
   cp_async_commit();
 
@@ -672,18 +676,26 @@ __global__ void __launch_bounds__(128) dkv_kernel(const __grid_constant__ Params
   const View& ov = is_dep ? p.dvd : p.dv;
   T* gdk = reinterpret_cast<T*>(ok.ptr) + ok.off(b, 0, h);
   T* gdv = reinterpret_cast<T*>(ov.ptr) + ov.off(b, 0, h);
+  const bool acc = is_dep && p.acc_depth != 0;   // depth gradients added to a cache shared by several layers
+  auto store2 = [&](T* dst, float a, float b2) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(dst);
+    if (acc) { const float2 old = Pack<T>::unpack(*w); a += old.x; b2 += old.y; }
+    *w = Pack<T>::pack(a, b2);
+  };
   if (keyA < n_keys) {
+    const int64_t rowA = is_dep ? dep_mem_row(p, keyA) : keyA;
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
-      *reinterpret_cast<uint32_t*>(gdk + (int64_t)keyA * ok.st + i * 8 + tq * 2) = Pack<T>::pack(dk[i][0] * p.scale, dk[i][1] * p.scale);
-      *reinterpret_cast<uint32_t*>(gdv + (int64_t)keyA * ov.st + i * 8 + tq * 2) = Pack<T>::pack(dv[i][0], dv[i][1]);
+      store2(gdk + rowA * ok.st + i * 8 + tq * 2, dk[i][0] * p.scale, dk[i][1] * p.scale);
+      store2(gdv + rowA * ov.st + i * 8 + tq * 2, dv[i][0], dv[i][1]);
     }
   }
   if (keyB < n_keys) {
+    const int64_t rowB = is_dep ? dep_mem_row(p, keyB) : keyB;
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) {
-      *reinterpret_cast<uint32_t*>(gdk + (int64_t)keyB * ok.st + i * 8 + tq * 2) = Pack<T>::pack(dk[i][2] * p.scale, dk[i][3] * p.scale);
-      *reinterpret_cast<uint32_t*>(gdv + (int64_t)keyB * ov.st + i * 8 + tq * 2) = Pack<T>::pack(dv[i][2], dv[i][3]);
+      store2(gdk + rowB * ok.st + i * 8 + tq * 2, dk[i][2] * p.scale, dk[i][3] * p.scale);
+      store2(gdv + rowB * ov.st + i * 8 + tq * 2, dv[i][2], dv[i][3]);
     }
   }
 }

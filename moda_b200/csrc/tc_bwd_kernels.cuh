@@ -53,6 +53,10 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                :: "l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+               :: "l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -174,6 +178,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     n_dep = (hi2 - lo + kStep - 1) / kStep;
   }
   const int n = n_seq + n_dep;
+  const int dep5 = (p.Ls != p.L) ? p.L : 0;      // in-place layer cache: 5-D depth maps
 
   if (tid == 0) {
     mbar_init(bars + 8 * B_.res, 256);
@@ -215,8 +220,13 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         if (elect_one()) {
           mbar_expect_tx(bar, 2 * kStepTile);
-          tma_load_tile<D>(dst, mk, bar, kStepHalf, h, row, b);
-          tma_load_tile<D>(dst + kStepTile, mv, bar, kStepHalf, h, row, b);
+          if (dep) {
+            tma_load_dep_tile<D>(dst, mk, bar, kStepHalf, h, row, b, dep5);
+            tma_load_dep_tile<D>(dst + kStepTile, mv, bar, kStepHalf, h, row, b, dep5);
+          } else {
+            tma_load_tile<D>(dst, mk, bar, kStepHalf, h, row, b);
+            tma_load_tile<D>(dst + kStepTile, mv, bar, kStepHalf, h, row, b);
+          }
         }
         __syncwarp();
         issued = i + 1;
@@ -562,7 +572,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       uint32_t regs[D / 2];
       if (key < n_keys) {
         const View& src = (wg == 0) ? (is_dep ? p.kd : p.k) : (is_dep ? p.vd : p.v);
-        const uint4* g4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(src.ptr) + src.off(b, key, h));
+        const uint4* g4 = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(src.ptr) +
+                                                         src.off(b, is_dep ? dep_mem_row(p, key) : (int64_t)key, h));
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
           const uint4 v4 = g4[i];
@@ -657,7 +668,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     if (ok && n > 0) {
       tc_fence_after();
       const View& ov = (wg == 0) ? (is_dep ? p.dvd : p.dv) : (is_dep ? p.dkd : p.dk);
-      T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, key, h);
+      T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, is_dep ? dep_mem_row(p, key) : (int64_t)key, h);
+      const bool acc = is_dep && p.acc_depth != 0;   // depth gradients added to a cache shared by several layers
       const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;      // warpgroup 0 stores dV, warpgroup 1 dK
       const float mul = (wg == 0) ? 1.f : p.scale;
 #pragma unroll
@@ -673,7 +685,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
             v4.y = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 2]) * mul, __uint_as_float(ov32[i * 8 + 3]) * mul);
             v4.z = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 4]) * mul, __uint_as_float(ov32[i * 8 + 5]) * mul);
             v4.w = Pack<T>::pack(__uint_as_float(ov32[i * 8 + 6]) * mul, __uint_as_float(ov32[i * 8 + 7]) * mul);
-            *reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8) = v4;
+            uint4* dst = reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8);
+            *dst = acc ? pack8_blend<T>(ov32 + i * 8, mul, *dst, 1.f) : v4;
           }
         }
       }
@@ -769,6 +782,7 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
 
   const int n_xb = (p.T_q + kStep - 1) / kStep;
   const int total = n_xb * p.H * p.B;                   // 64-row blocks; this CTA takes blockIdx.x, + gridDim.x, ...
+  const int dep5 = (p.Ls != p.L) ? p.L : 0;             // in-place layer cache: 5-D depth maps
 
   if (tid == 0) {
     mbar_init(bars + 8 * kDgRes, 1);
@@ -817,8 +831,8 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
         const uint32_t dst = sKV + slot * 2 * kTile, bar = bars + 8 * (kDgFull0 + slot);
         if (elect_one()) {
           mbar_expect_tx(bar, 2 * kTile);
-          tma_load_tile<D>(dst, &maps.kd, bar, kHalfBytes, k.h, row, k.b);
-          tma_load_tile<D>(dst + kTile, &maps.vd, bar, kHalfBytes, k.h, row, k.b);
+          tma_load_dep_tile<D>(dst, &maps.kd, bar, kHalfBytes, k.h, row, k.b, dep5);
+          tma_load_dep_tile<D>(dst + kTile, &maps.vd, bar, kHalfBytes, k.h, row, k.b, dep5);
         }
         __syncwarp();
         issued = gi + 1;
@@ -978,7 +992,7 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
         const int key0 = k.k_lo + i * kBN + wq * 32;         // first key row of this warp
         const uint32_t tacc = (wg ? tmem_dK : tmem_dV) + lane_addr;
         const float f = wg ? p.scale : 1.f;
-        if (key0 + 32 <= k.k_hi) {                           // every row of the warp is this block's
+        if (key0 + 32 <= k.k_hi && !p.acc_depth) {           // every row of the warp is this block's
           if (lane == 0) bulk_wait_read_all();               // this warp's previous store has read its rows
           __syncwarp();
           // staging = the TMA box layout: two [128 rows x 128 B] halves per tensor, 16-byte chunk c of
@@ -1003,14 +1017,18 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
             const uint32_t src = sOut + wg * kTile + wq * 32 * 128;
             const CUtensorMap* om = wg ? &omaps.dkd : &omaps.dvd;
 #pragma unroll
-            for (int bx = 0; bx < D / 64; ++bx) tma_store_4d(om, src + bx * kHalfBytes, 64 * bx, k.h, key0, k.b);
+            for (int bx = 0; bx < D / 64; ++bx) {
+              if (dep5 == 0) tma_store_4d(om, src + bx * kHalfBytes, 64 * bx, k.h, key0, k.b);
+              else tma_store_5d(om, src + bx * kHalfBytes, 64 * bx, k.h, 0, key0 / dep5, k.b);
+            }
             bulk_commit();
           }
           __syncwarp();
         } else {
           const int key = key0 + lane;
           const bool valid = key < k.k_hi;
-          T* gout = wg ? reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(k.b, key, k.h) : reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(k.b, key, k.h);
+          const int64_t mrow = dep_mem_row(p, valid ? key : k.k_lo);
+          T* gout = wg ? reinterpret_cast<T*>(p.dkd.ptr) + p.dkd.off(k.b, mrow, k.h) : reinterpret_cast<T*>(p.dvd.ptr) + p.dvd.off(k.b, mrow, k.h);
 #pragma unroll
           for (int q4 = 0; q4 < D / 32; ++q4) {
             uint32_t ov[32];
@@ -1018,7 +1036,10 @@ depth_grad_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvM
             tmem_wait_ld();
             if (valid) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) *reinterpret_cast<uint4*>(gout + q4 * 32 + e * 8) = pack8_scaled<T>(ov + e * 8, f);
+              for (int e = 0; e < 4; ++e) {
+                uint4* dst = reinterpret_cast<uint4*>(gout + q4 * 32 + e * 8);
+                *dst = p.acc_depth ? pack8_blend<T>(ov + e * 8, f, *dst, 1.f) : pack8_scaled<T>(ov + e * 8, f);
+              }
             }
           }
           tc_fence_before();
@@ -1050,7 +1071,7 @@ inline bool depth_grad_applies(const Params& p, const moda_problem* pr) {
 inline int padded_rows(int T_q) { return (T_q + 63) / 64 * 64 + 64; }
 
 inline bool bwd_supported(const moda_problem* pr) {
-  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
+  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && depth_layout_supported(pr);
 }
 
 inline size_t bwd_extra_workspace_bytes(const moda_problem* pr) {
@@ -1130,14 +1151,14 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, int n_sm, c
             make_map_rows(&m.dkv.q, p.q, dt, p.B, p.T_q, p.H, D, 64) &&
             make_map_rows(&m.dkv.dout, p.dout, dt, p.B, p.T_q, p.H, D, 64);
   if (ok && dep) {
-    ok = make_map_rows(&m.dq.kd, p.kd, dt, p.B, TL, p.H, D, 64) && make_map_rows(&m.dq.vd, p.vd, dt, p.B, TL, p.H, D, 64) &&
-         make_map_rows(&m.dkv.kd, p.kd, dt, p.B, TL, p.H, D, 128) && make_map_rows(&m.dkv.vd, p.vd, dt, p.B, TL, p.H, D, 128);
+    ok = make_map_depth(&m.dq.kd, p.kd, dt, p, D, 64) && make_map_depth(&m.dq.vd, p.vd, dt, p, D, 64) &&
+         make_map_depth(&m.dkv.kd, p.kd, dt, p, D, 128) && make_map_depth(&m.dkv.vd, p.vd, dt, p, D, 128);
   } else if (ok) {
     m.dq.kd = m.dq.k; m.dq.vd = m.dq.v; m.dkv.kd = m.dkv.k; m.dkv.vd = m.dkv.v;
   }
   if (!ok) return MODA_ERR_UNSUPPORTED;
   const bool dg = depth_grad_applies(p, pr);
-  if (dg && !(make_map_rows(&m.out.dkd, p.dkd, dt, p.B, TL, p.H, D, 32) && make_map_rows(&m.out.dvd, p.dvd, dt, p.B, TL, p.H, D, 32)))
+  if (dg && !(make_map_depth(&m.out.dkd, p.dkd, dt, p, D, 32) && make_map_depth(&m.out.dvd, p.dvd, dt, p, D, 32)))
     return MODA_ERR_UNSUPPORTED;
   if ((int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B > 0x7fffffff || n_sm <= 0) return MODA_ERR_UNSUPPORTED;
 

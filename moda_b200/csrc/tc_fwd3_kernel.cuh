@@ -97,6 +97,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
   const int r0 = pq * 2 * kBM;
   const F3Plan pl = f3_plan(p, r0);
   const bool two = r0 + kBM < p.T_q;                // the second query tile exists
+  const int dep5 = (p.Ls != p.L) ? p.L : 0;         // in-place layer cache: 5-D depth maps
 
   if (tid == 0) {
     mbar_init(bars + 8 * B_::q, 1);
@@ -144,8 +145,13 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
         if (elect_one()) {
           mbar_expect_tx(bar, 2 * kTile);
-          tma_load_tile<D>(dst, mk, bar, kHalfBytes, h, row, b);
-          tma_load_tile<D>(dst + kTile, mv, bar, kHalfBytes, h, row, b);
+          if (dep) {
+            tma_load_dep_tile<D>(dst, mk, bar, kHalfBytes, h, row, b, dep5);
+            tma_load_dep_tile<D>(dst + kTile, mv, bar, kHalfBytes, h, row, b, dep5);
+          } else {
+            tma_load_tile<D>(dst, mk, bar, kHalfBytes, h, row, b);
+            tma_load_tile<D>(dst + kTile, mv, bar, kHalfBytes, h, row, b);
+          }
         }
         __syncwarp();
         issued = s + 1;

@@ -122,6 +122,11 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" :: "l"(map) : "memory");
 }
@@ -338,6 +343,20 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* m
   for (int bx = 0; bx < D / 64; ++bx) tma_load_4d(dst + bx * box_bytes, map, bar, 64 * bx, h, row, b);
 }
 
+// The same for a tile of depth K/V rows [row, row + rows).  L5 == 0: the packed layout, a 4-D map
+// like every other tensor.  L5 == L > 0: the depth tensor is an in-place layer cache
+// (Params::Ls > L), its map is 5-D (D, H, L, T, B) with a box of L layers x rows / L positions,
+// which lands in shared memory in the same row order (position-major, layer-minor) as the packed
+// tile; `row` is a multiple of L because depth windows start at position boundaries.
+template <int D>
+__device__ __forceinline__ void tma_load_dep_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, uint32_t box_bytes,
+                                                  int h, int row, int b, int L5) {
+  if (L5 == 0) { tma_load_tile<D>(dst, map, bar, box_bytes, h, row, b); return; }
+  const int pos = row / L5;
+#pragma unroll
+  for (int bx = 0; bx < D / 64; ++bx) tma_load_5d(dst + bx * box_bytes, map, bar, 64 * bx, h, 0, pos, b);
+}
+
 // ======================================================================= forward
 // grid (ceil(T_q/128), H, B); 192 threads (4 softmax warps, MMA warp, TMA warp); two CTAs per SM.
 template <typename T, int D>
@@ -365,6 +384,7 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
   const int r0 = qt * kBM;
   const Walk walk = make_walk(p, r0);
   const int n_tiles = walk.n_seq + walk.n_dep;
+  const int dep5 = (p.Ls != p.L) ? p.L : 0;      // in-place layer cache: 5-D depth maps
 
   if (tid == 0) {
     mbar_init(bars + 8 * kBarQ, 1);
@@ -406,7 +426,8 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
         const uint32_t bar = bars + 8 * (is_k ? kBarK : kBarV);
         if (elect_one()) {
           mbar_expect_tx(bar, kTile);
-          tma_load_tile<D>(dst, m, bar, kHalfBytes, h, row, b);
+          if (dep) tma_load_dep_tile<D>(dst, m, bar, kHalfBytes, h, row, b, dep5);
+          else tma_load_tile<D>(dst, m, bar, kHalfBytes, h, row, b);
         }
         __syncwarp();
         if (is_k) { pend_k = true; pend_k_par = i & 1; } else { pend_v = true; pend_v_par = i & 1; }
@@ -605,8 +626,35 @@ inline bool make_map_rows(CUtensorMap* m, const View& v, int dtype, int B, int64
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Depth K/V (or their gradients) of an in-place layer cache: rows (t, l), l < L, at memory row
+// t * Ls + l.  5-D map (D, H, L, T, B), box [64, 1, L, box_rows / L, 1]: a tile of box_rows
+// consecutive depth rows of the operator.  box_rows must be a multiple of L.
+inline bool make_map_dep5(CUtensorMap* m, const View& v, int dtype, int B, int T, int L, int Ls, int H, int D, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || v.ptr == nullptr || L <= 0 || box_rows % L != 0) return false;
+  if ((H > 1 && v.sh <= 0) || v.st <= 0 || (B > 1 && v.sb <= 0)) return false;
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[4] = {(cuuint64_t)((H > 1 ? v.sh : 8) * 2), (cuuint64_t)(v.st * 2), (cuuint64_t)(v.st * 2 * Ls),
+                           (cuuint64_t)((B > 1 ? v.sb : 8) * 2)};
+  cuuint32_t box[5] = {64, 1, (cuuint32_t)L, (cuuint32_t)(box_rows / L), 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  return fn(m, dtype == MODA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, v.ptr,
+            dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// Map of a depth tensor in whichever of the two layouts the problem uses.
+inline bool make_map_depth(CUtensorMap* m, const View& v, int dtype, const Params& p, int D, int box_rows) {
+  if (p.Ls == p.L) return make_map_rows(m, v, dtype, p.B, (int64_t)p.T_kv * p.L, p.H, D, box_rows);
+  return make_map_dep5(m, v, dtype, p.B, p.T_kv, p.L, p.Ls, p.H, D, box_rows);
+}
+
+// The tcgen05 kernels take a positive scale (the row maximum is taken before scaling) and, for an
+// in-place layer cache (depth_rows_per_pos > L), a layer count that divides the 32-row boxes.
+inline bool depth_layout_supported(const moda_problem* pr) {
+  return pr->L == 0 || pr->depth_rows_per_pos <= pr->L || (32 % pr->L) == 0;
+}
 inline bool fwd_supported(const moda_problem* pr) {
-  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f;
+  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && depth_layout_supported(pr);
 }
 
 // Clears the abort flag of the launch about to be enqueued (the sticky word is left alone).
@@ -619,14 +667,12 @@ inline cudaError_t clear_launch_status(cudaStream_t st) {
 
 inline bool make_fwd_maps(FwdMaps* maps, const Params& p, const moda_problem* pr) {
   memset(maps, 0, sizeof(*maps));
-  const int64_t TL = (int64_t)p.T_kv * p.L;
   const int D = pr->D;
   bool ok = make_map_rows(&maps->q, p.q, pr->dtype, p.B, p.T_q, p.H, D, 128) &&
             make_map_rows(&maps->k, p.k, pr->dtype, p.B, p.T_kv, p.H, D, 128) &&
             make_map_rows(&maps->v, p.v, pr->dtype, p.B, p.T_kv, p.H, D, 128);
   if (ok && p.L > 0) {
-    ok = make_map_rows(&maps->kd, p.kd, pr->dtype, p.B, TL, p.H, D, 128) &&
-         make_map_rows(&maps->vd, p.vd, pr->dtype, p.B, TL, p.H, D, 128);
+    ok = make_map_depth(&maps->kd, p.kd, pr->dtype, p, D, 128) && make_map_depth(&maps->vd, p.vd, pr->dtype, p, D, 128);
   } else if (ok) {
     maps->kd = maps->k; maps->vd = maps->v;   // never dereferenced (no depth tiles)
   }

@@ -73,14 +73,15 @@ def _ref(t: Optional[Tensor4]):
     return ctypes.byref(t) if t is not None else None
 
 
-def _problem(q, T_kv, L, G, mode, scale, chunk_rows) -> Problem:
+def _problem(q, T_kv, L, G, mode, scale, chunk_rows, depth_rows_per_pos=0, accumulate_depth_grads=0) -> Problem:
     if not q.is_cuda:
         raise RuntimeError("moda_b200 runs on CUDA tensors only (there is no CPU path)")
     if q.dtype not in _DTYPES:
         raise TypeError(f"moda_b200 supports bf16/fp16 inputs, got {q.dtype}")
     B, T_q, H, D = q.shape
     return Problem(B, T_kv, H, D, G, L, mode, chunk_rows, _DTYPES[q.dtype], _forced_path,
-                   float(scale), q.device.index if q.device.index is not None else torch.cuda.current_device())
+                   float(scale), q.device.index if q.device.index is not None else torch.cuda.current_device(),
+                   int(depth_rows_per_pos), int(accumulate_depth_grads))
 
 
 def _check_same(q, *others):
@@ -89,17 +90,20 @@ def _check_same(q, *others):
             assert x.dtype == q.dtype and x.device == q.device, "all tensors must share dtype and device"
 
 
-def _forward(q, k, v, cached_k, cached_v, scale, G, mode, chunk_rows=CHUNK_VISIBLE_QUERY_ROWS):
+def _forward(q, k, v, cached_k, cached_v, scale, G, mode, chunk_rows=CHUNK_VISIBLE_QUERY_ROWS,
+             cache_layers=None, cache_capacity=0):
+    """``cache_layers`` / ``cache_capacity``: cached_k / cached_v are an in-place layer cache
+    ``[B, T_kv*capacity, H, D]`` of which the first ``cache_layers`` layers are valid."""
     B, T_q, H, D = q.shape
     assert T_q % G == 0, "T_q must be divisible by moda_group_num"
     T_kv = T_q // G
     use_depth = cached_k is not None and cached_v is not None
-    L = cached_k.shape[1] // T_kv if use_depth else 0
+    L = (cached_k.shape[1] // T_kv if cache_layers is None else cache_layers) if use_depth else 0
     _check_same(q, k, v, cached_k, cached_v)
     q, k, v, cached_k, cached_v = [None if x is None else _usable(x) for x in (q, k, v, cached_k, cached_v)]
     if not use_depth:
         cached_k = cached_v = None
-    prob = _problem(q, T_kv, L, G, mode, scale, chunk_rows)
+    prob = _problem(q, T_kv, L, G, mode, scale, chunk_rows, cache_capacity)
     o = torch.empty(B, T_q, H, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(B, T_q, H, dtype=torch.float32, device=q.device)
     lib = _cabi.load()
@@ -113,11 +117,14 @@ def _forward(q, k, v, cached_k, cached_v, scale, G, mode, chunk_rows=CHUNK_VISIB
 
 
 def _backward(q, k, v, cached_k, cached_v, o, lse, do, scale, G, mode,
-              chunk_rows=CHUNK_VISIBLE_QUERY_ROWS):
+              chunk_rows=CHUNK_VISIBLE_QUERY_ROWS, cache_layers=None, cache_capacity=0, grad_cache=None):
+    """``cache_layers`` / ``cache_capacity`` as in ``_forward``; ``grad_cache = (gk, gv)``: gradient
+    caches of the same layout to which the depth gradients are ADDED (the returned depth gradients
+    are then those tensors)."""
     B, T_q, H, D = q.shape
     T_kv = T_q // G
     use_depth = cached_k is not None and cached_v is not None
-    L = cached_k.shape[1] // T_kv if use_depth else 0
+    L = (cached_k.shape[1] // T_kv if cache_layers is None else cache_layers) if use_depth else 0
     _check_same(q, k, v, cached_k, cached_v, o, do)
     q, k, v, cached_k, cached_v, o, do = [
         None if x is None else _usable(x) for x in (q, k, v, cached_k, cached_v, o, do)]
@@ -125,12 +132,17 @@ def _backward(q, k, v, cached_k, cached_v, o, lse, do, scale, G, mode,
         cached_k = cached_v = None
     lse = lse.contiguous()
     assert lse.dtype == torch.float32
-    prob = _problem(q, T_kv, L, G, mode, scale, chunk_rows)
+    prob = _problem(q, T_kv, L, G, mode, scale, chunk_rows, cache_capacity, 1 if grad_cache is not None else 0)
     dq = torch.empty_like(q, memory_format=torch.contiguous_format)
     dk = torch.empty_like(k, memory_format=torch.contiguous_format) if k is not None else None
     dv = torch.empty_like(v, memory_format=torch.contiguous_format) if v is not None else None
-    dkd = torch.empty_like(cached_k, memory_format=torch.contiguous_format) if use_depth else None
-    dvd = torch.empty_like(cached_v, memory_format=torch.contiguous_format) if use_depth else None
+    if grad_cache is not None:
+        dkd, dvd = grad_cache
+        assert use_depth and dkd.shape == cached_k.shape and dvd.shape == cached_v.shape
+        assert _usable(dkd) is dkd and _usable(dvd) is dvd
+    else:
+        dkd = torch.empty_like(cached_k, memory_format=torch.contiguous_format) if use_depth else None
+        dvd = torch.empty_like(cached_v, memory_format=torch.contiguous_format) if use_depth else None
     lib = _cabi.load()
     nbytes = ctypes.c_size_t(0)
     _cabi.check(lib.moda_b200_bwd_workspace_bytes(ctypes.byref(prob), ctypes.byref(nbytes)),

@@ -154,6 +154,35 @@ def test_fold_qkv_returns_views_of_the_projection_outputs(built_library):
     assert ops._usable(e) is not e
 
 
+def test_depth_cache_copy_accounting(built_library):
+    """Bytes of K/V copied per forward: once per layer in place, against the stack-and-make-contiguous
+    rebuild before every layer of the reference's caller (vision_tasks/deit/models.py:361-375)."""
+    import moda_b200 as M
+    c = M.DepthKVCache(2, 10, 11, 6, 64, torch.bfloat16, "cpu")
+    per_layer = 2 * 2 * 10 * 6 * 64 * 2
+    assert c.bytes_copied_per_forward(12) == 11 * per_layer
+    assert c.bytes_copied_by_rebuilding(12) == 2 * sum(range(12)) * per_layer
+
+
+def test_depth_cache_layout_fields_are_validated(lib):
+    r = ctypes.byref
+    assert lib.moda_b200_check_problem(r(_prob(L=2, depth_rows_per_pos=0))) == 0
+    assert lib.moda_b200_check_problem(r(_prob(L=2, depth_rows_per_pos=2))) == 0
+    assert lib.moda_b200_check_problem(r(_prob(L=2, depth_rows_per_pos=11))) == 0
+    assert lib.moda_b200_check_problem(r(_prob(L=3, depth_rows_per_pos=2))) == 2     # fewer rows than layers
+    assert lib.moda_b200_check_problem(r(_prob(L=2, depth_rows_per_pos=-1))) == 2
+    # the tcgen05 kernels read an in-place cache through 5-D maps only when L divides their 32-row boxes
+    assert lib.moda_b200_resolve_path(r(_prob(L=4, depth_rows_per_pos=11, G=2, T_kv=64)), 0) == 2
+    assert lib.moda_b200_resolve_path(r(_prob(L=3, depth_rows_per_pos=11, G=2, T_kv=64)), 0) == 1
+    assert lib.moda_b200_resolve_path(r(_prob(L=3, depth_rows_per_pos=11, G=2, T_kv=64, path=2)), 0) == -10
+    # depth_append: layer index and capacity are checked before anything is launched
+    from moda_b200._cabi import Tensor4
+    t4 = Tensor4(0x1000, 64 * 2 * 64 * 11, 2 * 64, 64)
+    assert lib.moda_b200_depth_append(r(_prob(depth_rows_per_pos=11)), r(t4), r(t4), r(t4), r(t4), 11, None) == 2
+    assert lib.moda_b200_depth_append(r(_prob(depth_rows_per_pos=0)), r(t4), r(t4), r(t4), r(t4), 0, None) == 2
+    assert lib.moda_b200_depth_append(r(_prob(depth_rows_per_pos=11)), None, r(t4), r(t4), r(t4), 0, None) == 1
+
+
 def test_product_package_does_not_import_the_oracle():
     pkg = os.path.join(ROOT, "moda_b200")
     for dirpath, _, files in os.walk(pkg):
