@@ -535,6 +535,64 @@ def time_workload(M, _cabi, name, device, steps, warmup, pk):
     return rec
 
 
+def time_depth_cache_stack(M, _cabi, device, n_layers=12, steps=5, warmup=3):
+    """A DeiT-S-shaped stack of non-causal MoDA layers (config 5's shape: B=256, T=197, H=6, D=64; layer
+    i attends to the K/V of the i layers before it), forward + backward, with the depth cache kept in
+    place (DepthKVCache) and with the cache rebuilt before every layer by stack + reshape + contiguous
+    as the reference's caller does (vision_tasks/deit/models.py:361-390).  Device time per pass."""
+    mode, B, T, H, G, D, _ = WORKLOADS["config5_deit_noncausal_T197"]
+    gen = torch.Generator(device=device).manual_seed(4)
+    mk = lambda: torch.randn(B, T, H, D, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16).requires_grad_(True)  # noqa: E731
+    layers = [(mk(), mk(), mk()) for _ in range(n_layers)]
+    w = torch.randn(B, T, H, D, generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    cache = M.DepthKVCache(B, T, n_layers - 1, H, D, torch.bfloat16, device)
+
+    def clear():
+        for lay in layers:
+            for x in lay:
+                x.grad = None
+
+    def in_place():
+        cache.reset()
+        outs = []
+        for i, (q, k, v) in enumerate(layers):
+            outs.append(cache.attend(q, k, v, moda_group_num=1, is_causal=False))
+            if i + 1 < n_layers:
+                cache.append(k, v)
+        torch.autograd.backward(outs, [w] * n_layers)
+        clear()
+
+    def rebuilt():
+        outs, kv = [], []
+        for q, k, v in layers:
+            ck = cv = None
+            if kv:
+                ck = torch.stack([x[0] for x in kv], dim=2).reshape(B, T * len(kv), H, D).contiguous()
+                cv = torch.stack([x[1] for x in kv], dim=2).reshape(B, T * len(kv), H, D).contiguous()
+            outs.append(M.parallel_moda(q, k, v, cached_k=ck, cached_v=cv, moda_group_num=1, is_causal=False, warn_shape=False))
+            kv.append((k, v))
+        torch.autograd.backward(outs, [w] * n_layers)
+        clear()
+
+    res = {}
+    for name, fn in (("in_place_cache", in_place), ("rebuilt_cache", rebuilt)):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        res[name + "_ms"] = a.elapsed_time(b) / steps
+    res.update({"workload": "deit_s_stack_12_layers", "layers": n_layers, "B": B, "T": T, "H": H, "D": D, "timed": "fwd+bwd of the 12 attention layers",
+                "kv_bytes_copied_in_place": cache.bytes_copied_per_forward(n_layers),
+                "kv_bytes_copied_rebuilding": cache.bytes_copied_by_rebuilding(n_layers),
+                "device_status": _cabi.device_status()})
+    return res
+
+
 # seeds of the benchmark configurations (N(0,1) inputs from seed 1..4 for configs 2..5)
 WORKLOAD_SEEDS = {"config2_causal_T4096": 1, "config3_fda_T8192": 2, "config4_chunk_visible_T65536": 3,
                   "config5_deit_noncausal_T197": 4}
@@ -872,6 +930,11 @@ def main():
                     other.append(time_workload(M, _cabi, name, device, steps=5, warmup=3, pk=pk))
                 except RuntimeError as exc:
                     other.append({"workload": name, "error": str(exc)[:300]})
+            try:
+                other.append(time_depth_cache_stack(M, _cabi, device))
+            except RuntimeError as exc:
+                other.append({"workload": "deit_s_stack_12_layers", "error": str(exc)[:300]})
+            torch.cuda.empty_cache()
         if not args.no_triton_baseline:
             torch.cuda.empty_cache()
             triton_ref = triton_baseline_in_child(args.triton_timeout)
