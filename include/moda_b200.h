@@ -71,7 +71,11 @@ typedef enum moda_path {
      128-row query tile per CTA (two CTAs per SM), or two query tiles per CTA (one CTA per SM).
      Both give bit-identical results; the values exist so that each can be tested on any shape. */
   MODA_PATH_TCGEN05_ONE_TILE = 3,
-  MODA_PATH_TCGEN05_TWO_TILES = 4
+  MODA_PATH_TCGEN05_TWO_TILES = 4,
+  /* As MODA_PATH_TCGEN05, with the backward run as a query-parallel dq kernel plus a key-parallel
+     dk/dv kernel (the reference's structure, seven executed matmuls) also where the default is the
+     fused key-stationary backward (D = 128, five matmuls, dq summed in fixed point). */
+  MODA_PATH_TCGEN05_TWO_KERNEL_BWD = 5
 } moda_path;
 
 typedef struct moda_tensor4 {

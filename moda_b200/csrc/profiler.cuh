@@ -10,12 +10,12 @@ namespace moda {
 namespace prof {
 
 enum KernelId : int {
-  kFwdSimt = 0, kDelta, kDqSimt, kDkvSimt, kFwdTc, kPreTc, kDqTc, kDkvTc, kFdaFwd, kFdaBwd, kDepthGradTc, kDepthAppend, kCount
+  kFwdSimt = 0, kDelta, kDqSimt, kDkvSimt, kFwdTc, kPreTc, kDqTc, kDkvTc, kFdaFwd, kFdaBwd, kDepthGradTc, kDepthAppend, kBwdFusedTc, kBwdBoundsTc, kCount
 };
 inline const char* kernel_name(int id) {
   static const char* const names[kCount] = {"simt_fwd", "delta", "simt_dq", "simt_dkv", "tc_fwd",
                                             "tc_bwd_pre", "tc_dq", "tc_dkv", "fda_fwd", "fda_bwd", "tc_depth_grad",
-                                            "depth_append"};
+                                            "depth_append", "tc_bwd_fused", "tc_bwd_bounds"};
   return (id >= 0 && id < kCount) ? names[id] : "unknown";
 }
 

@@ -67,7 +67,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // four rows per warp, 32 consecutive rows of one (b, h) per block iteration; each lane has two
 // 16-byte loads of o and two of dO in flight (one of each for D = 64).
 template <typename T, int D>
-__global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params p, float* delta_t, float* lse_t, int T_qp) {
+__global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params p, float* delta_t, float* lse_t, float* norm_t, int T_qp) {
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, sub = lane & 7, grp = lane >> 3;
   const uint32_t groups_per_bh = (uint32_t)T_qp / 32u;             // T_qp is a multiple of 64
   const int64_t n_groups = (int64_t)p.B * p.H * groups_per_bh;
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params
     const uint32_t bh = (uint32_t)(gidx / groups_per_bh);
     const int r = (int)((uint32_t)(gidx - (int64_t)bh * groups_per_bh) * 32u) + w * 4 + grp;
     const int b = (int)(bh / (uint32_t)p.H), h = (int)(bh % (uint32_t)p.H);
-    float s = 0.f, l = 0.f;
+    float s = 0.f, l = 0.f, n2 = 0.f;     // n2: |dO row|^2, for the fixed-point scale of the fused backward
     if (r < p.T_q) {
       const T* po = reinterpret_cast<const T*>(p.o.ptr) + p.o.off(b, r, h);
       const T* pd = reinterpret_cast<const T*>(p.dout.ptr) + p.dout.off(b, r, h);
@@ -93,9 +93,16 @@ __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params
         for (int j = 0; j < 4; ++j) {
           const float2 x = Pack<T>::unpack(av[j]), y = Pack<T>::unpack(dv[j]);
           s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+          n2 = fmaf(y.x, y.x, fmaf(y.y, y.y, n2));
         }
       }
       if (sub == 0) l = p.lse[((int64_t)b * p.T_q + r) * p.H + h];
+    }
+    if (norm_t != nullptr) {
+      n2 += __shfl_xor_sync(0xffffffffu, n2, 1);
+      n2 += __shfl_xor_sync(0xffffffffu, n2, 2);
+      n2 += __shfl_xor_sync(0xffffffffu, n2, 4);
+      if (sub == 0) norm_t[(int64_t)bh * T_qp + r] = sqrtf(n2);
     }
     s += __shfl_xor_sync(0xffffffffu, s, 1);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -137,7 +144,7 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 template <typename T, int D>
 __global__ void __launch_bounds__(kDqThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
-          const float* lse_t, int T_qp) {
+          const float* lse_t, int T_qp, const int* dq_acc, const float4* scale_blk) {
   constexpr int R = kDqRing;
   constexpr BwdBars B_(R);
   constexpr uint32_t kStepTile = step_tile<D>();
@@ -177,6 +184,11 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     dep_c0 = lo;
     n_dep = (hi2 - lo + kStep - 1) / kStep;
   }
+  // dq_acc != nullptr: the sequence keys' share of dQ is already in the fixed-point accumulator the
+  // fused key-stationary kernel filled (tc_bwd_fused_kernel.cuh); this kernel then walks the depth
+  // keys only and its epilogue adds the two shares.
+  const bool seq_in_acc = dq_acc != nullptr;
+  if (seq_in_acc) n_seq = 0;
   const int n = n_seq + n_dep;
   const int dep5 = (p.Ls != p.L) ? p.L : 0;      // in-place layer cache: 5-D depth maps
 
@@ -372,14 +384,32 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
-    if (ok && n > 0) {
+    if (ok && (n > 0 || seq_in_acc)) {
       tc_fence_after();
       T* gdq = reinterpret_cast<T*>(p.dq.ptr) + p.dq.off(b, r, h);
+      const int64_t bh = (int64_t)b * p.H + h;
+      const float inv = (seq_in_acc && r < p.T_q) ? scale_blk[bh * (T_qp / 64) + r / 64].y : 0.f;
+      const int4* acc4 = seq_in_acc ? reinterpret_cast<const int4*>(dq_acc + (bh * T_qp + (r < p.T_q ? r : 0)) * D) : nullptr;
 #pragma unroll
       for (int q4 = (D / 64) * wg; q4 < (D / 64) * (wg + 1); ++q4) {   // each warpgroup stores half of the row
         uint32_t ov[32];
-        tmem_ld32<0>(tmem_dQ + lane_addr + q4 * 32, ov);
-        tmem_wait_ld();
+        if (n > 0) {
+          tmem_ld32<0>(tmem_dQ + lane_addr + q4 * 32, ov);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (seq_in_acc && r < p.T_q) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int4 a = acc4[q4 * 8 + i];
+            ov[4 * i + 0] = __float_as_uint(fmaf((float)a.x, inv, __uint_as_float(ov[4 * i + 0])));
+            ov[4 * i + 1] = __float_as_uint(fmaf((float)a.y, inv, __uint_as_float(ov[4 * i + 1])));
+            ov[4 * i + 2] = __float_as_uint(fmaf((float)a.z, inv, __uint_as_float(ov[4 * i + 2])));
+            ov[4 * i + 3] = __float_as_uint(fmaf((float)a.w, inv, __uint_as_float(ov[4 * i + 3])));
+          }
+        }
         if (r < p.T_q) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -1065,113 +1095,6 @@ inline bool depth_grad_applies(const Params& p, const moda_problem* pr) {
   if (p.L <= 0 || (kStep % p.G) != 0) return false;
   if (pr->mode == MODA_CHUNK_VISIBLE && (kStep % pr->chunk_rows) != 0) return false;
   return true;
-}
-
-// ------------------------------------------------------------------ host side
-inline int padded_rows(int T_q) { return (T_q + 63) / 64 * 64 + 64; }
-
-inline bool bwd_supported(const moda_problem* pr) {
-  return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && depth_layout_supported(pr);
-}
-
-inline size_t bwd_extra_workspace_bytes(const moda_problem* pr) {
-  if (!bwd_supported(pr)) return 0;
-  const size_t n = (size_t)pr->B * pr->H * padded_rows(pr->T_kv * pr->G) * sizeof(float);
-  return 2 * ((n + 255) & ~(size_t)255);
-}
-
-struct BwdMaps { DqMaps dq; DkvMaps dkv; DgOutMaps out; };
-
-template <typename T, int D>
-inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, float* delta_t, float* lse_t, int T_qp, bool dg,
-                              int n_sm, cudaStream_t st, int* launches) {
-  cudaError_t e;
-  {
-    const int64_t groups = (int64_t)p.B * p.H * (T_qp / 32);
-    const int64_t cap = (int64_t)n_sm * 16;
-    const int blocks = (int)(groups < cap ? groups : cap);
-    prof::Scope ps(prof::kPreTc, st);
-    pre_kernel<T, D><<<blocks, 256, 0, st>>>(p, delta_t, lse_t, T_qp);
-  }
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  *launches += 1;
-  {
-    auto kern = dq_kernel<T, D>;
-    const size_t smem = kDqRing * 2 * (size_t)step_tile<D>() + 2 * (size_t)kScoreTile + kCtlBytes;
-    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    dim3 grid((p.T_q + kBM - 1) / kBM, p.H, p.B);
-    prof::Scope ps(prof::kDqTc, st);
-    kern<<<grid, kDqThreads, smem, st>>>(p, m.dq, delta_t, lse_t, T_qp);
-  }
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  *launches += 1;
-  {
-    auto kern = dkv_kernel<T, D>;
-    const size_t smem = kDkvRing * (2 * (size_t)step_tile<D>() + 512) + 2 * (size_t)kDkvPairBytes + kCtlBytes;
-    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    const int n_seq = (p.T_kv + kBN - 1) / kBN;
-    const int n_dep = dg ? 0 : (int)(((int64_t)p.T_kv * p.L + kBN - 1) / kBN);
-    dim3 grid(n_seq + n_dep, p.H, p.B);
-    prof::Scope ps(prof::kDkvTc, st);
-    kern<<<grid, kDkvThreads, smem, st>>>(p, m.dkv, delta_t, lse_t, T_qp, n_seq);
-  }
-  if ((e = cudaGetLastError()) != cudaSuccess) return e;
-  *launches += 1;
-  if (dg) {
-    auto kern = depth_grad_kernel<T, D>;
-    constexpr uint32_t smem = dg_smem<D>();
-    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
-    const int64_t n_blocks = (int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B;
-    dim3 grid((unsigned)(n_blocks < n_sm ? n_blocks : n_sm));
-    {
-      prof::Scope ps(prof::kDepthGradTc, st);
-      kern<<<grid, kDgThreads, smem, st>>>(p, m.dkv, m.out, delta_t, lse_t, T_qp);
-    }
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    *launches += 1;
-  }
-  return cudaSuccess;
-}
-
-inline int bwd(const Params& p, const moda_problem* pr, void* extra, int n_sm, cudaStream_t st, int* launches, int* cuda_err) {
-  const int T_qp = padded_rows(p.T_q);
-  const size_t n = (((size_t)p.B * p.H * T_qp * sizeof(float)) + 255) & ~(size_t)255;
-  float* delta_t = reinterpret_cast<float*>(extra);
-  float* lse_t = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(extra) + n);
-  const int64_t TL = (int64_t)p.T_kv * p.L;
-  const bool dep = p.L > 0;
-  const int D = pr->D, dt = pr->dtype;
-
-  BwdMaps m;
-  memset(&m, 0, sizeof(m));
-  bool ok = make_map_rows(&m.dq.k, p.k, dt, p.B, p.T_kv, p.H, D, 64) &&
-            make_map_rows(&m.dq.v, p.v, dt, p.B, p.T_kv, p.H, D, 64) &&
-            make_map_rows(&m.dkv.k, p.k, dt, p.B, p.T_kv, p.H, D, 128) &&
-            make_map_rows(&m.dkv.v, p.v, dt, p.B, p.T_kv, p.H, D, 128) &&
-            make_map_rows(&m.dkv.q, p.q, dt, p.B, p.T_q, p.H, D, 64) &&
-            make_map_rows(&m.dkv.dout, p.dout, dt, p.B, p.T_q, p.H, D, 64);
-  if (ok && dep) {
-    ok = make_map_depth(&m.dq.kd, p.kd, dt, p, D, 64) && make_map_depth(&m.dq.vd, p.vd, dt, p, D, 64) &&
-         make_map_depth(&m.dkv.kd, p.kd, dt, p, D, 128) && make_map_depth(&m.dkv.vd, p.vd, dt, p, D, 128);
-  } else if (ok) {
-    m.dq.kd = m.dq.k; m.dq.vd = m.dq.v; m.dkv.kd = m.dkv.k; m.dkv.vd = m.dkv.v;
-  }
-  if (!ok) return MODA_ERR_UNSUPPORTED;
-  const bool dg = depth_grad_applies(p, pr);
-  if (dg && !(make_map_depth(&m.out.dkd, p.dkd, dt, p, D, 32) && make_map_depth(&m.out.dvd, p.dvd, dt, p, D, 32)))
-    return MODA_ERR_UNSUPPORTED;
-  if ((int64_t)((p.T_q + kStep - 1) / kStep) * p.H * p.B > 0x7fffffff || n_sm <= 0) return MODA_ERR_UNSUPPORTED;
-
-  cudaError_t e = clear_launch_status(st);
-  if (e == cudaSuccess) {
-    const bool bf = dt == MODA_BF16;
-    if (D == 128) e = bf ? launch_bwd<__nv_bfloat16, 128>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches)
-                         : launch_bwd<__half, 128>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches);
-    else e = bf ? launch_bwd<__nv_bfloat16, 64>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches)
-                : launch_bwd<__half, 64>(p, m, delta_t, lse_t, T_qp, dg, n_sm, st, launches);
-  }
-  if (e != cudaSuccess) { *cuda_err = (int)e; return MODA_ERR_CUDA; }
-  return MODA_OK;
 }
 
 }  // namespace tc

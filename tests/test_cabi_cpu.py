@@ -49,7 +49,7 @@ def _prob(**kw):
     ({"B": 0}, 2), ({"T_kv": 0}, 2), ({"L": -1}, 2), ({"G": 0}, 2),
     ({"D": 96}, 3), ({"D": 256}, 3),
     ({"dtype": 2}, 4),
-    ({"mode": 7}, 6), ({"mode": 3, "L": 0}, 6), ({"path": 5}, 6),
+    ({"mode": 7}, 6), ({"mode": 3, "L": 0}, 6), ({"path": 6}, 6), ({"path": 5}, 0),
     ({"mode": 2, "chunk_rows": 0}, 7), ({"mode": 2, "chunk_rows": 64, "G": 3}, 7),
     ({"mode": 2, "chunk_rows": 64, "G": 4}, 0),
 ])

@@ -251,12 +251,44 @@ def test_tcgen05_path_refuses_what_it_cannot_run(M):
     (1, 1, 1, "bf16"), (64, 0, 1, "bf16"), (127, 2, 1, "fp16"), (129, 3, 2, "bf16"), (300, 5, 4, "bf16"),
     (1000, 3, 4, "fp16"), (513, 16, 8, "bf16"), (1536, 24, 4, "bf16"),
 ])
-@pytest.mark.parametrize("D", [64, 128])
-def test_tcgen05_forward_and_backward(M, mode, T, L, G, dt, D):
-    """tcgen05 forward + backward (statistics pass, dq, dk/dv and depth-gradient kernels), forced."""
+@pytest.mark.parametrize("D,bwd", [(64, "two_kernel"), (128, "fused"), (128, "two_kernel")])
+def test_tcgen05_forward_and_backward(M, mode, T, L, G, dt, D, bwd):
+    """tcgen05 forward + backward, forced: the fused key-stationary backward (D = 128: five matmuls,
+    dq summed in fixed point) and the two-kernel backward (dq kernel + dk/dv kernel), each with the
+    statistics pass and the depth-gradient kernel."""
     from moda_b200 import _cabi
-    _run_case(M, mode, 1, T, 2, D, L, G, DT[dt], None, seed=200 + T, path=M.PATH_TCGEN05, check_bwd=True)
+    path = M.PATH_TCGEN05 if bwd == "fused" or D == 64 else M.PATH_TCGEN05_TWO_KERNEL_BWD
+    _run_case(M, mode, 2 if T < 600 else 1, T, 2, D, L, G, DT[dt], None, seed=200 + T, path=path, check_bwd=True)
     assert _cabi.device_status() == 0
+
+
+@pytest.mark.parametrize("scale_dout", [1.0, 3.0e4, 1.0e-6])
+def test_fused_backward_fixed_point_scale_follows_the_gradient_magnitude(M, scale_dout):
+    """dq of the fused backward is summed as scaled integers; the scale comes from a bound on each
+    64-row block's |dQ|, so upstream gradients of any magnitude (loss scaling, vanishing gradients)
+    keep the same relative accuracy.  Rows of very different magnitude in one call included."""
+    dev = torch.device("cuda", 0)
+    B, T, H, D, L, G = 1, 700, 2, 128, 4, 2
+    q, k, v, kd, vd, dout = mo.make_inputs(321, B, T, H, D, L, G, dtype=torch.bfloat16)
+    dout = (dout.float() * scale_dout)
+    dout[:, : T * G // 2] *= 1.0e-3                      # half of the rows a thousand times smaller
+    dout = dout.to(torch.bfloat16)
+    ref = mo.moda_attention_ref_grads(q, k, v, kd, vd, dout, None, G, mo.MODE_CAUSAL, 1)
+    q, k, v, kd, vd, dout = [x.to(dev) for x in (q, k, v, kd, vd, dout)]
+    old = M.set_kernel_path(M.PATH_TCGEN05)
+    try:
+        o, lse = M.parallel_moda_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=G)
+        g1 = M.parallel_moda_bwd(q, k, v, o, None, lse, dout, cached_k=kd, cached_v=vd, moda_group_num=G)
+        g2 = M.parallel_moda_bwd(q, k, v, o, None, lse, dout, cached_k=kd, cached_v=vd, moda_group_num=G)
+    finally:
+        M.set_kernel_path(old)
+    for a, b in zip(g1, g2):
+        assert (a is None and b is None) or torch.equal(a, b)          # integer sums: order cannot matter
+    dq = g1[0].float().cpu()
+    half = T * G // 2
+    for name, got, want in (("dq small rows", dq[:, :half], ref[2][:, :half]), ("dq large rows", dq[:, half:], ref[2][:, half:])):
+        e = ((got - want).pow(2).sum().sqrt() / want.pow(2).sum().sqrt()).item()
+        assert e <= 5e-2, f"{name}: rel-L2 {e}"
 
 
 def test_tcgen05_backward_bitwise_reproducible_and_batched(M):
@@ -395,7 +427,7 @@ def _random_cases(seed, n):
         T = min(T, max(1, 4200 // G))
         L = rng.choice([0, 1, 2, 3, 5, 8, 11, 16, 24, 32, 33])
         cases.append((mode, rng.choice([1, 2]), T, rng.choice([1, 2, 3]), L, G, rng.choice(["bf16", "fp16"]),
-                      rng.choice([64, 128]), rng.choice(["auto", "tcgen05", "one_tile", "two_tiles"]),
+                      rng.choice([64, 128]), rng.choice(["auto", "tcgen05", "one_tile", "two_tiles", "two_kernel_bwd"]),
                       rng.randrange(1 << 30)))
     return cases
 
@@ -406,6 +438,6 @@ def test_randomised_shapes(M, mode, B, T, H, L, G, dt, D, path, seed):
     dim and kernel path (auto / tcgen05 / each forward forced); forward and backward."""
     from moda_b200 import _cabi
     paths = {"auto": None, "tcgen05": M.PATH_TCGEN05, "one_tile": M.PATH_TCGEN05_ONE_TILE,
-             "two_tiles": M.PATH_TCGEN05_TWO_TILES}
+             "two_tiles": M.PATH_TCGEN05_TWO_TILES, "two_kernel_bwd": M.PATH_TCGEN05_TWO_KERNEL_BWD}
     _run_case(M, mode, B, T, H, D, L, G, DT[dt], None, seed=seed, path=paths[path])
     assert _cabi.device_status() == 0
