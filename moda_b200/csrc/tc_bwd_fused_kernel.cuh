@@ -11,8 +11,8 @@
 // tiles to one query row have to be summed in global memory.  Floating-point atomics would make the
 // result depend on the order in which CTAs happen to run; instead the partial sums are FIXED-POINT:
 // every 64-row query block has a power-of-two scale 2^e chosen from a bound on its rows' |dQ| so
-// that the scaled values fit 30 bits, each contribution is rounded to int32 once and added with
-// red.global.add.s32.  Integer addition is associative, so the accumulated value - and with it dq -
+// that the scaled values fit 30 bits, each contribution is rounded to int32 once and added with an
+// integer bulk reduction (cp.reduce.async.bulk ... add.s32).  Integer addition is associative, so the accumulated value - and with it dq -
 // is bit-identical from run to run whatever the order.  The quantisation step is 2^-29 of the
 // bound, far below the 16-bit rounding of dq.  A later pass (dq_kernel walking only the depth keys)
 // adds the depth keys' share in fp32 and writes dq.
@@ -40,7 +40,7 @@ constexpr int kFuRing = 3;                                  // ring of {Q, dO, l
 constexpr uint32_t kFuStat = 768;                           // 64 lse, 64 delta, one float4 {scale, 1/scale, -, -}
 struct FuBars {   // barrier indices
   static constexpr int res = 0, kfull = 1, full0 = 2, empty0 = 2 + kFuRing, s0 = 2 + 2 * kFuRing, p0 = s0 + 2,
-                       r0 = p0 + 2, t0 = r0 + 2, done = t0 + 2, qfree = done + 1, count = qfree + 1;
+                       r0 = p0 + 2, t0 = r0 + 2, done = t0 + 2, qfree = done + 1, ws0 = qfree + 1, count = ws0 + 2;
 };
 static_assert(FuBars::count <= kMaxBars, "control block too small");
 constexpr uint32_t kFuSmem = kTileBytes + kFuRing * 2 * step_tile<128>() + 2 * kDkvPairBytes + kFuRing * kFuStat + kCtlBytes;
@@ -49,10 +49,6 @@ constexpr uint32_t kFuSmem = kTileBytes + kFuRing * 2 * step_tile<128>() + 2 * k
 __host__ __device__ constexpr uint32_t instr_desc_ab(uint32_t fmt, uint32_t n, bool a_mn_major, bool b_mn_major) {
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((n >> 3) << 17) | ((128u >> 4) << 24);
-}
-
-__device__ __forceinline__ void red_add_s32(int* addr, int v) {
-  asm volatile("red.global.add.s32 [%0], %1;" :: "l"(addr), "r"(v) : "memory");
 }
 
 // ------------------------------------------------------------------ bounds for the fixed-point scale
@@ -182,6 +178,7 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + 8 * (B_::s0 + i), 1); mbar_init(bars + 8 * (B_::p0 + i), 128);
       mbar_init(bars + 8 * (B_::r0 + i), 128); mbar_init(bars + 8 * (B_::t0 + i), 1);
+      mbar_init(bars + 8 * (B_::ws0 + i), 128);
     }
     *abort_flag = 0;
     *drain_flag = 0;
@@ -338,8 +335,21 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
     const float c = p.scale_log2;
     bool ok = true;
     float esc_prev = 0.f;     // fixed-point scale of this warpgroup's previous step
+    uint32_t wphase = 0;      // phase of this warpgroup's own barrier
+    // All 128 threads of the warpgroup meet (a bounded mbarrier wait, like every other wait here: a
+    // named bar.sync would spin forever if one warp of the group had left through the abort path).
+    auto wg_sync = [&]() -> bool {
+      mbar_arrive(bars + 8 * (B_::ws0 + wg));
+      const bool r = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_::ws0 + wg), wphase & 1, abort_flag, B_::ws0 + wg));
+      ++wphase;
+      return r;
+    };
 
-    // dQ^T of step j (this warpgroup's previous step): out of TMEM, scaled, rounded, added
+    // dQ^T of step j (this warpgroup's previous step): out of TMEM, scaled and rounded to int32,
+    // transposed into [64 query rows][128] in shared memory - the warpgroup's own P^T / dS^T tile
+    // pair, which update(j) has finished reading and which is exactly 32 KB - and added to the
+    // accumulator rows with ONE bulk reduction (an L2-side integer add of 32 KB; per-thread
+    // red.global instructions for the same words were 18 ms slower per backward of 65536 positions).
     auto dq_out = [&](int j, float esc) -> bool {
       if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_::t0 + (j & 1)), (j >> 1) & 1, abort_flag, B_::t0 + (j & 1)))) return false;
       tc_fence_after();
@@ -349,10 +359,23 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bars + 8 * B_::qfree);
-      int* dst = dq_acc + (stat_base + q_begin + (int64_t)j * kStep) * D + row;
+      int* stage = reinterpret_cast<int*>(smem_raw + pt_off + (j & 1) * kDkvPairBytes);
 #pragma unroll
-      for (int q = 0; q < 64; ++q) red_add_s32(dst + q * D, __float2int_rn(__uint_as_float(qv[q]) * esc));
+      for (int q = 0; q < 64; ++q) stage[q * D + row] = __float2int_rn(__uint_as_float(qv[q]) * esc);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (!wg_sync()) return false;
+      if (quarter == 0 && lane == 0) {
+        int* dst = dq_acc + (stat_base + q_begin + (int64_t)j * kStep) * D;
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.s32 [%0], [%1], %2;"
+                     :: "l"(dst), "r"(sPT + (uint32_t)(j & 1) * kDkvPairBytes), "r"(kDkvPairBytes) : "memory");
+        bulk_commit();
+      }
       return true;
+    };
+    // the bulk reduction issued by dq_out must have read the tile pair before it is written again
+    auto pair_free = [&]() -> bool {
+      if (quarter == 0 && lane == 0) bulk_wait_read_all();
+      return wg_sync();
     };
 
     for (int i = wg; i < n; i += 2) {
@@ -401,7 +424,9 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
         pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
         pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
       }
-      // (the update of step i - 2 has finished reading this warpgroup's tile pair: dq_out waited for it)
+      // the update of step i - 2 has finished reading this warpgroup's tile pair (dq_out waited for
+      // it), and so has the reduction of dQ^T(i - 2) that was staged in it
+      if (!(ok = pair_free())) break;
       {   // rows of the K-major, 128B-swizzled [128 x 64] tiles: 16-byte chunk c lives at chunk c ^ (row & 7)
         unsigned char* prow = smem_raw + pt_off + (i & 1) * kDkvPairBytes + row * 128;
 #pragma unroll
@@ -419,6 +444,7 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
       const int j_last = ((n - 1 - wg) / 2) * 2 + wg;
       ok = dq_out(j_last, esc_prev);
     }
+    if (quarter == 0 && lane == 0) bulk_wait_read_all();     // staged rows are read before the CTA's smem goes
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_::done, 0, abort_flag, B_::done));
     if (ok && n > 0) {
       tc_fence_after();
