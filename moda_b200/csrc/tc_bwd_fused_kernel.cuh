@@ -23,6 +23,16 @@
 // with the maxima over the sequence keys of the (batch, head), times a safety factor for the
 // rounding of P and dS to 16 bits.
 //
+// Work decomposition.  A CTA is one (query segment, key tile) pair: segments of kFuSegRows query
+// rows, CTAs ordered segment-major, so that the CTAs resident at any time add their dQ contributions
+// to the same few megabytes of the accumulator (which then live in L2: with one CTA per key tile
+// walking all of its query rows the resident CTAs were spread over the whole sequence and the
+// reductions ran at DRAM speed) and read the same Q / dO rows.  dK and dV of a key tile are then the
+// sum over its segments: the CTAs of one key tile add their fp32 partial sums into a per-tile
+// buffer strictly in segment order - CTA (s, j) waits (bounded) on a counter for CTA (s - 1, j),
+// which has a lower block index and was therefore scheduled earlier - and the last segment writes
+// dk / dv.  A fixed order of fp32 additions, like a fixed-point sum, does not depend on timing.
+//
 // Warp roles as in dkv_kernel (TMA warp, score-MMA warp, update-MMA warp, two softmax warpgroups on
 // alternate steps).  TMEM (512 columns): [0,64) S^T, [64,128) dP^T (one fp32 score stage),
 // [128,256) dV, [256,384) dK, [384,448) V rows as the 16-bit A operand of dP^T, [448,512) dQ^T
@@ -36,6 +46,7 @@
 namespace moda {
 namespace tc {
 
+constexpr int kFuSegRows = 8192;                            // query rows per segment (128 steps)
 constexpr int kFuRing = 3;                                  // ring of {Q, dO, lse, delta, scale} step slots
 constexpr uint32_t kFuStat = 768;                           // 64 lse, 64 delta, one float4 {scale, 1/scale, -, -}
 struct FuBars {   // barrier indices
@@ -126,12 +137,40 @@ __global__ void __launch_bounds__(256) scale_kernel(const float* delta_t, const 
   }
 }
 
+// Key tiles that see at least one row of query segment s.
+__host__ __device__ __forceinline__ int fu_tiles_in_segment(const Params& p, int s, int n_tiles) {
+  if (p.mode == kNonCausal) return n_tiles;
+  const int64_t last_row = min((int64_t)(s + 1) * kFuSegRows, (int64_t)p.T_q) - 1;     // last valid row of the segment
+  const int64_t last_key = last_row / p.G;                                             // its last visible key
+  return (int)min((int64_t)n_tiles, last_key / kBN + 1);
+}
+inline int64_t fu_grid_size(const Params& p) {
+  const int n_tiles = (p.T_kv + kBN - 1) / kBN, n_seg = (p.T_q + kFuSegRows - 1) / kFuSegRows;
+  int64_t n = 0;
+  for (int s = 0; s < n_seg; ++s) n += fu_tiles_in_segment(p, s, n_tiles);
+  return n;
+}
+
+// Bounded wait on a global counter written by other CTAs (release/acquire through the counter).
+__device__ __forceinline__ bool wait_counter(const int* ctr, int want, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= want) return true;
+    if (*abort_flag != 0) return false;
+    __nanosleep(64);
+  }
+  *abort_flag = 1;
+  record_failure(3 << 8);
+  return false;
+}
+
 // =========================================================================== fused backward
-// grid (ceil(T_kv/128), H, B), 352 threads.
+// grid (sum over segments of the key tiles that see them, H, B), 352 threads.
 template <typename T>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
-                 const float* lse_t, const float4* scale_blk, int* dq_acc, int T_qp) {
+                 const float* lse_t, const float4* scale_blk, int* dq_acc, float* dkv_part, int* tile_ctr, int T_qp) {
   constexpr int D = 128;
   constexpr int R = kFuRing;
   using B_ = FuBars;
@@ -160,14 +199,26 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
 
   const int h = blockIdx.y, b = blockIdx.z;
-  const int c0 = (int)blockIdx.x * kBN;        // key tile 0 is seen by every query row: heaviest tiles first
   const int n_keys = p.T_kv;
+  const int n_tiles = (n_keys + kBN - 1) / kBN;
+  const int n_seg = (p.T_q + kFuSegRows - 1) / kFuSegRows;
+  int seg = 0, tile = (int)blockIdx.x;         // block index -> (segment, key tile), segment-major
+  for (; seg < n_seg; ++seg) {
+    const int ns = fu_tiles_in_segment(p, seg, n_tiles);
+    if (tile < ns) break;
+    tile -= ns;
+  }
+  if (seg >= n_seg) return;
+  const int c0 = tile * kBN;
   const int c_last = min(c0 + kBN, n_keys) - 1;
 
-  // query rows that can see a key of this tile: [q_begin, T_q), walked in steps of 64
-  int q_begin = (p.mode == kNonCausal) ? 0 : c0 * p.G;
-  q_begin = (q_begin / kStep) * kStep;
-  const int n = (p.T_q - q_begin + kStep - 1) / kStep;
+  // query rows of this segment that can see a key of this tile: [q_begin, q_end), in steps of 64
+  int q_tile = (p.mode == kNonCausal) ? 0 : c0 * p.G;          // first row that sees the tile
+  q_tile = (q_tile / kStep) * kStep;
+  const int seg_first = q_tile / kFuSegRows;                    // first segment of this key tile
+  const int q_begin = max(q_tile, seg * kFuSegRows);
+  const int q_end = min((seg + 1) * kFuSegRows, (p.T_q + kStep - 1) / kStep * kStep);
+  const int n = (q_end - q_begin) / kStep;
 
   if (tid == 0) {
     mbar_init(bars + 8 * B_::res, 128);
@@ -448,18 +499,47 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_::done, 0, abort_flag, B_::done));
     if (ok && n > 0) {
       tc_fence_after();
-      const View& ov = (wg == 0) ? p.dv : p.dk;
-      T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, key, h);
-      const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;      // warpgroup 0 stores dV, warpgroup 1 dK
-      const float mul = (wg == 0) ? 1.f : p.scale;
+      // dV (warpgroup 0) / dK (warpgroup 1) of this segment, added to the partial sums of the earlier
+      // segments of the key tile in segment order; the last segment writes the 16-bit result.
+      const int64_t tile_id = ((int64_t)b * p.H + h) * n_tiles + tile;
+      int* ctr = tile_ctr + tile_id;
+      const bool first = seg == seg_first, last = seg == n_seg - 1;
+      if (!first) ok = __all_sync(0xffffffffu, wait_counter(ctr, 256 * (seg - seg_first), abort_flag));
+      if (ok) {
+        const View& ov = (wg == 0) ? p.dv : p.dk;
+        T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, key, h);
+        float* part = dkv_part + ((tile_id * 2 + wg) * kBN + row) * D;      // this key row's fp32 partial sums
+        const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;
+        const float mul = (wg == 0) ? 1.f : p.scale;
 #pragma unroll
-      for (int q4 = 0; q4 < D / 32; ++q4) {
-        uint32_t ov32[32];
-        tmem_ld32<0>(tsrc + lane_addr + q4 * 32, ov32);
-        tmem_wait_ld();
-        if (key < n_keys) {
+        for (int q4 = 0; q4 < D / 32; ++q4) {
+          uint32_t ov32[32];
+          tmem_ld32<0>(tsrc + lane_addr + q4 * 32, ov32);
+          tmem_wait_ld();
+          if (!first) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8) = pack8_scaled<T>(ov32 + i * 8, mul);
+            for (int i = 0; i < 8; ++i) {
+              const float4 a = *reinterpret_cast<const float4*>(part + q4 * 32 + 4 * i);
+              ov32[4 * i + 0] = __float_as_uint(__uint_as_float(ov32[4 * i + 0]) + a.x);
+              ov32[4 * i + 1] = __float_as_uint(__uint_as_float(ov32[4 * i + 1]) + a.y);
+              ov32[4 * i + 2] = __float_as_uint(__uint_as_float(ov32[4 * i + 2]) + a.z);
+              ov32[4 * i + 3] = __float_as_uint(__uint_as_float(ov32[4 * i + 3]) + a.w);
+            }
+          }
+          if (last) {
+            if (key < n_keys) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8) = pack8_scaled<T>(ov32 + i * 8, mul);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<uint4*>(part + q4 * 32 + 4 * i) = make_uint4(ov32[4 * i], ov32[4 * i + 1], ov32[4 * i + 2], ov32[4 * i + 3]);
+          }
+        }
+        if (!last) {       // publish: this thread's partial sums are visible before its count is
+          __threadfence();
+          atomicAdd(ctr, 1);
         }
       }
     }
