@@ -84,8 +84,8 @@ NCU_TRAFFIC_SOURCE = {"tc_fwd": "scaled from the T=8192 ncu capture", "tc_dq": "
 # dk/dv kernel dK and dV; the scores both backward kernels recompute (S, dP) are owned by neither,
 # so the per-kernel figures of a two-kernel backward do not add up to the step's - the whole-step
 # figure in roofline.step is the one that counts every algorithmic FLOP exactly once.
-OWNED_MATMULS = {"simt_fwd": 2, "tc_fwd": 2, "simt_dq": 1, "tc_dq": 1, "simt_dkv": 2, "tc_dkv": 2}
-EXECUTED_MATMULS = {"simt_fwd": 2, "tc_fwd": 2, "simt_dq": 3, "tc_dq": 3, "simt_dkv": 4, "tc_dkv": 4}
+OWNED_MATMULS = {"simt_fwd": 2, "tc_fwd": 2, "simt_dq": 1, "tc_dq": 1, "simt_dkv": 2, "tc_dkv": 2, "tc_bwd_fused": 5}
+EXECUTED_MATMULS = {"simt_fwd": 2, "tc_fwd": 2, "simt_dq": 3, "tc_dq": 3, "simt_dkv": 4, "tc_dkv": 4, "tc_bwd_fused": 5}
 
 
 def pairs(mode, B, T, Hkv, G, L):
@@ -606,7 +606,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton_baseline"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--only-workload", action="store_true", help="triton_baseline: time --workload only, also when it is the default one")
-    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05"])
+    ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05", "fused_bwd"])
     ap.add_argument("--cpu-sample-T", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -645,7 +645,8 @@ def main():
     import moda_b200 as M
     from moda_b200 import _cabi
     from moda_b200.sharding import gather_units, partition_units
-    M.set_kernel_path({"auto": M.PATH_AUTO, "simt": M.PATH_SIMT_MMA, "tcgen05": M.PATH_TCGEN05}[args.path])
+    M.set_kernel_path({"auto": M.PATH_AUTO, "simt": M.PATH_SIMT_MMA, "tcgen05": M.PATH_TCGEN05,
+                       "fused_bwd": M.PATH_TCGEN05_FUSED_BWD}[args.path])
 
     n_units = B * Hkv
     units = partition_units(n_units, world, rank)
@@ -828,6 +829,31 @@ def main():
         depth_overhead["forward_only"] = block("fwd")
         depth_overhead["note"] = "same kernels, same q/k/v/dO, L = 0; (t_full - t_seq_only) / t_full; three alternations"
 
+    # ---- the alternative backward (one fused five-matmul kernel), for the record -----------------
+    fused_variant = None
+    if rank == 0 and world == 1 and D == 128 and mode != "fda" and not args.fwd_only and args.path == "auto":
+        old_path = M.set_kernel_path(M.PATH_TCGEN05_FUSED_BWD)
+        try:
+            one_step()
+            torch.cuda.synchronize()
+            _cabi.profile_begin()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(args.steps):
+                one_step()
+            b_.record()
+            torch.cuda.synchronize()
+            pv = _cabi.profile_end()
+            fused_variant = {"path": "MODA_PATH_TCGEN05_FUSED_BWD", "ms_per_step": a_.elapsed_time(b_) / args.steps,
+                             "kernels_ms_per_launch": {k_: round(m_ / c_, 3) for k_, (c_, m_) in pv.items()},
+                             "device_status": _cabi.device_status(),
+                             "note": "same workload with the sequence keys' backward as one key-stationary kernel "
+                                     "(5 executed matmuls, dq summed in fixed point) instead of dq + dk/dv kernels (7)"}
+        except RuntimeError as exc:
+            fused_variant = {"error": str(exc)[:300]}
+        finally:
+            M.set_kernel_path(old_path)
+
     # ---- end-to-end through the public autograd operator with host buffers -------------
     e2e = None
     if not args.no_e2e and not args.fwd_only and len(units) > 0:
@@ -962,7 +988,7 @@ def main():
             "frac_of_measured_bf16_peak": value / (pk["tflops"] * world),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
             "clocks": clocks, "remeasured": remeasured, "depth_overhead": depth_overhead,
-            "device_status": dev_status,
+            "device_status": dev_status, "fused_backward_variant": fused_variant,
             "other_workloads": other, "reference_triton": triton_ref,
             "validation": {"per_unit_checksum_o_lse": [[round(float(a), 3), round(float(b), 3)] for a, b in cs_all.tolist()]},
         }

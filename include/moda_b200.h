@@ -72,10 +72,12 @@ typedef enum moda_path {
      Both give bit-identical results; the values exist so that each can be tested on any shape. */
   MODA_PATH_TCGEN05_ONE_TILE = 3,
   MODA_PATH_TCGEN05_TWO_TILES = 4,
-  /* As MODA_PATH_TCGEN05, with the backward run as a query-parallel dq kernel plus a key-parallel
-     dk/dv kernel (the reference's structure, seven executed matmuls) also where the default is the
-     fused key-stationary backward (D = 128, five matmuls, dq summed in fixed point). */
-  MODA_PATH_TCGEN05_TWO_KERNEL_BWD = 5
+  /* As MODA_PATH_TCGEN05, with the backward over the sequence keys run as ONE key-stationary kernel
+     that executes the five matmuls once each and sums dq in fixed point (D = 128 only; otherwise as
+     MODA_PATH_TCGEN05).  The default is a query-parallel dq kernel plus a key-parallel dk/dv kernel
+     (the reference's structure, seven executed matmuls), which measures no slower; the fused form
+     needs more workspace (moda_b200_bwd_workspace_bytes accounts for the path). */
+  MODA_PATH_TCGEN05_FUSED_BWD = 5
 } moda_path;
 
 typedef struct moda_tensor4 {

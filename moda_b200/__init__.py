@@ -22,7 +22,7 @@ from .ops import (  # noqa: F401
 from .depth_cache import DepthKVCache  # noqa: F401
 from ._cabi import (  # noqa: F401
     MODE_CAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY, MODE_NONCAUSAL,
-    PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05, PATH_TCGEN05_ONE_TILE, PATH_TCGEN05_TWO_TILES, PATH_TCGEN05_TWO_KERNEL_BWD,
+    PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05, PATH_TCGEN05_ONE_TILE, PATH_TCGEN05_TWO_TILES, PATH_TCGEN05_FUSED_BWD,
     ModaLibraryError,
     device_status,
 )

@@ -17,7 +17,7 @@ MODE_CAUSAL, MODE_NONCAUSAL, MODE_CHUNK_VISIBLE, MODE_DEPTH_ONLY = 0, 1, 2, 3
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 PATH_AUTO, PATH_SIMT_MMA, PATH_TCGEN05 = 0, 1, 2
 PATH_TCGEN05_ONE_TILE, PATH_TCGEN05_TWO_TILES = 3, 4   # tcgen05 with the forward kernel fixed (tests)
-PATH_TCGEN05_TWO_KERNEL_BWD = 5                        # tcgen05 with the dq + dk/dv backward forced
+PATH_TCGEN05_FUSED_BWD = 5                             # tcgen05 with the fused five-matmul backward (D = 128)
 STATIC_SCRATCH_BYTES = 8 << 20   # MODA_B200_STATIC_SCRATCH_BYTES
 
 # every symbol include/moda_b200.h declares

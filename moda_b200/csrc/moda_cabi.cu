@@ -70,7 +70,7 @@ int check_problem(const moda_problem* pr) {
   if (pr->mode == MODA_CHUNK_VISIBLE) {
     if (pr->chunk_rows < 1 || pr->chunk_rows % pr->G != 0) return MODA_ERR_CHUNK;
   }
-  if (pr->path < MODA_PATH_AUTO || pr->path > MODA_PATH_TCGEN05_TWO_KERNEL_BWD) return MODA_ERR_MODE;
+  if (pr->path < MODA_PATH_AUTO || pr->path > MODA_PATH_TCGEN05_FUSED_BWD) return MODA_ERR_MODE;
   if (!(pr->scale == pr->scale)) return MODA_ERR_SHAPE;  // NaN scale
   if (pr->depth_rows_per_pos < 0 || (pr->depth_rows_per_pos > 0 && pr->depth_rows_per_pos < pr->L)) return MODA_ERR_SHAPE;
   if ((int64_t)pr->T_kv * pr->depth_rows_per_pos > (int64_t)1 << 30) return MODA_ERR_SHAPE;

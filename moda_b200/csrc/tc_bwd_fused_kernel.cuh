@@ -23,15 +23,13 @@
 // with the maxima over the sequence keys of the (batch, head), times a safety factor for the
 // rounding of P and dS to 16 bits.
 //
-// Work decomposition.  A CTA is one (query segment, key tile) pair: segments of kFuSegRows query
-// rows, CTAs ordered segment-major, so that the CTAs resident at any time add their dQ contributions
-// to the same few megabytes of the accumulator (which then live in L2: with one CTA per key tile
-// walking all of its query rows the resident CTAs were spread over the whole sequence and the
-// reductions ran at DRAM speed) and read the same Q / dO rows.  dK and dV of a key tile are then the
-// sum over its segments: the CTAs of one key tile add their fp32 partial sums into a per-tile
-// buffer strictly in segment order - CTA (s, j) waits (bounded) on a counter for CTA (s - 1, j),
-// which has a lower block index and was therefore scheduled earlier - and the last segment writes
-// dk / dv.  A fixed order of fp32 additions, like a fixed-point sum, does not depend on timing.
+// Where this stands.  At T = 65536 (G = 4, D = 128, 8 KV heads) this kernel takes as long as the
+// dq and dk/dv kernels together although it executes 5/7 of their matmuls: with one CTA per MMA
+// (cta_group::1) every kernel here is bound by shared-memory bandwidth, not by the tensor pipe, and
+// what decides the time is the bytes of shared memory moved per 128 x 64 block of scores.  Two
+// kernels have 2 x 512 TMEM columns and keep Q, dO, K and V as TMEM operands; one kernel has 512,
+// keeps V only, and additionally stages the dQ contribution through shared memory.  It is therefore
+// an alternative (MODA_PATH_TCGEN05_FUSED_BWD), not the default.
 //
 // Warp roles as in dkv_kernel (TMA warp, score-MMA warp, update-MMA warp, two softmax warpgroups on
 // alternate steps).  TMEM (512 columns): [0,64) S^T, [64,128) dP^T (one fp32 score stage),
@@ -46,12 +44,11 @@
 namespace moda {
 namespace tc {
 
-constexpr int kFuSegRows = 8192;                            // query rows per segment (128 steps)
 constexpr int kFuRing = 3;                                  // ring of {Q, dO, lse, delta, scale} step slots
 constexpr uint32_t kFuStat = 768;                           // 64 lse, 64 delta, one float4 {scale, 1/scale, -, -}
 struct FuBars {   // barrier indices
   static constexpr int res = 0, kfull = 1, full0 = 2, empty0 = 2 + kFuRing, s0 = 2 + 2 * kFuRing, p0 = s0 + 2,
-                       r0 = p0 + 2, t0 = r0 + 2, done = t0 + 2, qfree = done + 1, ws0 = qfree + 1, count = ws0 + 2;
+                       r0 = p0 + 2, t0 = r0 + 2, done = t0 + 2, qfree = done + 1, ws0 = qfree + 1, qd0 = ws0 + 2, count = qd0 + 2;
 };
 static_assert(FuBars::count <= kMaxBars, "control block too small");
 constexpr uint32_t kFuSmem = kTileBytes + kFuRing * 2 * step_tile<128>() + 2 * kDkvPairBytes + kFuRing * kFuStat + kCtlBytes;
@@ -137,40 +134,12 @@ __global__ void __launch_bounds__(256) scale_kernel(const float* delta_t, const 
   }
 }
 
-// Key tiles that see at least one row of query segment s.
-__host__ __device__ __forceinline__ int fu_tiles_in_segment(const Params& p, int s, int n_tiles) {
-  if (p.mode == kNonCausal) return n_tiles;
-  const int64_t last_row = min((int64_t)(s + 1) * kFuSegRows, (int64_t)p.T_q) - 1;     // last valid row of the segment
-  const int64_t last_key = last_row / p.G;                                             // its last visible key
-  return (int)min((int64_t)n_tiles, last_key / kBN + 1);
-}
-inline int64_t fu_grid_size(const Params& p) {
-  const int n_tiles = (p.T_kv + kBN - 1) / kBN, n_seg = (p.T_q + kFuSegRows - 1) / kFuSegRows;
-  int64_t n = 0;
-  for (int s = 0; s < n_seg; ++s) n += fu_tiles_in_segment(p, s, n_tiles);
-  return n;
-}
-
-// Bounded wait on a global counter written by other CTAs (release/acquire through the counter).
-__device__ __forceinline__ bool wait_counter(const int* ctr, int want, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
-    if (v >= want) return true;
-    if (*abort_flag != 0) return false;
-    __nanosleep(64);
-  }
-  *abort_flag = 1;
-  record_failure(3 << 8);
-  return false;
-}
-
 // =========================================================================== fused backward
-// grid (sum over segments of the key tiles that see them, H, B), 352 threads.
+// grid (ceil(T_kv/128), H, B), 352 threads.
 template <typename T>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
-                 const float* lse_t, const float4* scale_blk, int* dq_acc, float* dkv_part, int* tile_ctr, int T_qp) {
+                 const float* lse_t, const float4* scale_blk, int* dq_acc, int T_qp) {
   constexpr int D = 128;
   constexpr int R = kFuRing;
   using B_ = FuBars;
@@ -199,26 +168,14 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
 
   const int h = blockIdx.y, b = blockIdx.z;
+  const int c0 = (int)blockIdx.x * kBN;        // key tile 0 is seen by every query row: heaviest tiles first
   const int n_keys = p.T_kv;
-  const int n_tiles = (n_keys + kBN - 1) / kBN;
-  const int n_seg = (p.T_q + kFuSegRows - 1) / kFuSegRows;
-  int seg = 0, tile = (int)blockIdx.x;         // block index -> (segment, key tile), segment-major
-  for (; seg < n_seg; ++seg) {
-    const int ns = fu_tiles_in_segment(p, seg, n_tiles);
-    if (tile < ns) break;
-    tile -= ns;
-  }
-  if (seg >= n_seg) return;
-  const int c0 = tile * kBN;
   const int c_last = min(c0 + kBN, n_keys) - 1;
 
-  // query rows of this segment that can see a key of this tile: [q_begin, q_end), in steps of 64
-  int q_tile = (p.mode == kNonCausal) ? 0 : c0 * p.G;          // first row that sees the tile
-  q_tile = (q_tile / kStep) * kStep;
-  const int seg_first = q_tile / kFuSegRows;                    // first segment of this key tile
-  const int q_begin = max(q_tile, seg * kFuSegRows);
-  const int q_end = min((seg + 1) * kFuSegRows, (p.T_q + kStep - 1) / kStep * kStep);
-  const int n = (q_end - q_begin) / kStep;
+  // query rows that can see a key of this tile: [q_begin, T_q), walked in steps of 64
+  int q_begin = (p.mode == kNonCausal) ? 0 : c0 * p.G;
+  q_begin = (q_begin / kStep) * kStep;
+  const int n = (p.T_q - q_begin + kStep - 1) / kStep;
 
   if (tid == 0) {
     mbar_init(bars + 8 * B_::res, 128);
@@ -230,6 +187,7 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
       mbar_init(bars + 8 * (B_::s0 + i), 1); mbar_init(bars + 8 * (B_::p0 + i), 128);
       mbar_init(bars + 8 * (B_::r0 + i), 128); mbar_init(bars + 8 * (B_::t0 + i), 1);
       mbar_init(bars + 8 * (B_::ws0 + i), 128);
+      mbar_init(bars + 8 * (B_::qd0 + i), 1);
     }
     *abort_flag = 0;
     *drain_flag = 0;
@@ -331,22 +289,22 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
         const uint32_t pair = sPT + (j & 1) * kDkvPairBytes;
         const uint64_t dpt = desc_kmajor(pair), dst = desc_kmajor(pair + kScoreTile);
         const uint64_t dsb = desc_mnmajor(pair + kScoreTile, kScoreTile);
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            mma_ss(tmem_dV, desc_add(dpt, kk * 32), desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-            mma_ss(tmem_dK, desc_add(dst, kk * 32), desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-          }
-          tc_commit(bars + 8 * (B_::empty0 + slot));      // ring slot j may be refilled
-        }
-        __syncwarp();
+        // dQ^T first: while dV / dK of this step run, the warpgroup takes dQ^T(j) out of TMEM, so the
+        // block is free again by the time the next step's dQ^T is issued
         if (j >= 1 && !(ok = mbar_wait(bars + 8 * B_::qfree, (j - 1) & 1, abort_flag, B_::qfree))) break;
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             mma_ss(tmem_dQ, desc_add(dkt, kk * 2048), desc_add(dsb, kk * 2048), idesc_q, kk > 0);
-          tc_commit(bars + 8 * (B_::t0 + (j & 1)));       // tile pair j & 1 may be rewritten; dQ^T(j) is complete
+          tc_commit(bars + 8 * (B_::qd0 + (j & 1)));      // dQ^T(j) is complete
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            mma_ss(tmem_dV, desc_add(dpt, kk * 32), desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            mma_ss(tmem_dK, desc_add(dst, kk * 32), desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(bars + 8 * (B_::empty0 + slot));      // ring slot j may be refilled
+          tc_commit(bars + 8 * (B_::t0 + (j & 1)));       // tile pair j & 1 may be rewritten
           if (j == n - 1) tc_commit(bars + 8 * B_::done);
         }
         __syncwarp();
@@ -399,10 +357,9 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
     // dQ^T of step j (this warpgroup's previous step): out of TMEM, scaled and rounded to int32,
     // transposed into [64 query rows][128] in shared memory - the warpgroup's own P^T / dS^T tile
     // pair, which update(j) has finished reading and which is exactly 32 KB - and added to the
-    // accumulator rows with ONE bulk reduction (an L2-side integer add of 32 KB; per-thread
-    // red.global instructions for the same words were 18 ms slower per backward of 65536 positions).
+    // accumulator rows with ONE bulk reduction (an L2-side integer add of 32 KB).
     auto dq_out = [&](int j, float esc) -> bool {
-      if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_::t0 + (j & 1)), (j >> 1) & 1, abort_flag, B_::t0 + (j & 1)))) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_::qd0 + (j & 1)), (j >> 1) & 1, abort_flag, B_::qd0 + (j & 1)))) return false;
       tc_fence_after();
       uint32_t qv[64];
       tmem_ld32<0>(tmem_dQ + lane_addr, qv);
@@ -410,6 +367,8 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bars + 8 * B_::qfree);
+      // the tile pair is the staging buffer: dV / dK of step j must have finished reading it
+      if (!__all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_::t0 + (j & 1)), (j >> 1) & 1, abort_flag, B_::t0 + (j & 1)))) return false;
       int* stage = reinterpret_cast<int*>(smem_raw + pt_off + (j & 1) * kDkvPairBytes);
 #pragma unroll
       for (int q = 0; q < 64; ++q) stage[q * D + row] = __float2int_rn(__uint_as_float(qv[q]) * esc);
@@ -499,47 +458,18 @@ bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMa
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_::done, 0, abort_flag, B_::done));
     if (ok && n > 0) {
       tc_fence_after();
-      // dV (warpgroup 0) / dK (warpgroup 1) of this segment, added to the partial sums of the earlier
-      // segments of the key tile in segment order; the last segment writes the 16-bit result.
-      const int64_t tile_id = ((int64_t)b * p.H + h) * n_tiles + tile;
-      int* ctr = tile_ctr + tile_id;
-      const bool first = seg == seg_first, last = seg == n_seg - 1;
-      if (!first) ok = __all_sync(0xffffffffu, wait_counter(ctr, 256 * (seg - seg_first), abort_flag));
-      if (ok) {
-        const View& ov = (wg == 0) ? p.dv : p.dk;
-        T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, key, h);
-        float* part = dkv_part + ((tile_id * 2 + wg) * kBN + row) * D;      // this key row's fp32 partial sums
-        const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;
-        const float mul = (wg == 0) ? 1.f : p.scale;
+      const View& ov = (wg == 0) ? p.dv : p.dk;
+      T* gout = reinterpret_cast<T*>(ov.ptr) + ov.off(b, key, h);
+      const uint32_t tsrc = (wg == 0) ? tmem_dV : tmem_dK;      // warpgroup 0 stores dV, warpgroup 1 dK
+      const float mul = (wg == 0) ? 1.f : p.scale;
 #pragma unroll
-        for (int q4 = 0; q4 < D / 32; ++q4) {
-          uint32_t ov32[32];
-          tmem_ld32<0>(tsrc + lane_addr + q4 * 32, ov32);
-          tmem_wait_ld();
-          if (!first) {
+      for (int q4 = 0; q4 < D / 32; ++q4) {
+        uint32_t ov32[32];
+        tmem_ld32<0>(tsrc + lane_addr + q4 * 32, ov32);
+        tmem_wait_ld();
+        if (key < n_keys) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 a = *reinterpret_cast<const float4*>(part + q4 * 32 + 4 * i);
-              ov32[4 * i + 0] = __float_as_uint(__uint_as_float(ov32[4 * i + 0]) + a.x);
-              ov32[4 * i + 1] = __float_as_uint(__uint_as_float(ov32[4 * i + 1]) + a.y);
-              ov32[4 * i + 2] = __float_as_uint(__uint_as_float(ov32[4 * i + 2]) + a.z);
-              ov32[4 * i + 3] = __float_as_uint(__uint_as_float(ov32[4 * i + 3]) + a.w);
-            }
-          }
-          if (last) {
-            if (key < n_keys) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8) = pack8_scaled<T>(ov32 + i * 8, mul);
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint4*>(part + q4 * 32 + 4 * i) = make_uint4(ov32[4 * i], ov32[4 * i + 1], ov32[4 * i + 2], ov32[4 * i + 3]);
-          }
-        }
-        if (!last) {       // publish: this thread's partial sums are visible before its count is
-          __threadfence();
-          atomicAdd(ctr, 1);
+          for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(gout + q4 * 32 + i * 8) = pack8_scaled<T>(ov32 + i * 8, mul);
         }
       }
     }

@@ -1,12 +1,13 @@
 // Host side of the tcgen05 backward: workspace layout, tensor maps and the launch sequences.
 //
-// Two sequences exist.  The FUSED one (D = 128, the default there) runs
+// Two sequences exist.  The default TWO-KERNEL one is the reference's structure: a query-parallel
+// dq kernel and a key-parallel dk/dv kernel that both recompute the scores (seven executed matmuls).
+// The FUSED one (D = 128, selected with MODA_PATH_TCGEN05_FUSED_BWD) runs
 //     bounds (kvmax, pre, scale)  ->  bwd_fused_kernel over the sequence key tiles (dK, dV and the
 //     sequence keys' share of dQ in a fixed-point accumulator)  ->  dq_kernel over the depth keys only,
 //     which adds the two shares and writes dq  ->  depth gradients
-// and executes the five matmuls of the backward once each.  The TWO-KERNEL one (D = 64, or forced
-// with MODA_PATH_TCGEN05_TWO_KERNEL_BWD) is the reference's structure: a query-parallel dq kernel
-// and a key-parallel dk/dv kernel that both recompute the scores.
+// and executes the five matmuls of the backward once each; measured, it is no faster (see
+// tc_bwd_fused_kernel.cuh), which is why it is not the default.
 #pragma once
 #include "tc_bwd_fused_kernel.cuh"
 
@@ -19,17 +20,16 @@ inline bool bwd_supported(const moda_problem* pr) {
   return (pr->D == 128 || pr->D == 64) && pr->mode != MODA_DEPTH_ONLY && pr->scale > 0.f && depth_layout_supported(pr);
 }
 inline bool bwd_is_fused(const moda_problem* pr) {
-  return bwd_supported(pr) && pr->D == 128 && pr->path != MODA_PATH_TCGEN05_TWO_KERNEL_BWD;
+  return bwd_supported(pr) && pr->D == 128 && pr->path == MODA_PATH_TCGEN05_FUSED_BWD;
 }
 
 inline size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 // Workspace after the per-row delta of the generic path: delta_t, lse_t [B, H, T_qp] fp32 and, for
 // the fused sequence, norm_t [B, H, T_qp] fp32, scale_blk [B, H, T_qp / 64] float4, kvmax [B, H, 2]
-// the dQ accumulator [B, H, T_qp, 128] int32, the fp32 partial sums of dV and dK per key tile
-// [B, H, tiles, 2, 128, 128] and one counter per key tile.
+// and the dQ accumulator [B, H, T_qp, 128] int32.
 struct BwdWorkspace {
-  size_t stat = 0, scale = 0, kvmax = 0, acc = 0, part = 0, ctr = 0, total = 0;
+  size_t stat = 0, scale = 0, kvmax = 0, acc = 0, total = 0;
   explicit BwdWorkspace(const moda_problem* pr) {
     if (!bwd_supported(pr)) return;
     const size_t rows = (size_t)pr->B * pr->H * padded_rows(pr->T_kv * pr->G);
@@ -39,20 +39,14 @@ struct BwdWorkspace {
       scale = align256(rows / 64 * sizeof(float4));
       kvmax = align256((size_t)pr->B * pr->H * 2 * sizeof(int));
       acc = align256(rows * 128 * sizeof(int));
-      const size_t tiles = (size_t)pr->B * pr->H * ((pr->T_kv + kBN - 1) / kBN);
-      part = align256(tiles * 2 * kBN * 128 * sizeof(float));
-      ctr = align256(tiles * sizeof(int));
-      total += stat + scale + kvmax + acc + part + ctr;
+      total += stat + scale + kvmax + acc;
     }
   }
 };
 inline size_t bwd_extra_workspace_bytes(const moda_problem* pr) { return BwdWorkspace(pr).total; }
 
 struct BwdMaps { DqMaps dq; DkvMaps dkv; DgOutMaps out; };
-struct BwdBuffers {
-  float *delta_t, *lse_t, *norm_t; float4* scale_blk; int* kvmax; int* dq_acc; float* dkv_part; int* tile_ctr;
-  size_t acc_bytes, kvmax_bytes, ctr_bytes;
-};
+struct BwdBuffers { float *delta_t, *lse_t, *norm_t; float4* scale_blk; int* kvmax; int* dq_acc; size_t acc_bytes, kvmax_bytes; };
 
 template <typename T, int D>
 inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, const BwdBuffers& w, int T_qp, bool dg, bool fused,
@@ -95,15 +89,12 @@ inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, const BwdBuffer
       if ((e = cudaGetLastError()) != cudaSuccess) return e;
       *launches += 1;
       if ((e = cudaMemsetAsync(w.dq_acc, 0, w.acc_bytes, st)) != cudaSuccess) return e;
-      if ((e = cudaMemsetAsync(w.tile_ctr, 0, w.ctr_bytes, st)) != cudaSuccess) return e;
       {
         auto kern = bwd_fused_kernel<T>;
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFuSmem)) != cudaSuccess) return e;
-        const int64_t n_cta = fu_grid_size(p);
-        if (n_cta > 0x7fffffff) return cudaErrorInvalidConfiguration;
-        dim3 grid((unsigned)n_cta, p.H, p.B);
+        dim3 grid(n_seq, p.H, p.B);
         prof::Scope ps(prof::kBwdFusedTc, st);
-        kern<<<grid, kDkvThreads, kFuSmem, st>>>(p, m.dkv, delta_t, lse_t, w.scale_blk, w.dq_acc, w.dkv_part, w.tile_ctr, T_qp);
+        kern<<<grid, kDkvThreads, kFuSmem, st>>>(p, m.dkv, delta_t, lse_t, w.scale_blk, w.dq_acc, T_qp);
       }
       if ((e = cudaGetLastError()) != cudaSuccess) return e;
       *launches += 1;
@@ -175,11 +166,8 @@ inline int bwd(const Params& p, const moda_problem* pr, void* extra, int n_sm, c
     w.scale_blk = reinterpret_cast<float4*>(base + 3 * ws.stat);
     w.kvmax = reinterpret_cast<int*>(base + 3 * ws.stat + ws.scale);
     w.dq_acc = reinterpret_cast<int*>(base + 3 * ws.stat + ws.scale + ws.kvmax);
-    w.dkv_part = reinterpret_cast<float*>(base + 3 * ws.stat + ws.scale + ws.kvmax + ws.acc);
-    w.tile_ctr = reinterpret_cast<int*>(base + 3 * ws.stat + ws.scale + ws.kvmax + ws.acc + ws.part);
     w.acc_bytes = ws.acc;
     w.kvmax_bytes = ws.kvmax;
-    w.ctr_bytes = ws.ctr;
   }
   const bool dep = p.L > 0;
   const int D = pr->D, dt = pr->dtype;

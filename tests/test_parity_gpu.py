@@ -253,11 +253,11 @@ def test_tcgen05_path_refuses_what_it_cannot_run(M):
 ])
 @pytest.mark.parametrize("D,bwd", [(64, "two_kernel"), (128, "fused"), (128, "two_kernel")])
 def test_tcgen05_forward_and_backward(M, mode, T, L, G, dt, D, bwd):
-    """tcgen05 forward + backward, forced: the fused key-stationary backward (D = 128: five matmuls,
-    dq summed in fixed point) and the two-kernel backward (dq kernel + dk/dv kernel), each with the
-    statistics pass and the depth-gradient kernel."""
+    """tcgen05 forward + backward, forced: the two-kernel backward (dq kernel + dk/dv kernel, the
+    default) and the fused key-stationary backward (D = 128: five matmuls, dq summed in fixed
+    point), each with the statistics pass and the depth-gradient kernel."""
     from moda_b200 import _cabi
-    path = M.PATH_TCGEN05 if bwd == "fused" or D == 64 else M.PATH_TCGEN05_TWO_KERNEL_BWD
+    path = M.PATH_TCGEN05_FUSED_BWD if bwd == "fused" else M.PATH_TCGEN05
     _run_case(M, mode, 2 if T < 600 else 1, T, 2, D, L, G, DT[dt], None, seed=200 + T, path=path, check_bwd=True)
     assert _cabi.device_status() == 0
 
@@ -275,7 +275,7 @@ def test_fused_backward_fixed_point_scale_follows_the_gradient_magnitude(M, scal
     dout = dout.to(torch.bfloat16)
     ref = mo.moda_attention_ref_grads(q, k, v, kd, vd, dout, None, G, mo.MODE_CAUSAL, 1)
     q, k, v, kd, vd, dout = [x.to(dev) for x in (q, k, v, kd, vd, dout)]
-    old = M.set_kernel_path(M.PATH_TCGEN05)
+    old = M.set_kernel_path(M.PATH_TCGEN05_FUSED_BWD)
     try:
         o, lse = M.parallel_moda_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=G)
         g1 = M.parallel_moda_bwd(q, k, v, o, None, lse, dout, cached_k=kd, cached_v=vd, moda_group_num=G)
@@ -427,7 +427,7 @@ def _random_cases(seed, n):
         T = min(T, max(1, 4200 // G))
         L = rng.choice([0, 1, 2, 3, 5, 8, 11, 16, 24, 32, 33])
         cases.append((mode, rng.choice([1, 2]), T, rng.choice([1, 2, 3]), L, G, rng.choice(["bf16", "fp16"]),
-                      rng.choice([64, 128]), rng.choice(["auto", "tcgen05", "one_tile", "two_tiles", "two_kernel_bwd"]),
+                      rng.choice([64, 128]), rng.choice(["auto", "tcgen05", "one_tile", "two_tiles", "fused_bwd"]),
                       rng.randrange(1 << 30)))
     return cases
 
@@ -438,6 +438,6 @@ def test_randomised_shapes(M, mode, B, T, H, L, G, dt, D, path, seed):
     dim and kernel path (auto / tcgen05 / each forward forced); forward and backward."""
     from moda_b200 import _cabi
     paths = {"auto": None, "tcgen05": M.PATH_TCGEN05, "one_tile": M.PATH_TCGEN05_ONE_TILE,
-             "two_tiles": M.PATH_TCGEN05_TWO_TILES, "two_kernel_bwd": M.PATH_TCGEN05_TWO_KERNEL_BWD}
+             "two_tiles": M.PATH_TCGEN05_TWO_TILES, "fused_bwd": M.PATH_TCGEN05_FUSED_BWD}
     _run_case(M, mode, B, T, H, D, L, G, DT[dt], None, seed=seed, path=paths[path])
     assert _cabi.device_status() == 0
