@@ -42,6 +42,7 @@ WORKLOADS = {
     "config3_fda_T8192": ("fda", 8, 8192, 16, 1, 128, 32),
     "config5_deit_noncausal_T197": ("noncausal", 256, 197, 6, 1, 64, 11),
     "small_chunk_visible_T8192": ("chunk", 1, 8192, 8, 4, 128, 32),
+    "small_fda_T8192": ("fda", 1, 8192, 4, 1, 128, 32),               # config 3 at 1/32 of its units (profiler captures)
     # sequence-only twin of config 4 (same kernels, L = 0): gives the depth-KV overhead
     "config4_seq_only_twin_T65536": ("chunk", 1, 65536, 8, 4, 128, 0),
     # the causal, own-position-depth operator at config 4's size
