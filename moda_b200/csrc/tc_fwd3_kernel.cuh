@@ -20,17 +20,24 @@
 //   warp 8 (MMA)   S_a = Q_a K^T (SS, M128 N128), O_a += P_a V (TS, N = D: P_a packed over S_a in TMEM).
 //   warps 0-3 / 4-7  softmax of query tile 0 / 1, lazy O rescale, epilogue.
 //
-// TMEM (512 columns): S_0 [0,128), S_1 [128,256), O_0 [256,256+D), O_1 [384,384+D).  Every wait is
-// bounded, as in the other tcgen05 kernels.
+// TMEM (512 columns): S_0 [0,128), S_1 [128,256), O_0 [256,256+D), O_1 [384,384+D).  A softmax warp
+// hands P over in two parts (columns [0,48) and [48,64) of the packed block), so most of PV runs
+// under the last exponentials.  Every wait is bounded, as in the other tcgen05 kernels.
 #pragma once
 #include "tc_bwd_kernels.cuh"
 
 namespace moda {
 namespace tc {
 
-constexpr int kF3Threads = 320;
-// barriers: q, full[2], empty[2], s[2], p[2], done
-struct F3Bars { static constexpr int q = 0, full0 = 1, empty0 = 3, s0 = 5, p0 = 7, done = 9, count = 10; };
+constexpr int kF3Threads = 384;          // 8 softmax warps + MMA warp + TMA warp + 2 idle warps (a whole warpgroup)
+// Registers per thread: the CTA starts with 168 (65536 / 384, rounded down to a multiple of 8); after
+// the set-up the last warpgroup (MMA, TMA) gives registers back and the softmax warpgroups take
+// them, so that a softmax thread holds its 128 scores, the packed P and the partial sums without spills.
+constexpr uint32_t kF3SoftmaxRegs = 216, kF3IssueRegs = 72;
+static_assert(2 * 128 * kF3SoftmaxRegs + 128 * kF3IssueRegs <= 384 * 168, "register pool of the CTA exceeded");
+// barriers: q, full[2], empty[2], s[2], p[2] (first kF3PSplit pairs of P stored), done, pl[2] (the rest)
+struct F3Bars { static constexpr int q = 0, full0 = 1, empty0 = 3, s0 = 5, p0 = 7, done = 9, pl0 = 10, count = 12; };
+constexpr int kF3PSplit = 48;   // 16-bit pairs (= TMEM columns) of P handed to the PV matmul ahead of the last 16
 static_assert(F3Bars::count <= kMaxBars, "control block too small");
 template <int D> __host__ __device__ constexpr uint32_t f3_smem() { return 6 * tile_bytes<D>() + kCtlBytes; }   // Q_0, Q_1, two {K, V} slots
 
@@ -106,7 +113,8 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       mbar_init(bars + 8 * (B_::full0 + i), 1);
       mbar_init(bars + 8 * (B_::empty0 + i), 1);
       mbar_init(bars + 8 * (B_::s0 + i), 1);
-      mbar_init(bars + 8 * (B_::p0 + i), 128);
+      mbar_init(bars + 8 * (B_::p0 + i), 4);      // one arrival per softmax warp
+      mbar_init(bars + 8 * (B_::pl0 + i), 4);
     }
     *abort_flag = 0;
     *drain_flag = 0;
@@ -123,7 +131,10 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
 
+  // Warpgroup-wide register reallocation, first thing in every role: all four warps of the last
+  // warpgroup release, so the requests of the softmax warpgroups cannot starve.
   if (warp == 9) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kF3IssueRegs));
     // ---------------------------------------------------------------- TMA warp
     if (pl.n > 0) {
       if (elect_one()) {
@@ -163,6 +174,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       }
     }
   } else if (warp == 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kF3IssueRegs));
     // ---------------------------------------------------------------- MMA warp
     if (pl.n > 0) {
       constexpr uint32_t idesc_qk = instr_desc(fmt, 128, false);
@@ -187,7 +199,8 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         ++qk_cnt[a];
         return true;
       };
-      // O_a += P_a V(s); `last`: no other MMA of step s follows, the slot may be refilled
+      // O_a += P_a V(s); `last`: no other MMA of step s follows, the slot may be refilled.  The
+      // matmuls over the first kF3PSplit columns of P go out while the softmax still computes the rest.
       auto pv = [&](int a, int s, bool last) -> bool {
         if (!mbar_wait(bars + 8 * (B_::p0 + a), pv_cnt[a] & 1, abort_flag, B_::p0 + a)) return false;
         tc_fence_after();
@@ -195,8 +208,16 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         const uint32_t sV = sRing + slot * 2 * kTile + kTile, tS = tmem + a * 128, tO = tmem + 256 + a * 128;
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
+          for (int kk = 0; kk < kF3PSplit / 8; ++kk)
             mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[a] > 0 || kk > 0) ? 1u : 0u);
+        }
+        __syncwarp();
+        if (!mbar_wait(bars + 8 * (B_::pl0 + a), pv_cnt[a] & 1, abort_flag, B_::pl0 + a)) return false;
+        tc_fence_after();
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = kF3PSplit / 8; kk < 8; ++kk)
+            mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv, 1u);
           if (last) tc_commit(bars + 8 * (B_::empty0 + slot));
         }
         __syncwarp();
@@ -229,7 +250,10 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         __syncwarp();
       }
     }
+  } else if (warp >= 10) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kF3IssueRegs));
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(kF3SoftmaxRegs));
     // ---------------------------------------------------------------- softmax warps
     const int a = warp >> 2, wq = warp & 3;          // query tile; TMEM lane quarter
     const int row = wq * 32 + lane;                  // row of the tile == TMEM lane
@@ -259,21 +283,28 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       // A depth tile holds the rows of several positions; a warp whose 32 query rows see none of
       // its columns contributes an all-zero P block and skips the scores altogether.
       const bool none = is_dep && __all_sync(0xffffffffu, (c0 + kBN <= lo) || (c0 >= hi));
+      // P is complete for a group of columns once every lane's stores have finished: one arrival per warp
+      auto p_ready = [&](int bar_id) {
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + 8 * (bar_id + a));
+      };
       if (none) {
         uint32_t z[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) z[i] = 0u;
         tmem_st32<0>(tmem_S + lane_addr + 0, z);
         tmem_st32<32>(tmem_S + lane_addr + 32, z);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(bars + 8 * (B_::p0 + a));
+        p_ready(B_::p0);
+        p_ready(B_::pl0);
         ++cnt;
         continue;
       }
       float alpha = 1.f;
       bool grow = false;
       uint32_t pk[64];
+      float sc[128];
       {
         uint32_t su[128];
         tmem_ld32<0>(tmem_S + lane_addr + 0, su);
@@ -281,10 +312,10 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         tmem_ld32<64>(tmem_S + lane_addr + 64, su);
         tmem_ld32<96>(tmem_S + lane_addr + 96, su);
         tmem_wait_ld();
-        softmax_row128<T, kPolyEvery>(su, masked, is_dep && (p.L & 31) == 0, c0, lo, hi, c, m_used, l, alpha, grow, pk);
+#pragma unroll
+        for (int i = 0; i < 128; ++i) sc[i] = __uint_as_float(su[i]);
       }
-      tmem_st32<0>(tmem_S + lane_addr + 0, pk);
-      tmem_st32<32>(tmem_S + lane_addr + 32, pk);
+      softmax_prepare(sc, masked, is_dep && (p.L & 31) == 0, c0, lo, hi, c, m_used, l, alpha, grow);
       // rescale O (TMEM round trip) only when some row of this warp moved its maximum; the PV of
       // this tile's previous step finished before these scores were produced (issue order)
       if (__any_sync(0xffffffffu, grow)) {
@@ -298,9 +329,15 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
           tmem_st32<0>(tmem_O + lane_addr + q4 * 32, ov);
         }
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bars + 8 * (B_::p0 + a));
+      float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      softmax_exps<T, kPolyEvery, 0, kF3PSplit>(sc, c, m_used, sum2, pk);
+      tmem_st32<0>(tmem_S + lane_addr + 0, pk);
+      tmem_st16<32>(tmem_S + lane_addr + 32, pk);
+      p_ready(B_::p0);
+      softmax_exps<T, kPolyEvery, kF3PSplit, 64>(sc, c, m_used, sum2, pk);
+      tmem_st16<48>(tmem_S + lane_addr + 48, pk);
+      p_ready(B_::pl0);
+      l += softmax_total(sum2);
       ++cnt;
     }
 

@@ -228,19 +228,16 @@ __device__ __forceinline__ float2 exp2x2_fma(float2 x) {
                      __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23)));
 }
 
-// One row's online-softmax step over the 128 scores of a key tile (register bits in su; thread =
-// query row).  Masks columns outside [lo, hi) when `masked` (`uniform32`: [lo, hi) and the tile are
-// aligned to 32 columns), takes the row maximum, keeps the old
-// reference maximum unless the new one is more than 2^8 larger (lazy rescale: alpha / grow tell
-// the caller to rescale O), and returns P = exp2(s * c - m) as 64 packed 16-bit pairs, with the
-// row sum added to l.  scale > 0 is required (the maximum is taken before scaling).  One pair in
-// kPolyEvery takes its two exponentials on the FMA pipe (exp2x2_fma) instead of the exp2 unit.
-template <typename T, int kPolyEvery>
-__device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, bool uniform32, int c0, int lo, int hi, float c,
-                                               float& m_used, float& l, float& alpha, bool& grow, uint32_t (&pk)[64]) {
-  float s[128];
-#pragma unroll
-  for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
+// One row's online-softmax step over the 128 scores of a key tile (thread = query row), in two
+// parts so that a caller can hand the first columns of P to the PV matmul before the last ones
+// are computed.  scale > 0 is required (the maximum is taken before scaling).
+//
+// softmax_prepare: masks columns outside [lo, hi) when `masked` (`uniform32`: [lo, hi) and the tile
+// are aligned to 32 columns), takes the row maximum, keeps the old reference maximum unless the
+// new one is more than 2^8 larger (lazy rescale: alpha / grow tell the caller to rescale O) and
+// scales the running row sum l by alpha.
+__device__ __forceinline__ void softmax_prepare(float (&s)[128], bool masked, bool uniform32, int c0, int lo, int hi, float c,
+                                                float& m_used, float& l, float& alpha, bool& grow) {
   if (masked && uniform32) {
     // depth tile with L a multiple of 32: a row sees whole positions, so each aligned group of 32
     // columns is visible or not as a whole - four tests instead of 128
@@ -277,12 +274,18 @@ __device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool m
     grow = (m_used != -INFINITY);    // nothing accumulated yet => nothing to rescale
     m_used = m_new;
   }
-  const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
   l *= alpha;
+}
+
+// softmax_exps: P = exp2(s * c - m) for the column pairs [I0, I1) as packed 16-bit pairs in pk, their
+// sums added to the four partial sums.  One pair in kPolyEvery takes its two exponentials on the FMA
+// pipe (exp2x2_fma) instead of the exp2 unit.
+template <typename T, int kPolyEvery, int I0, int I1>
+__device__ __forceinline__ void softmax_exps(const float (&s)[128], float c, float m_used, float2 (&sum2)[4], uint32_t (&pk)[64]) {
+  const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
   const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_sub, -m_sub);
-  float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-  for (int i = 0; i < 64; ++i) {
+  for (int i = I0; i < I1; ++i) {
     const float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), c2, nm2);
     float2 pp;
     if (kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery > 0 ? kPolyEvery : 1) - 1) {
@@ -294,8 +297,23 @@ __device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool m
     sum2[i & 3] = __fadd2_rn(sum2[i & 3], pp);
     pk[i] = Pack<T>::pack(pp.x, pp.y);
   }
+}
+__device__ __forceinline__ float softmax_total(const float2 (&sum2)[4]) {
   const float2 tot = __fadd2_rn(__fadd2_rn(sum2[0], sum2[1]), __fadd2_rn(sum2[2], sum2[3]));
-  l += tot.x + tot.y;
+  return tot.x + tot.y;
+}
+
+// The whole step at once.
+template <typename T, int kPolyEvery>
+__device__ __forceinline__ void softmax_row128(const uint32_t (&su)[128], bool masked, bool uniform32, int c0, int lo, int hi, float c,
+                                               float& m_used, float& l, float& alpha, bool& grow, uint32_t (&pk)[64]) {
+  float s[128];
+#pragma unroll
+  for (int i = 0; i < 128; ++i) s[i] = __uint_as_float(su[i]);
+  softmax_prepare(s, masked, uniform32, c0, lo, hi, c, m_used, l, alpha, grow);
+  float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+  softmax_exps<T, kPolyEvery, 0, 64>(s, c, m_used, sum2, pk);
+  l += softmax_total(sum2);
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
