@@ -66,9 +66,10 @@ __device__ __forceinline__ void decode_unit(int64_t unit, int H, int T_kv, int& 
 
 // ------------------------------------------------------------------------- forward
 // One warp per (b, t, h); all G query rows of the position reuse the K/V rows (L1-resident on
-// the second and later reads).
+// the second and later reads).  With 128-byte rows (D = 64) a unit is a few KB and the kernels are
+// bound by latency and instruction issue rather than by HBM, so more warps are kept resident there.
 template <typename T, int D>
-__global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(256, D == 64 ? 3 : 2) fwd_kernel(const __grid_constant__ Params p) {
   constexpr int CH = D / 64;
   const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
   const int64_t n_units = (int64_t)p.B * p.T_kv * p.H;
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(256, 2) fwd_kernel(const __grid_constant__ Par
 // ------------------------------------------------------------------------- backward
 // One warp per (b, t, h), G query rows held in registers (G is a template parameter).
 template <typename T, int D, int G>
-__global__ void __launch_bounds__(128, (G == 1) ? 3 : 2) bwd_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__(128, (G == 1) ? (D == 64 ? 5 : 3) : 2) bwd_kernel(const __grid_constant__ Params p) {
   constexpr int CH = D / 64;
   const int lane = threadIdx.x & 31, sub = lane & 7, grp = lane >> 3;
   const int64_t n_units = (int64_t)p.B * p.T_kv * p.H;

@@ -21,8 +21,8 @@
 //   warps 0-3 / 4-7  softmax of query tile 0 / 1, lazy O rescale, epilogue.
 //
 // TMEM (512 columns): S_0 [0,128), S_1 [128,256), O_0 [256,256+D), O_1 [384,384+D).  A softmax warp
-// hands P over in two parts (columns [0,48) and [48,64) of the packed block), so most of PV runs
-// under the last exponentials.  Every wait is bounded, as in the other tcgen05 kernels.
+// hands P over in two halves (columns [0,32) and [32,64) of the packed block), so the first half of PV
+// runs under the last exponentials.  Every wait is bounded, as in the other tcgen05 kernels.
 #pragma once
 #include "tc_bwd_kernels.cuh"
 
@@ -33,11 +33,15 @@ constexpr int kF3Threads = 384;          // 8 softmax warps + MMA warp + TMA war
 // Registers per thread: the CTA starts with 168 (65536 / 384, rounded down to a multiple of 8); after
 // the set-up the last warpgroup (MMA, TMA) gives registers back and the softmax warpgroups take
 // them, so that a softmax thread holds its 128 scores, the packed P and the partial sums without spills.
-constexpr uint32_t kF3SoftmaxRegs = 216, kF3IssueRegs = 72;
+constexpr uint32_t kF3SoftmaxRegs = 232, kF3IssueRegs = 40;
 static_assert(2 * 128 * kF3SoftmaxRegs + 128 * kF3IssueRegs <= 384 * 168, "register pool of the CTA exceeded");
-// barriers: q, full[2], empty[2], s[2], p[2] (first kF3PSplit pairs of P stored), done, pl[2] (the rest)
-struct F3Bars { static constexpr int q = 0, full0 = 1, empty0 = 3, s0 = 5, p0 = 7, done = 9, pl0 = 10, count = 12; };
-constexpr int kF3PSplit = 48;   // 16-bit pairs (= TMEM columns) of P handed to the PV matmul ahead of the last 16
+// P reaches the PV matmul in kF3Parts parts: part i = packed columns [kF3Bound[i], kF3Bound[i+1]) of
+// the 64 (multiples of 16: a tcgen05.st of 16 columns, two K = 16 slices of the matmul).
+constexpr int kF3Parts = 2;
+__device__ constexpr int kF3Bound[5] = {0, 32, 64, 64, 64};
+static_assert(kF3Parts >= 1 && kF3Parts <= 4, "one to four parts");
+// barriers: q, full[2], empty[2], s[2], done, p[part][2] (part of P stored)
+struct F3Bars { static constexpr int q = 0, full0 = 1, empty0 = 3, s0 = 5, done = 7, p0 = 8, count = 8 + 2 * kF3Parts; };
 static_assert(F3Bars::count <= kMaxBars, "control block too small");
 template <int D> __host__ __device__ constexpr uint32_t f3_smem() { return 6 * tile_bytes<D>() + kCtlBytes; }   // Q_0, Q_1, two {K, V} slots
 
@@ -73,6 +77,35 @@ __device__ __forceinline__ void f3_step(const F3Plan& pl, int s, int& part, bool
   part = 1 << a;
   is_dep = true;
   row = pl.w[a].dep_c0 + d * kBN;
+}
+
+// 16 columns of pk starting at column j (j is a compile-time constant after unrolling)
+__device__ __forceinline__ void tmem_st16_at(uint32_t taddr, const uint32_t (&pk)[64], int j) {
+  if (j == 0) tmem_st16<0>(taddr, pk);
+  else if (j == 16) tmem_st16<16>(taddr + 16, pk);
+  else if (j == 32) tmem_st16<32>(taddr + 32, pk);
+  else tmem_st16<48>(taddr + 48, pk);
+}
+
+// Part kPart of a row's P (and the parts after it): exponentials, store into TMEM, signal.
+template <typename T, int kPolyEvery, int kPart, typename Ready>
+__device__ __forceinline__ void softmax_part(const float (&sc)[128], float c, float m_used, float2 (&sum2)[4], uint32_t (&pk)[64],
+                                             uint32_t taddr, Ready& p_ready) {
+  if constexpr (kPart < kF3Parts) {
+    constexpr int i0 = kF3Bound[kPart], i1 = kF3Bound[kPart + 1];
+    static_assert(i0 % 16 == 0 && i1 % 16 == 0 && i0 < i1 && i1 <= 64, "parts are multiples of 16 columns");
+    softmax_exps<T, kPolyEvery, i0, i1>(sc, c, m_used, sum2, pk);
+    if constexpr (i0 % 32 == 0 && i1 - i0 >= 32) {
+      tmem_st32<i0>(taddr + i0, pk);
+      if constexpr (i1 - i0 >= 48) tmem_st16<i0 + 32>(taddr + i0 + 32, pk);
+      if constexpr (i1 - i0 == 64) tmem_st16<i0 + 48>(taddr + i0 + 48, pk);
+    } else {
+#pragma unroll
+      for (int j = i0; j < i1; j += 16) tmem_st16_at(taddr, pk, j);
+    }
+    p_ready(F3Bars::p0 + 2 * kPart);
+    softmax_part<T, kPolyEvery, kPart + 1>(sc, c, m_used, sum2, pk, taddr, p_ready);
+  }
 }
 
 template <typename T, int D, int kPolyEvery>
@@ -113,8 +146,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       mbar_init(bars + 8 * (B_::full0 + i), 1);
       mbar_init(bars + 8 * (B_::empty0 + i), 1);
       mbar_init(bars + 8 * (B_::s0 + i), 1);
-      mbar_init(bars + 8 * (B_::p0 + i), 4);      // one arrival per softmax warp
-      mbar_init(bars + 8 * (B_::pl0 + i), 4);
+      for (int j = 0; j < kF3Parts; ++j) mbar_init(bars + 8 * (B_::p0 + 2 * j + i), 4);   // one arrival per softmax warp
     }
     *abort_flag = 0;
     *drain_flag = 0;
@@ -200,27 +232,22 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         return true;
       };
       // O_a += P_a V(s); `last`: no other MMA of step s follows, the slot may be refilled.  The
-      // matmuls over the first kF3PSplit columns of P go out while the softmax still computes the rest.
+      // matmuls over a part of P go out while the softmax still computes the next one.
       auto pv = [&](int a, int s, bool last) -> bool {
-        if (!mbar_wait(bars + 8 * (B_::p0 + a), pv_cnt[a] & 1, abort_flag, B_::p0 + a)) return false;
-        tc_fence_after();
         const uint32_t slot = s & 1;
         const uint32_t sV = sRing + slot * 2 * kTile + kTile, tS = tmem + a * 128, tO = tmem + 256 + a * 128;
-        if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kF3PSplit / 8; ++kk)
-            mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[a] > 0 || kk > 0) ? 1u : 0u);
-        }
-        __syncwarp();
-        if (!mbar_wait(bars + 8 * (B_::pl0 + a), pv_cnt[a] & 1, abort_flag, B_::pl0 + a)) return false;
-        tc_fence_after();
-        if (elect_one()) {
+        for (int part = 0; part < kF3Parts; ++part) {
+          if (!mbar_wait(bars + 8 * (B_::p0 + 2 * part + a), pv_cnt[a] & 1, abort_flag, B_::p0 + 2 * part + a)) return false;
+          tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = kF3PSplit / 8; kk < 8; ++kk)
-            mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv, 1u);
-          if (last) tc_commit(bars + 8 * (B_::empty0 + slot));
+            for (int kk = kF3Bound[part] / 8; kk < kF3Bound[part + 1] / 8; ++kk)
+              mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[a] > 0 || kk > 0) ? 1u : 0u);
+            if (last && part == kF3Parts - 1) tc_commit(bars + 8 * (B_::empty0 + slot));
+          }
+          __syncwarp();
         }
-        __syncwarp();
         ++pv_cnt[a];
         return true;
       };
@@ -296,8 +323,8 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         for (int i = 0; i < 64; ++i) z[i] = 0u;
         tmem_st32<0>(tmem_S + lane_addr + 0, z);
         tmem_st32<32>(tmem_S + lane_addr + 32, z);
-        p_ready(B_::p0);
-        p_ready(B_::pl0);
+#pragma unroll
+        for (int part = 0; part < kF3Parts; ++part) p_ready(B_::p0 + 2 * part);
         ++cnt;
         continue;
       }
@@ -330,13 +357,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         }
       }
       float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      softmax_exps<T, kPolyEvery, 0, kF3PSplit>(sc, c, m_used, sum2, pk);
-      tmem_st32<0>(tmem_S + lane_addr + 0, pk);
-      tmem_st16<32>(tmem_S + lane_addr + 32, pk);
-      p_ready(B_::p0);
-      softmax_exps<T, kPolyEvery, kF3PSplit, 64>(sc, c, m_used, sum2, pk);
-      tmem_st16<48>(tmem_S + lane_addr + 48, pk);
-      p_ready(B_::pl0);
+      softmax_part<T, kPolyEvery, 0>(sc, c, m_used, sum2, pk, tmem_S + lane_addr, p_ready);
       l += softmax_total(sum2);
       ++cnt;
     }
