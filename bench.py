@@ -108,6 +108,74 @@ def pairs(mode, B, T, Hkv, G, L):
     return B * Hq * (seq + dep)
 
 
+def executed_blocks(mode, B, T, Hkv, G, L):
+    """(sequence, depth) counts of the 128-query-row x 128-key blocks the tcgen05 attention kernels
+    execute, partly masked blocks included: the unit of the tensor-pipe model below."""
+    tq = T * G
+    n_qt = -(-tq // 128)
+    seq = 0
+    if mode == "noncausal":
+        seq = n_qt * -(-T // 128)
+    elif mode in ("causal", "chunk"):
+        for i in range(n_qt):
+            last_pos = (min(128 * (i + 1), tq) - 1) // G
+            seq += -(-(last_pos + 1) // 128)
+    # depth rows in reach of a query tile: the rows of the positions it covers
+    pos_per_tile = -(-128 // G)
+    dep = n_qt * -(-(pos_per_tile * L) // 128) if L > 0 else 0
+    return B * Hkv * seq, B * Hkv * dep
+
+
+# tcgen05.mma instructions (M = 128, K = 16) per executed 128 x 128 block, by kernel, as
+# {shape: count}: scores of the forward are SS N = 128, P V is TS N = D over 128 keys; the backward
+# kernels step by 64 (keys in dq, query rows in dk/dv): scores TS N = 64 from operands resident in
+# TMEM, updates SS N = D over 64 rows of dS / P^T / dS^T in shared memory.
+def mma_mix(kernel, D):
+    kd, upd = D // 16, "ss_n%d" % D
+    if kernel == "tc_fwd":
+        return {"ss_n128": kd, "ts_n%d" % D: 8}
+    if kernel == "tc_dq":
+        return {"ts_n64": 2 * 2 * kd, upd: 2 * 4}
+    if kernel == "tc_dkv":
+        return {"ts_n64": 2 * 2 * kd, upd: 2 * 2 * 4}
+    return None
+
+
+def tensor_pipe_model(M, device, prof, mode, B, T, Hkv, G, D, L, shard_frac, sm_mhz):
+    """Tensor-pipe time each attention kernel's instruction mix needs per block, from instruction
+    rates measured on this GPU (moda_b200.tensor_pipe_rates), beside the clocks per block the
+    kernel took: pipe_busy = the former / the latter."""
+    if D not in (64, 128) or not sm_mhz or not any(k in prof for k in ("tc_fwd", "tc_dq", "tc_dkv")):
+        return None
+    rates = M.tensor_pipe_rates(device)
+    if min(rates.values()) <= 0:
+        return {"clocks_per_mma": rates, "note": "probe wait expired"}
+    n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+    seq_b, dep_b = executed_blocks(mode, B, T, Hkv, G, L)
+    out = {"clocks_per_mma": {k: round(v, 1) for k, v in rates.items()},
+           "nominal_clocks_per_mma": {"n64": 32, "n128": 64, "n256": 128},
+           "blocks_128x128": {"sequence": int(seq_b * shard_frac), "depth": int(dep_b * shard_frac)},
+           "sm_mhz_used": sm_mhz, "kernels": {},
+           "note": "pipe_clocks_per_block = sum over the kernel's tcgen05.mma instructions per 128x128 block of the "
+                   "measured clocks per instruction (one issuing warp; two warps overlap a little better, so dq and "
+                   "dk/dv can read slightly above 1); measured_clocks_per_block = launch time x median SM clock x SMs "
+                   "/ blocks; pipe_busy = their ratio.  nominal_frac = what the same mix would reach of the nominal "
+                   "8192 flop/clock/SM if the pipe were never idle: the ceiling the instruction shapes allow."}
+    for k_ in ("tc_fwd", "tc_dq", "tc_dkv"):
+        if k_ not in prof or prof[k_][1] <= 0:
+            continue
+        cnt, tot_ms = prof[k_]
+        mix = mma_mix(k_, D)
+        blocks = (seq_b + (0 if k_ == "tc_dkv" else dep_b)) * shard_frac
+        pipe = sum(n * rates[sh] for sh, n in mix.items())
+        nominal = sum(n * int(sh.split("_n")[1]) / 2 for sh, n in mix.items())
+        meas = tot_ms / cnt * 1e-3 * sm_mhz * 1e6 * n_sm / blocks
+        out["kernels"][k_] = {"mma_per_block": mix, "pipe_clocks_per_block": round(pipe, 1),
+                              "measured_clocks_per_block": round(meas, 1), "pipe_busy": round(pipe / meas, 3),
+                              "nominal_frac_of_mix": round(nominal / pipe, 3)}
+    return out
+
+
 def flops(mode, B, T, Hkv, G, D, L, fwd=True, bwd=True):
     p = pairs(mode, B, T, Hkv, G, L)
     return (4 * D * p if fwd else 0) + (10 * D * p if bwd else 0)
@@ -615,6 +683,7 @@ def main():
     ap.add_argument("--no-other-workloads", action="store_true", help="skip the secondary workloads (configs 2, 3, 5, published shape)")
     ap.add_argument("--no-triton-baseline", action="store_true", help="skip the reference-Triton-kernels leg")
     ap.add_argument("--triton-timeout", type=int, default=420)
+    ap.add_argument("--no-pipe-model", action="store_true", help="skip the tcgen05.mma rate probe and the tensor-pipe model")
     ap.add_argument("--fwd-only", action="store_true", help="time forward only (exploration; not the headline)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
@@ -788,6 +857,8 @@ def main():
                         "traffic_source": NCU_TRAFFIC_SOURCE.get(name) if traffic else None,
                         "peak_source": pk["source"] + " (sustained cuBLAS bf16 at %s MHz)" % pk.get("peak_sm_mhz"),
                         "avg_launch_ms": avg_ms, "step": step_block, "kernels": kernels}
+            if world == 1 and not args.no_pipe_model:
+                roofline["tensor_pipe"] = tensor_pipe_model(M, device, prof, mode, B, T, Hkv, G, D, L, shard_frac, sm_mhz)
 
     # ---- depth-KV overhead: the same kernels on the same q, k, v, dO with L = 0 ---------------
     # (t_MoDA - t_seq_only) / t_MoDA, forward only and forward+backward, the two timed back to back

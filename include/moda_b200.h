@@ -235,6 +235,18 @@ const char *moda_b200_kernel_name(int kernel_id);
  */
 int moda_b200_device_status(int *status);
 
+/*
+ * Measurement aid (no reference counterpart): clocks per tcgen05.mma instruction (kind::f16, bf16,
+ * M = 128, K = 16; issue of 64 back-to-back instructions to completion, one CTA) for the six
+ * shapes the attention kernels are built from, written to clocks_per_mma[6] (DEVICE memory) in the
+ * order SS N=64, SS N=128, SS N=256, TS N=64, TS N=128, TS N=256 (SS: A and B operands in shared
+ * memory; TS: A in TMEM).  The nominal rate would be N/2 clocks.  bench.py turns these into the
+ * tensor-pipe time a kernel's instruction mix needs per tile, which is the ceiling its measured
+ * time is compared with.  A value of -1 means the bounded wait of the probe expired.  Asynchronous
+ * on `stream`.
+ */
+int moda_b200_tensor_pipe_rates(int device, float *clocks_per_mma, void *stream);
+
 /* Number of kernel launches the last successful call on this host thread issued. */
 int moda_b200_last_launch_count(void);
 

@@ -18,6 +18,7 @@ from .ops import (  # noqa: F401
     parallel_moda_chunk_visible_fwd,
     parallel_moda_fwd,
     set_kernel_path,
+    tensor_pipe_rates,
 )
 from .depth_cache import DepthKVCache  # noqa: F401
 from ._cabi import (  # noqa: F401
@@ -31,5 +32,5 @@ __all__ = [
     "parallel_moda", "parallel_moda_fwd", "parallel_moda_bwd",
     "parallel_moda_chunk_visible", "parallel_moda_chunk_visible_fwd", "parallel_moda_chunk_visible_bwd",
     "parallel_fda", "parallel_fda_fwd", "parallel_fda_bwd",
-    "moda_attention", "fold_qkv", "DepthKVCache", "set_kernel_path", "last_launch_count", "device_status",
+    "moda_attention", "fold_qkv", "DepthKVCache", "set_kernel_path", "last_launch_count", "device_status", "tensor_pipe_rates",
 ]

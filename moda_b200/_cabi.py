@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "moda_b200_profile_end",
     "moda_b200_kernel_name",
     "moda_b200_device_status",
+    "moda_b200_tensor_pipe_rates",
     "moda_b200_last_launch_count",
     "moda_b200_last_cuda_error",
     "moda_b200_status_string",
@@ -112,6 +113,8 @@ def load() -> ctypes.CDLL:
     lib.moda_b200_kernel_name.restype = ctypes.c_char_p
     lib.moda_b200_device_status.argtypes = [IP]
     lib.moda_b200_device_status.restype = ctypes.c_int
+    lib.moda_b200_tensor_pipe_rates.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    lib.moda_b200_tensor_pipe_rates.restype = ctypes.c_int
     lib.moda_b200_last_launch_count.restype = ctypes.c_int
     lib.moda_b200_last_cuda_error.restype = ctypes.c_int
     lib.moda_b200_status_string.argtypes = [ctypes.c_int]
@@ -146,6 +149,16 @@ def profile_end() -> dict:
     ms = (ctypes.c_float * 16)()
     check(lib.moda_b200_profile_end(16, ctypes.byref(n), ids, cnt, ms), "moda_b200_profile_end")
     return {lib.moda_b200_kernel_name(ids[i]).decode(): (int(cnt[i]), float(ms[i])) for i in range(n.value)}
+
+
+TENSOR_PIPE_SHAPES = ("ss_n64", "ss_n128", "ss_n256", "ts_n64", "ts_n128", "ts_n256")
+
+
+def tensor_pipe_rates(device_ptr: int, device: int, stream: int = 0) -> None:
+    """Enqueue the tcgen05.mma rate probe: six floats (clocks per instruction, in the order of
+    ``TENSOR_PIPE_SHAPES``) are written to the DEVICE buffer at ``device_ptr``."""
+    check(load().moda_b200_tensor_pipe_rates(int(device), ctypes.c_void_p(device_ptr), ctypes.c_void_p(stream)),
+          "moda_b200_tensor_pipe_rates")
 
 
 def device_status() -> int:

@@ -15,6 +15,7 @@
 #include "tc_bwd_kernels.cuh"
 #include "tc_fwd3_kernel.cuh"
 #include "tc_bwd_launch.cuh"
+#include "mma_rate_probe.cuh"
 #endif
 
 namespace {
@@ -533,6 +534,17 @@ int moda_b200_bwd_static_scratch(const moda_problem* prob, const moda_tensor4* q
   if (int rc = static_scratch_address(prob->device, &scratch)) return rc;
   return moda_b200_bwd(prob, q, k, v, depth_k, depth_v, o, lse, dout, dq, dk, dv, d_depth_k, d_depth_v,
                        scratch, (size_t)MODA_B200_STATIC_SCRATCH_BYTES, stream);
+}
+
+int moda_b200_tensor_pipe_rates(int device, float* clocks_per_mma, void* stream) {
+  if (!clocks_per_mma) return MODA_ERR_NULL;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(guard.err);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  MODA_CUDA(tc::clear_launch_status(st));
+  MODA_CUDA(tc::mma_rates(clocks_per_mma, st));
+  g_last_launches = 12;
+  return MODA_OK;
 }
 
 int moda_b200_last_launch_count(void) { return g_last_launches; }

@@ -163,6 +163,19 @@ def last_launch_count() -> int:
     return int(_cabi.load().moda_b200_last_launch_count())
 
 
+def tensor_pipe_rates(device=None) -> dict:
+    """Measured clocks per ``tcgen05.mma`` instruction (M = 128, K = 16, bf16) for the shapes the
+    attention kernels use: ``{"ss_n64": .., "ss_n128": .., "ss_n256": .., "ts_n64": .., "ts_n128": ..,
+    "ts_n256": ..}`` (SS: both operands in shared memory, TS: A in TMEM; nominal would be N/2).
+    Measurement aid with no reference counterpart; synchronises the current stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    out = torch.zeros(6, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.tensor_pipe_rates(out.data_ptr(), dev.index or 0, torch.cuda.current_stream().cuda_stream)
+        vals = out.cpu().tolist()
+    return dict(zip(_cabi.TENSOR_PIPE_SHAPES, vals))
+
+
 # --------------------------------------------------------------------------- autograd
 class _ModaFunction(torch.autograd.Function):
     """Autograd glue (reference: moda_v14.py:2649-2789, moda_v16.py:3320-3493,

@@ -441,3 +441,20 @@ def test_randomised_shapes(M, mode, B, T, H, L, G, dt, D, path, seed):
              "two_tiles": M.PATH_TCGEN05_TWO_TILES, "fused_bwd": M.PATH_TCGEN05_FUSED_BWD}
     _run_case(M, mode, B, T, H, D, L, G, DT[dt], None, seed=seed, path=paths[path])
     assert _cabi.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_tensor_pipe_rate_probe(M):
+    """The measurement aid returns one finite rate per instruction shape, no faster than the
+    nominal N/2 clocks and ordered as the shapes are (larger N and an A operand in shared memory
+    cost more), and leaves the status word clean."""
+    r = M.tensor_pipe_rates()
+    assert set(r) == {"ss_n64", "ss_n128", "ss_n256", "ts_n64", "ts_n128", "ts_n256"}
+    for name, v in r.items():
+        n = int(name.split("_n")[1])
+        assert n / 2 * 0.95 <= v < 4 * n, (name, v)
+    assert r["ts_n64"] < r["ts_n128"] < r["ts_n256"]
+    assert r["ss_n64"] < r["ss_n128"] < r["ss_n256"]
+    for n in (64, 128, 256):
+        assert r[f"ts_n{n}"] < r[f"ss_n{n}"]
+    assert M.device_status() == 0
