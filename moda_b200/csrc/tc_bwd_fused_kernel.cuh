@@ -137,7 +137,7 @@ __global__ void __launch_bounds__(256) scale_kernel(const float* delta_t, const 
 // =========================================================================== fused backward
 // grid (ceil(T_kv/128), H, B), 352 threads.
 template <typename T>
-__global__ void __launch_bounds__(kDkvThreads, 1)
+__global__ void __launch_bounds__(kFusedBwdThreads, 1)
 bwd_fused_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
                  const float* lse_t, const float4* scale_blk, int* dq_acc, int T_qp) {
   constexpr int D = 128;

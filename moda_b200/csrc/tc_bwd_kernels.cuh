@@ -37,8 +37,13 @@ constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delt
 constexpr uint32_t kStepHalf = 64 * 64 * 2;    // one TMA box of a step tile: [64 rows x 64 elements]
 template <int D> __host__ __device__ constexpr uint32_t step_tile() { return (uint32_t)(D / 64) * kStepHalf; }   // [64 x D] 16-bit tile
 constexpr uint32_t kScoreTile = 128 * 64 * 2;  // [128 x 64] 16-bit tile of dS, P^T or dS^T (K-major, 128 B per row)
-constexpr int kDqThreads = 352;                // 8 softmax warps + score-MMA, TMA and update-MMA warps
+// 8 softmax warps + S-MMA (8), TMA (9), update-MMA (10) and dP-MMA (11) warps.  The two score matmuls
+// of a step have an issuing warp each: a tcgen05.mma occupies its issuing warp for some 30 clocks
+// (60 with two shared-memory descriptors), as long as an N = 64 instruction takes to execute, so one
+// warp issuing both could not run ahead of the tensor pipe.
+constexpr int kDqThreads = 384;
 constexpr int kDkvThreads = kDqThreads;
+constexpr int kFusedBwdThreads = 352;          // the fused kernel keeps one score-MMA warp
 
 struct DqMaps { CUtensorMap k, v, kd, vd; };               // 64-row boxes
 struct DkvMaps { CUtensorMap k, v, kd, vd, q, dout; };     // k, v, kd, vd: 128-row boxes; q, dout 64-row
@@ -134,7 +139,7 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t block_s
 __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { return d + (uint64_t)(byte_off >> 4); }
 
 // ============================================================================ dq
-// grid (ceil(T_q/128), H, B), 352 threads.  TMEM (512 columns):
+// grid (ceil(T_q/128), H, B), 384 threads.  TMEM (512 columns):
 //   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32);
 //   [256, 256+D) dQ (fp32);  [384, 384+D/2) Q (16-bit A operand);  [448, 448+D/2) dO (16-bit A operand).
 // Shared memory: ring of kDqRing x {K step tile, V step tile} ([64 x D] each), then two
@@ -147,6 +152,9 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
           const float* lse_t, int T_qp, const int* dq_acc, const float4* scale_blk) {
   constexpr int R = kDqRing;
   constexpr BwdBars B_(R);
+  // two issuing warps for the score matmuls at D = 128 (8 instructions each per step); at D = 64 a
+  // step has 4 + 4 and one warp issues them faster than two warps take turns on the barriers
+  constexpr bool kSplitScores = D == 128;
   constexpr uint32_t kStepTile = step_tile<D>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
@@ -197,7 +205,8 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
     mbar_init(bars + 8 * B_.done, 1);
     for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128);
+      mbar_init(bars + 8 * (B_.s0 + i), kSplitScores ? 2 : 1);    // one commit per score-MMA warp
+      mbar_init(bars + 8 * (B_.p0 + i), 128);
       mbar_init(bars + 8 * (B_.r0 + i), 128); mbar_init(bars + 8 * (B_.t0 + i), 1);
     }
     *abort_flag = 0;
@@ -248,11 +257,13 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
           mbar_wait(bars + 8 * (B_.full0 + i % R), (i / R) & 1, drain_flag, B_.full0 + i % R);
       }
     }
-  } else if (warp == 8) {
-    // ---------------------------------------------------------------- score-MMA warp
-    // S(i) = Q K(i)^T and dP(i) = dO V(i)^T into TMEM stage i&1, as soon as the warpgroup that
-    // owned the stage has the previous scores in registers and the step tiles have landed.
-    if (n > 0) {
+  } else if (warp == 8 || warp == 11) {
+    // ---------------------------------------------------------------- score-MMA warps
+    // S(i) = Q K(i)^T (warp 8) and dP(i) = dO V(i)^T (warp 11, or warp 8 as well when the scores
+    // are not split) into TMEM stage i&1, as soon as the warpgroup that owned the stage has the
+    // previous scores in registers and the step tiles have landed.
+    const bool is_s = warp == 8;
+    if (n > 0 && (is_s || kSplitScores)) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
       bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // Q, dO are in TMEM
       tc_fence_after();
@@ -264,13 +275,26 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const uint32_t sK = sRing + slot * 2 * kStepTile;
         const uint64_t dk = desc_kmajor(sK), dv = desc_kmajor(sK + kStepTile);
         const uint32_t tS = tmem + (i & 1) * 128, tP = tS + 64;
-        if (elect_one()) {
+        // (each form is a straight run of instructions: a branch per matmul would cost more issue
+        // time than the matmul)
+        if (!kSplitScores) {
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            mma_ts(tS, tmem_Q + kk * 8, desc_add(dk, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-            mma_ts(tP, tmem_dO + kk * 8, desc_add(dv, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            for (int kk = 0; kk < D / 16; ++kk) {
+              mma_ts(tS, tmem_Q + kk * 8, desc_add(dk, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+              mma_ts(tP, tmem_dO + kk * 8, desc_add(dv, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            }
+            tc_commit(bars + 8 * (B_.s0 + (i & 1)));
           }
-          tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+        } else {
+          const uint32_t tAcc = is_s ? tS : tP, tA = is_s ? tmem_Q : tmem_dO;
+          const uint64_t db = is_s ? dk : dv;
+          if (elect_one()) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk)
+              mma_ts(tAcc, tA + kk * 8, desc_add(db, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
+            tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+          }
         }
         __syncwarp();
       }
@@ -429,7 +453,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 }
 
 // =========================================================================== dk / dv
-// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 352 threads; key tiles of 128.
+// grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 384 threads; key tiles of 128.
 // TMEM (512 columns): [0, 64) S^T and [64, 128) dP^T (one fp32 score stage);
 //   [128, 128+D) dV; [256, 256+D) dK; [384, 384+D/2) K and [448, 448+D/2) V rows as 16-bit A operands.
 // Shared memory: ring of kDkvRing x {Q step tile, dO step tile}; two {P^T, dS^T} tile pairs
@@ -492,7 +516,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     mbar_init(bars + 8 * B_.done, 1);
     for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 8 * (B_.s0 + i), 1); mbar_init(bars + 8 * (B_.p0 + i), 128);
+      mbar_init(bars + 8 * (B_.s0 + i), 2);    // one commit per score-MMA warp
+      mbar_init(bars + 8 * (B_.p0 + i), 128);
       mbar_init(bars + 8 * (B_.r0 + i), 128); mbar_init(bars + 8 * (B_.t0 + i), 1);
     }
     *abort_flag = 0;
@@ -540,10 +565,11 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
           mbar_wait(bars + 8 * (B_.full0 + i % R), (i / R) & 1, drain_flag, B_.full0 + i % R);
       }
     }
-  } else if (warp == 8) {
-    // ---------------------------------------------------------------- score-MMA warp
-    // S^T(i) = K Q(i)^T and dP^T(i) = V dO(i)^T (A from TMEM) into the score stage, as soon as
-    // the previous step's scores have been read into registers and the step tiles have landed.
+  } else if (warp == 8 || warp == 11) {
+    // ---------------------------------------------------------------- score-MMA warps
+    // S^T(i) = K Q(i)^T (warp 8) and dP^T(i) = V dO(i)^T (warp 11), A from TMEM, into the score stage,
+    // as soon as the previous step's scores have been read into registers and the step tiles have landed.
+    const bool is_s = warp == 8;
     if (n > 0) {
       constexpr uint32_t idesc_s = instr_desc(fmt, 64, false);
       bool ok = mbar_wait(bars + 8 * B_.res, 0, abort_flag, B_.res);   // K, V are in TMEM
@@ -554,13 +580,12 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         if (!(ok = mbar_wait(bars + 8 * (B_.full0 + slot), (i / R) & 1, abort_flag, B_.full0 + slot))) break;
         tc_fence_after();
         const uint32_t sQ = sRing + slot * 2 * kStepTile;
-        const uint64_t dq = desc_kmajor(sQ), ddo = desc_kmajor(sQ + kStepTile);
+        const uint64_t db = desc_kmajor(is_s ? sQ : sQ + kStepTile);
+        const uint32_t tAcc = is_s ? tmem_S : tmem_P, tA = is_s ? tmem_K : tmem_V;
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            mma_ts(tmem_S, tmem_K + kk * 8, desc_add(dq, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-            mma_ts(tmem_P, tmem_V + kk * 8, desc_add(ddo, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
-          }
+          for (int kk = 0; kk < D / 16; ++kk)
+            mma_ts(tAcc, tA + kk * 8, desc_add(db, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           tc_commit(bars + 8 * (B_.s0 + (i & 1)));
         }
         __syncwarp();

@@ -94,7 +94,7 @@ inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, const BwdBuffer
         if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFuSmem)) != cudaSuccess) return e;
         dim3 grid(n_seq, p.H, p.B);
         prof::Scope ps(prof::kBwdFusedTc, st);
-        kern<<<grid, kDkvThreads, kFuSmem, st>>>(p, m.dkv, delta_t, lse_t, w.scale_blk, w.dq_acc, T_qp);
+        kern<<<grid, kFusedBwdThreads, kFuSmem, st>>>(p, m.dkv, delta_t, lse_t, w.scale_blk, w.dq_acc, T_qp);
       }
       if ((e = cudaGetLastError()) != cudaSuccess) return e;
       *launches += 1;
