@@ -218,12 +218,13 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         const uint32_t slot = s & 1;
         if (!mbar_wait(bars + 8 * (B_::full0 + slot), (s >> 1) & 1, abort_flag, B_::full0 + slot)) return false;
         tc_fence_after();
-        const uint32_t sK = sRing + slot * 2 * kTile, sQa = sQ + a * kTile, tS = tmem + a * 128;
+        const uint64_t dK = desc_kmajor(sRing + slot * 2 * kTile), dQa = desc_kmajor(sQ + a * kTile);
+        const uint32_t tS = tmem + a * 128;
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
-            mma_ss(tS, smem_desc_sw128(sQa + off, 16, 1024), smem_desc_sw128(sK + off, 16, 1024), idesc_qk, kk > 0);
+            mma_ss(tS, desc_add(dQa, off), desc_add(dK, off), idesc_qk, kk > 0);
           }
           tc_commit(bars + 8 * (B_::s0 + a));
         }
@@ -235,7 +236,8 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       // matmuls over a part of P go out while the softmax still computes the next one.
       auto pv = [&](int a, int s, bool last) -> bool {
         const uint32_t slot = s & 1;
-        const uint32_t sV = sRing + slot * 2 * kTile + kTile, tS = tmem + a * 128, tO = tmem + 256 + a * 128;
+        const uint64_t dV = desc_mnmajor(sRing + slot * 2 * kTile + kTile, kHalfBytes);
+        const uint32_t tS = tmem + a * 128, tO = tmem + 256 + a * 128;
 #pragma unroll
         for (int part = 0; part < kF3Parts; ++part) {
           if (!mbar_wait(bars + 8 * (B_::p0 + 2 * part + a), pv_cnt[a] & 1, abort_flag, B_::p0 + 2 * part + a)) return false;
@@ -243,7 +245,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
           if (elect_one()) {
 #pragma unroll
             for (int kk = kF3Bound[part] / 8; kk < kF3Bound[part + 1] / 8; ++kk)
-              mma_ts(tO, tS + kk * 8, smem_desc_sw128(sV + kk * 2048, kHalfBytes, 1024), idesc_pv, (pv_cnt[a] > 0 || kk > 0) ? 1u : 0u);
+              mma_ts(tO, tS + kk * 8, desc_add(dV, kk * 2048), idesc_pv, (pv_cnt[a] > 0 || kk > 0) ? 1u : 0u);
             if (last && part == kF3Parts - 1) tc_commit(bars + 8 * (B_::empty0 + slot));
           }
           __syncwarp();
@@ -257,7 +259,53 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         for (int a = 0; ok && a < 2; ++a)
           if (part & (1 << a)) ok = qk(a, 0);
       }
-      for (int s = 0; ok && s < pl.n; ++s) {
+      // Steady state: steps that both tiles take part in and whose successor is such a step too
+      // (all but the last sequence steps).  The same order as the general loop below, PV_0(s),
+      // QK_0(s+1), PV_1(s), QK_1(s+1), as straight runs of instructions: the time this warp spends
+      // between two matmuls is time the tensor pipe waits.
+      int s = 0;
+      const int n_both = min(pl.w[0].n_seq, pl.w[1].n_seq);
+      if (ok && n_both > 1) {
+        const uint64_t dQ[2] = {desc_kmajor(sQ), desc_kmajor(sQ + kTile)};
+        for (; ok && s + 1 < n_both; ++s) {
+          const uint32_t slot = s & 1, par = s & 1;       // both tiles have taken part in s steps so far
+          const uint64_t dV = desc_mnmajor(sRing + slot * 2 * kTile + kTile, kHalfBytes);
+          const uint64_t dKn = desc_kmajor(sRing + (slot ^ 1) * 2 * kTile);
+          const uint32_t acc = s > 0 ? 1u : 0u;
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            const uint32_t tS = tmem + a * 128, tO = tmem + 256 + a * 128;
+#pragma unroll
+            for (int part_i = 0; part_i < kF3Parts; ++part_i) {
+              if (!(ok = mbar_wait(bars + 8 * (B_::p0 + 2 * part_i + a), par, abort_flag, B_::p0 + 2 * part_i + a))) break;
+              tc_fence_after();
+              if (elect_one()) {
+#pragma unroll
+                for (int kk = kF3Bound[part_i] / 8; kk < kF3Bound[part_i + 1] / 8; ++kk)
+                  mma_ts(tO, tS + kk * 8, desc_add(dV, kk * 2048), idesc_pv, kk > 0 ? 1u : acc);
+                if (a == 1 && part_i == kF3Parts - 1) tc_commit(bars + 8 * (B_::empty0 + slot));
+              }
+              __syncwarp();
+            }
+            if (!ok) break;
+            // K(s+1): one wait serves both tiles
+            if (a == 0 && !(ok = mbar_wait(bars + 8 * (B_::full0 + (slot ^ 1)), ((s + 1) >> 1) & 1, abort_flag, B_::full0 + (slot ^ 1)))) break;
+            tc_fence_after();
+            if (elect_one()) {
+#pragma unroll
+              for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3) * 32;
+                mma_ss(tS, desc_add(dQ[a], off), desc_add(dKn, off), idesc_qk, kk > 0);
+              }
+              tc_commit(bars + 8 * (B_::s0 + a));
+            }
+            __syncwarp();
+          }
+        }
+        qk_cnt[0] = qk_cnt[1] = s + 1;
+        pv_cnt[0] = pv_cnt[1] = s;
+      }
+      for (; ok && s < pl.n; ++s) {
         f3_step(pl, s, part, dep, row);
         part_next = 0;
         if (s + 1 < pl.n) f3_step(pl, s + 1, part_next, dep, row);
