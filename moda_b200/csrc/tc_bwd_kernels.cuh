@@ -379,9 +379,15 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: stage is free
       // straight-line passes over the 64 columns (no branches inside, so the scheduler can
       // overlap the exp2 latency of one column with the arithmetic of the others)
+      // (packed fp32 pairs: the warps are bound by instruction issue, not by the exp2 unit)
       float pr[64];
+      const float2 c2 = make_float2(c, c), nl2 = make_float2(-lse_r, -lse_r), nd2 = make_float2(-dl_r, -dl_r);
 #pragma unroll
-      for (int jj = 0; jj < 64; ++jj) pr[jj] = fast_exp2(fmaf(__uint_as_float(su[jj]), c, -lse_r));
+      for (int jj = 0; jj < 32; ++jj) {
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(su[2 * jj]), __uint_as_float(su[2 * jj + 1])), c2, nl2);
+        pr[2 * jj] = fast_exp2(x.x);
+        pr[2 * jj + 1] = fast_exp2(x.y);
+      }
       if (masked) {
 #pragma unroll
         for (int jj = 0; jj < 64; ++jj) {
@@ -391,9 +397,11 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
       }
       uint32_t pk[32];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj)
-        pk[jj] = Pack<T>::pack(pr[2 * jj] * (__uint_as_float(du[2 * jj]) - dl_r),
-                               pr[2 * jj + 1] * (__uint_as_float(du[2 * jj + 1]) - dl_r));
+      for (int jj = 0; jj < 32; ++jj) {
+        const float2 d = __fadd2_rn(make_float2(__uint_as_float(du[2 * jj]), __uint_as_float(du[2 * jj + 1])), nd2);
+        const float2 ds = __fmul2_rn(make_float2(pr[2 * jj], pr[2 * jj + 1]), d);
+        pk[jj] = Pack<T>::pack(ds.x, ds.y);
+      }
       if (i >= 2) {   // the update of step i-2 must have finished reading this dS tile
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
         if (!ok) break;
@@ -677,18 +685,21 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bars + 8 * (B_.r0 + (i & 1)));      // scores are in registers: the stage is free
+      // (packed fp32 pairs: the warps are bound by instruction issue, not by the exp2 unit)
       float pr[64], dd[64];
+      const float2 c2 = make_float2(c, c);
 #pragma unroll
       for (int j4 = 0; j4 < 16; ++j4) {
         const float4 l4 = st4[j4], d4 = st4[16 + j4];
-        pr[4 * j4 + 0] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 0]), c, -l4.x));
-        pr[4 * j4 + 1] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 1]), c, -l4.y));
-        pr[4 * j4 + 2] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 2]), c, -l4.z));
-        pr[4 * j4 + 3] = fast_exp2(fmaf(__uint_as_float(su[4 * j4 + 3]), c, -l4.w));
-        dd[4 * j4 + 0] = __uint_as_float(du[4 * j4 + 0]) - d4.x;
-        dd[4 * j4 + 1] = __uint_as_float(du[4 * j4 + 1]) - d4.y;
-        dd[4 * j4 + 2] = __uint_as_float(du[4 * j4 + 2]) - d4.z;
-        dd[4 * j4 + 3] = __uint_as_float(du[4 * j4 + 3]) - d4.w;
+        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(su[4 * j4 + 0]), __uint_as_float(su[4 * j4 + 1])), c2, make_float2(-l4.x, -l4.y));
+        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(su[4 * j4 + 2]), __uint_as_float(su[4 * j4 + 3])), c2, make_float2(-l4.z, -l4.w));
+        pr[4 * j4 + 0] = fast_exp2(x0.x);
+        pr[4 * j4 + 1] = fast_exp2(x0.y);
+        pr[4 * j4 + 2] = fast_exp2(x1.x);
+        pr[4 * j4 + 3] = fast_exp2(x1.y);
+        const float2 e0 = __fadd2_rn(make_float2(__uint_as_float(du[4 * j4 + 0]), __uint_as_float(du[4 * j4 + 1])), make_float2(-d4.x, -d4.y));
+        const float2 e1 = __fadd2_rn(make_float2(__uint_as_float(du[4 * j4 + 2]), __uint_as_float(du[4 * j4 + 3])), make_float2(-d4.z, -d4.w));
+        dd[4 * j4 + 0] = e0.x; dd[4 * j4 + 1] = e0.y; dd[4 * j4 + 2] = e1.x; dd[4 * j4 + 3] = e1.y;
       }
       if (masked) {
 #pragma unroll
@@ -701,7 +712,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) {
         pp[jj] = Pack<T>::pack(pr[2 * jj], pr[2 * jj + 1]);
-        pd[jj] = Pack<T>::pack(pr[2 * jj] * dd[2 * jj], pr[2 * jj + 1] * dd[2 * jj + 1]);
+        const float2 ds = __fmul2_rn(make_float2(pr[2 * jj], pr[2 * jj + 1]), make_float2(dd[2 * jj], dd[2 * jj + 1]));
+        pd[jj] = Pack<T>::pack(ds.x, ds.y);
       }
       if (i >= 2) {   // the update of step i-2 must have finished reading this warpgroup's tile pair
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
