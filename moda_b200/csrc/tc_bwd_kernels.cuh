@@ -32,8 +32,13 @@ namespace moda {
 namespace tc {
 
 constexpr int kStep = 64;                      // keys (dq) or query rows (dkv) per pipeline step
-constexpr int kDqRing = 6;                     // dq: ring of {K, V} step tiles
-constexpr int kDkvRing = 5;                    // dkv: ring of {Q, dO, lse, delta} step tiles
+// Ring depths (step tiles in flight).  A slot is refilled only when the update matmul that reads it
+// last has completed, two steps after its scores, and a TMA load of a step's tiles takes longer
+// than a step: five slots are needed (four cost dk/dv a fifth of its speed, three a third at
+// D = 64; more than five gain nothing).  At D = 128 five (dk/dv) and six (dq) are also what fits
+// in shared memory.
+template <int D> __host__ __device__ constexpr int dq_ring() { return 6; }                    // {K, V} step tiles
+template <int D> __host__ __device__ constexpr int dkv_ring() { return D == 128 ? 5 : 6; }    // {Q, dO, lse, delta} step tiles
 constexpr uint32_t kStepHalf = 64 * 64 * 2;    // one TMA box of a step tile: [64 rows x 64 elements]
 template <int D> __host__ __device__ constexpr uint32_t step_tile() { return (uint32_t)(D / 64) * kStepHalf; }   // [64 x D] 16-bit tile
 constexpr uint32_t kScoreTile = 128 * 64 * 2;  // [128 x 64] 16-bit tile of dS, P^T or dS^T (K-major, 128 B per row)
@@ -124,11 +129,25 @@ __global__ void __launch_bounds__(256) pre_kernel(const __grid_constant__ Params
 constexpr int kMaxBars = 24;
 constexpr uint32_t kCtlBytes = 8 * kMaxBars + 32;
 struct BwdBars {          // barrier indices for a ring of R slots
-  int res, full0, empty0, s0, p0, done, r0, t0;
+  int res, full0, empty0, s0, p0, done, r0, t0, i0;   // i0: "the score matmuls of a step have been issued" (dk/dv)
   __host__ __device__ constexpr explicit BwdBars(int R)
-      : res(0), full0(1), empty0(1 + R), s0(1 + 2 * R), p0(3 + 2 * R), done(5 + 2 * R), r0(6 + 2 * R), t0(8 + 2 * R) {}
+      : res(0), full0(1), empty0(1 + R), s0(1 + 2 * R), p0(3 + 2 * R), done(5 + 2 * R), r0(6 + 2 * R), t0(8 + 2 * R),
+        i0(10 + 2 * R) {}
 };
-static_assert(9 + 2 * kDqRing < kMaxBars && 9 + 2 * kDkvRing < kMaxBars, "control block too small");
+// A wait that is only a scheduling hint: a few short tries, then carry on whatever the outcome.
+__device__ __forceinline__ void mbar_wait_hint(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
+  for (int i = 0; i < 6; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(400u) : "memory");
+    if (ok) break;
+  }
+}
+static_assert(9 + 2 * dq_ring<128>() < kMaxBars && 11 + 2 * dkv_ring<64>() < kMaxBars, "control block too small");
 
 // Base of a 128-byte-swizzle descriptor for a tile at `addr`; per-MMA offsets (multiples of
 // 16 bytes, staying inside the tile) are added to the low word.
@@ -142,7 +161,7 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 // grid (ceil(T_q/128), H, B), 384 threads.  TMEM (512 columns):
 //   stage s in {0,1}: [s*128, +64) S (fp32), [s*128+64, +64) dP (fp32);
 //   [256, 256+D) dQ (fp32);  [384, 384+D/2) Q (16-bit A operand);  [448, 448+D/2) dO (16-bit A operand).
-// Shared memory: ring of kDqRing x {K step tile, V step tile} ([64 x D] each), then two
+// Shared memory: ring of dq_ring<D>() x {K step tile, V step tile} ([64 x D] each), then two
 // [128 x 64] dS tiles (K-major, 128-byte swizzle).  A softmax warpgroup releases its TMEM stage
 // as soon as it has the scores in registers, so the next-but-one score MMAs overlap its math;
 // dS reaches the update MMA through shared memory.
@@ -150,7 +169,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kDqThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
           const float* lse_t, int T_qp, const int* dq_acc, const float4* scale_blk) {
-  constexpr int R = kDqRing;
+  constexpr int R = dq_ring<D>();
   constexpr BwdBars B_(R);
   // two issuing warps for the score matmuls at D = 128 (8 instructions each per step); at D = 64 a
   // step has 4 + 4 and one warp issues them faster than two warps take turns on the barriers
@@ -464,7 +483,7 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 // grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 384 threads; key tiles of 128.
 // TMEM (512 columns): [0, 64) S^T and [64, 128) dP^T (one fp32 score stage);
 //   [128, 128+D) dV; [256, 256+D) dK; [384, 384+D/2) K and [448, 448+D/2) V rows as 16-bit A operands.
-// Shared memory: ring of kDkvRing x {Q step tile, dO step tile}; two {P^T, dS^T} tile pairs
+// Shared memory: ring of dkv_ring<D>() x {Q step tile, dO step tile}; two {P^T, dS^T} tile pairs
 // ([128 keys x 64 rows], K-major, 128-byte swizzle), one per softmax warpgroup; the ring of
 // {64 lse, 64 delta}.  A warpgroup releases the score stage as soon as the scores are in its
 // registers, so the next step's score MMAs overlap its math; P^T and dS^T reach the update
@@ -475,7 +494,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps maps, const float* delta_t,
            const float* lse_t, int T_qp, int n_seq_key_tiles) {
-  constexpr int R = kDkvRing;
+  constexpr int R = dkv_ring<D>();
   constexpr BwdBars B_(R);
   constexpr uint32_t kStepTile = step_tile<D>();
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -525,6 +544,7 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
     for (int i = 0; i < R; ++i) { mbar_init(bars + 8 * (B_.full0 + i), 1); mbar_init(bars + 8 * (B_.empty0 + i), 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + 8 * (B_.s0 + i), 2);    // one commit per score-MMA warp
+      mbar_init(bars + 8 * (B_.i0 + i), 2);    // one arrival per score-MMA warp
       mbar_init(bars + 8 * (B_.p0 + i), 128);
       mbar_init(bars + 8 * (B_.r0 + i), 128); mbar_init(bars + 8 * (B_.t0 + i), 1);
     }
@@ -595,6 +615,7 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
           for (int kk = 0; kk < D / 16; ++kk)
             mma_ts(tAcc, tA + kk * 8, desc_add(db, (kk >> 2) * kStepHalf + (kk & 3) * 32), idesc_s, kk > 0);
           tc_commit(bars + 8 * (B_.s0 + (i & 1)));
+          mbar_arrive(bars + 8 * (B_.i0 + (i & 1)));     // issued, not yet executed (see the update warp)
         }
         __syncwarp();
       }
@@ -608,6 +629,11 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
       bool ok = true;
       for (int j = 0; ok && j < n; ++j) {
         if (!(ok = mbar_wait(bars + 8 * (B_.p0 + (j & 1)), (j >> 1) & 1, abort_flag, B_.p0 + (j & 1)))) break;
+        // The tensor pipe executes matmuls in the order they arrive.  The scores of step j+2 become
+        // issuable at about the time these tiles become ready, and they are what the single score
+        // stage - and with it the softmax warps - waits for, while nothing waits for this update:
+        // let the scores go first.  A hint, not a dependency: the wait is short and falls through.
+        if (j + 2 < n) mbar_wait_hint(bars + 8 * (B_.i0 + (j & 1)), ((j + 2) >> 1) & 1);
         tc_fence_after();
         const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
         const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);

@@ -76,8 +76,8 @@ inline cudaError_t launch_bwd(const Params& p, const BwdMaps& m, const BwdBuffer
   }
   if ((e = cudaGetLastError()) != cudaSuccess) return e;
   *launches += 1;
-  const size_t dq_smem = kDqRing * 2 * (size_t)step_tile<D>() + 2 * (size_t)kScoreTile + kCtlBytes;
-  const size_t dkv_smem = kDkvRing * (2 * (size_t)step_tile<D>() + 512) + 2 * (size_t)kDkvPairBytes + kCtlBytes;
+  const size_t dq_smem = dq_ring<D>() * 2 * (size_t)step_tile<D>() + 2 * (size_t)kScoreTile + kCtlBytes;
+  const size_t dkv_smem = dkv_ring<D>() * (2 * (size_t)step_tile<D>() + 512) + 2 * (size_t)kDkvPairBytes + kCtlBytes;
   if (fused) {
     if constexpr (D == 128) {
       {
