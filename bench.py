@@ -931,8 +931,10 @@ def main():
     if not args.no_e2e and not args.fwd_only and len(units) > 0:
         try:
             # One (batch, KV-head) unit at a time, as the operator's callers shard it anyway: the
-            # H2D copy of unit u+1 and the D2H copy of unit u-1 run on their own streams under the
-            # kernels of unit u (two device buffer sets).  Every input byte still crosses PCIe inside
+            # H2D copy of the next unit and the D2H copy of the previous one run on their own streams
+            # under the kernels of the current unit (two device buffer sets), across step boundaries
+            # too - the next step's inputs are on their way while this step's results go back, as
+            # with a prefetching loader.  Every input byte of every step still crosses PCIe inside
             # the timed region, and every output byte crosses back.
             names = ["q", "k", "v", "kd", "vd"]
             n_u = len(units)
@@ -947,16 +949,16 @@ def main():
             in_done = [torch.cuda.Event() for _ in range(2)]
             cmp_done = [torch.cuda.Event() for _ in range(2)]
 
-            def e2e_step():
+            def e2e_steps(n_steps):
                 cur = torch.cuda.current_stream()
                 for st in (s_in, s_cmp, s_out):
                     st.wait_stream(cur)
                 nbytes = 0
-                for u in range(n_u):
-                    k2 = u % 2
+                for g in range(n_steps * n_u):
+                    u, k2 = g % n_u, g % 2
                     with torch.cuda.stream(s_in), torch.no_grad():
-                        if u >= 2:
-                            s_in.wait_event(cmp_done[k2])      # the kernels of unit u-2 have read this set
+                        if g >= 2:
+                            s_in.wait_event(cmp_done[k2])      # the kernels that last read this set have run
                         for n in names + ["dout"]:
                             if dev[k2][n] is not None:
                                 dev[k2][n].copy_(host[u][n], non_blocking=True)
@@ -980,15 +982,14 @@ def main():
                         nbytes += sum(x.numel() * x.element_size() for x in outs)
                 for st in (s_in, s_cmp, s_out):
                     cur.wait_stream(st)
-                return nbytes
+                return nbytes // n_steps
 
-            d2h = e2e_step()
+            d2h = e2e_steps(1)
             barrier()
-            n_e2e = max(1, min(args.steps, 2))
+            n_e2e = max(1, min(args.steps, 3))
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            for _ in range(n_e2e):
-                e2e_step()
+            e2e_steps(n_e2e)
             b.record()
             barrier()
             ems = a.elapsed_time(b)
@@ -1002,7 +1003,7 @@ def main():
                    "ms_per_step": ems / n_e2e,
                    "h2d_gbs_per_rank": h2d / sec / 1e9, "d2h_gbs_per_rank": d2h / sec / 1e9,
                    "note": "per-rank bytes; pinned host buffers; one (batch, KV-head) unit per operator call, "
-                           "copies of neighbouring units on their own streams under the kernels"}
+                           "copies of neighbouring units (of this and the next step) on their own streams under the kernels"}
             # the pipelined results are the whole-tensor results, unit by unit
             if o is not None and res_host[0] is not None:
                 torch.cuda.synchronize()
