@@ -165,3 +165,49 @@ def test_config3_full_size_sampled_positions(built_library):
         check_grad(f"dq ({b},{t},{h})", dq[b, t, h].float().cpu(), rdq[0, 0, 0])
         check_grad(f"d_depth_k ({b},{t},{h})", dkd[b, sl, h].float().cpu(), rdk[0, :, 0])
         check_grad(f"d_depth_v ({b},{t},{h})", dvd[b, sl, h].float().cpu(), rdv[0, :, 0])
+
+
+def test_published_shape_d64_full_length(built_library):
+    """The one shape the reference publishes a kernel time for (README.md:94: T = 65536, G = 8,
+    d = 64, L = 64, causal own-position depth; one of the 8 KV heads) through the D = 64 tcgen05
+    kernels at full length: sampled query rows, depth rows and the last sequence keys against the
+    oracle's single-row forms, causal prefix invariance and run-to-run reproducibility."""
+    import moda_b200 as M
+    from moda_b200 import _cabi
+    dev = torch.device("cuda", 0)
+    Tp_, Gp, Lp, Dp = 65536, 8, 64, 64
+    gen = torch.Generator(device=dev).manual_seed(7)
+    mk = lambda rows: torch.randn(1, rows, 1, Dp, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v, kd, vd, dout = mk(Tp_ * Gp), mk(Tp_), mk(Tp_), mk(Tp_ * Lp), mk(Tp_ * Lp), mk(Tp_ * Gp)
+    scale = Dp ** -0.5
+
+    def run(q, k, v, kd, vd, dout):
+        o, lse = M.parallel_moda_fwd(q, k, v, cached_k=kd, cached_v=vd, moda_group_num=Gp, is_causal=True)
+        dq, dk, dv, _, dkd, dvd = M.parallel_moda_bwd(q, k, v, o, None, lse, dout, cached_k=kd, cached_v=vd,
+                                                      moda_group_num=Gp, is_causal=True)
+        return o, lse, dq, dk, dv, dkd, dvd
+
+    first = run(q, k, v, kd, vd, dout)
+    assert _cabi.device_status() == 0
+    for a, b in zip(first, run(q, k, v, kd, vd, dout)):
+        assert torch.equal(a, b)
+    o, lse, dq, dk, dv, dkd, dvd = first
+    Tc = 2048
+    po, plse, pdq, *_ = run(q[:, :Tc * Gp], k[:, :Tc], v[:, :Tc], kd[:, :Tc * Lp], vd[:, :Tc * Lp], dout[:, :Tc * Gp])
+    assert torch.equal(po, o[:, :Tc * Gp]) and torch.equal(plse, lse[:, :Tc * Gp]) and torch.equal(pdq, dq[:, :Tc * Gp])
+
+    cq, ck, cv, ckd, cvd, cdo = [x.cpu() for x in (q, k, v, kd, vd, dout)]
+    co, clse, cdq, cdk, cdv, cdkd, cdvd = [x.cpu() for x in first]
+    for r in [0, 7, 8, 1023, 1024, 262145, Tp_ * Gp - 257, Tp_ * Gp - 1]:
+        tm = mo.row_terms(cq, ck, cv, ckd, cvd, cdo, 0, 0, r, scale, Gp, mo.MODE_CAUSAL, 1)
+        assert max_abs(co[0, r, 0].float(), tm["o"]) <= TOL_O_MAX_ABS, f"o row {r}"
+        assert abs(clse[0, r, 0].item() - tm["lse"].item()) <= TOL_LSE_MAX_ABS, f"lse row {r}"
+        assert rel_l2(cdq[0, r, 0].float(), tm["dq"]) <= TOL_GRAD_REL_L2, f"dq row {r}"
+    for c in [0, 63, 64, 64 * 1000 + 17, Tp_ * Lp - 1]:
+        rk, rv = mo.depth_row_grads(cq, ck, cv, ckd, cvd, cdo, 0, 0, c, scale, Gp, mo.MODE_CAUSAL, 1)
+        assert rel_l2(cdkd[0, c, 0].float(), rk) <= TOL_GRAD_REL_L2, f"d_depth_k row {c}"
+        assert rel_l2(cdvd[0, c, 0].float(), rv) <= TOL_GRAD_REL_L2, f"d_depth_v row {c}"
+    for j in [Tp_ - 1, Tp_ - 2]:
+        rk, rv = mo.seq_key_grads(cq, ck, cv, ckd, cvd, cdo, 0, 0, j, scale, Gp, mo.MODE_CAUSAL, 1)
+        assert rel_l2(cdk[0, j, 0].float(), rk) <= TOL_GRAD_REL_L2, f"dk key {j}"
+        assert rel_l2(cdv[0, j, 0].float(), rv) <= TOL_GRAD_REL_L2, f"dv key {j}"
