@@ -1,6 +1,6 @@
 """Installs the UNMODIFIED reference package into ``baseline/_ref`` (git-ignored).
 
-    python baseline/install_reference.py [path to a hustvl/MoDA checkout]   (default /root/reference)
+    python baseline/install_reference.py [path to a hustvl/MoDA checkout]   (default: $MODA_REFERENCE_DIR)
 
 The reference's Python package (``libs/moda_triton``: the ``fla`` tree with its Triton kernels) is
 built into a wheel from a temporary copy (the checkout itself may be read-only) and installed with
@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MODA_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
     src = os.path.join(ref, "libs", "moda_triton")
     if not os.path.isdir(os.path.join(src, "fla")):
         raise SystemExit(f"{src} does not hold the reference package")

@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MODA_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
     path = os.path.join(ref, "libs", "moda_triton", "tests", "ops", "test_moda.py")
     tree = ast.parse(open(path).read())
     cases = None
