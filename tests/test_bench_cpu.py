@@ -79,3 +79,25 @@ def test_kernel_attribution_tables_cover_the_same_kernels():
     # the published shape: 14 * d * Hq * (T (T + 1) / 2 + T L) FLOP
     fl = b.flops(*b.WORKLOADS["published_causal_T65536_d64"], fwd=True, bwd=True)
     assert abs(fl - 14 * 64 * 64 * (65536 * 65537 // 2 + 65536 * 64)) < 1
+
+
+def test_tensor_pipe_model_counts():
+    """The block and instruction counts behind roofline.tensor_pipe: config 4 executes one 128 x 128
+    block per (query tile, visible key tile) and eight depth blocks per query tile; the forward
+    issues 8 + 8 matmul instructions per block at D = 128, the backward kernels 32 score
+    instructions plus 8 (dq) or 16 (dk/dv) update instructions."""
+    b = _bench()
+    mode, B, T, Hkv, G, D, L = b.WORKLOADS["config4_chunk_visible_T65536"]
+    seq, dep = b.executed_blocks(mode, B, T, Hkv, G, L)
+    n_qt = T * G // 128
+    assert dep == B * Hkv * n_qt * 8
+    # query tile i covers positions 32 i .. 32 i + 31 and sees ceil((32 i + 32) / 128) key tiles
+    assert seq == B * Hkv * sum(-(-(32 * i + 32) // 128) for i in range(n_qt))
+    # at least the algorithmic pairs, at most one extra (diagonal) tile per query tile
+    alg = b.pairs(mode, B, T, Hkv, G, 0) / (128 * 128)
+    assert alg <= seq <= alg + B * Hkv * n_qt
+    assert b.mma_mix("tc_fwd", 128) == {"ss_n128": 8, "ts_n128": 8}
+    assert b.mma_mix("tc_dq", 128) == {"ts_n64": 32, "ss_n128": 8}
+    assert b.mma_mix("tc_dkv", 128) == {"ts_n64": 32, "ss_n128": 16}
+    assert b.mma_mix("tc_fwd", 64) == {"ss_n128": 4, "ts_n64": 8}
+    assert b.mma_mix("fda_fwd", 128) is None
