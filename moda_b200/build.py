@@ -6,9 +6,9 @@ The library is a plain C-ABI shared object (no torch, no pybind); it is rebuilt 
 any file under ``moda_b200/csrc`` or ``include/`` is newer than the ``.so``.
 
 ``build_wait_test()`` compiles the same sources with ``-DMODA_WAIT_TEST`` into
-``libmoda_b200_waittest.so``: a test-only build in which the one-tile tcgen05 forward
-withholds one barrier arrival and every bounded wait gives up after about a millisecond, so
-that the wait-expiry teardown path can be exercised on a GPU without hanging it.  The
+``libmoda_b200_waittest.so``: a test-only build in which the tcgen05 forwards and the dq /
+dk/dv kernels withhold one barrier arrival and every bounded wait gives up after about a
+millisecond, so that the wait-expiry teardown path can be exercised on a GPU without hanging it.  The
 product never loads that file.
 """
 from __future__ import annotations

@@ -432,7 +432,12 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
           *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#ifndef MODA_WAIT_TEST
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
+#endif
+      // (the wait-expiry test build withholds this arrival: the update warp's bounded wait on the
+      // "tiles ready" barrier, which no TMA load targets, then runs out and the CTA leaves through
+      // the teardown path)
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
     if (ok && (n > 0 || seq_in_acc)) {
@@ -755,7 +760,12 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#ifndef MODA_WAIT_TEST
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
+#endif
+      // (the wait-expiry test build withholds this arrival: the update warp's bounded wait on the
+      // "tiles ready" barrier, which no TMA load targets, then runs out and the CTA leaves through
+      // the teardown path)
     }
     if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * B_.done, 0, abort_flag, B_.done));
     if (ok && n > 0) {

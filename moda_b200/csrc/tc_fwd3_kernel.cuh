@@ -363,6 +363,12 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
+#ifdef MODA_WAIT_TEST
+        // wait-expiry test build: the arrival for the first part of P is withheld, so the MMA warp's
+        // bounded wait on that barrier (which no TMA load targets) runs out and the CTA leaves
+        // through the teardown path
+        if (bar_id == B_::p0) return;
+#endif
         if (lane == 0) mbar_arrive(bars + 8 * (bar_id + a));
       };
       if (none) {
