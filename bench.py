@@ -193,6 +193,47 @@ def peaks():
     return {"tflops": 1400.0, "tflops_burst": 1590.0, "hbm_gbs": 6650.0, "peak_sm_mhz": 1300.0, "source": "fallback"}
 
 
+def nvml_handle(index):
+    """NVML handle of CUDA device `index`.  NVML orders devices by PCI bus id and
+    CUDA_VISIBLE_DEVICES may renumber, so the match is by UUID."""
+    import pynvml as nv
+    nv.nvmlInit()
+    uuid = str(torch.cuda.get_device_properties(index).uuid)
+    for i in range(nv.nvmlDeviceGetCount()):
+        h = nv.nvmlDeviceGetHandleByIndex(i)
+        u = nv.nvmlDeviceGetUUID(h)
+        u = u.decode() if isinstance(u, bytes) else u
+        if uuid in u:
+            return nv, h
+    return nv, nv.nvmlDeviceGetHandleByIndex(index)
+
+
+def bind_host_near_gpu(index):
+    """Keeps this rank's host threads on the CPUs NVML lists as local to its GPU, so that the pinned
+    buffers it allocates afterwards (first touch) land in that GPU's NUMA node and the ranks of one
+    node do not all copy through one socket's memory.  A process-level affinity only; returns what
+    it did, or why it did nothing."""
+    try:
+        nv, handle = nvml_handle(index)
+        allowed = os.sched_getaffinity(0)
+        words = nv.nvmlDeviceGetCpuAffinity(handle, (max(allowed | {os.cpu_count() or 1}) + 64) // 64)
+        local = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus = local & allowed
+        if not cpus:
+            return {"bound": False, "why": "no CPU local to the GPU is available to this process"}
+        if cpus == allowed:
+            return {"bound": False, "why": "every available CPU is local to the GPU", "cpus": len(cpus)}
+        os.sched_setaffinity(0, cpus)
+        info = {"bound": True, "cpus": len(cpus), "of": len(allowed)}
+        try:
+            info["numa_node"] = int(nv.nvmlDeviceGetNumaNodeId(handle))
+        except Exception:
+            pass
+        return info
+    except Exception as exc:      # no NVML, no affinity call: the run goes on unbound
+        return {"bound": False, "why": f"{type(exc).__name__}: {exc}"[:120]}
+
+
 class ClockSampler:
     """Samples SM clocks and clock-event (throttle) reasons during the timed region: NVML in a
     thread of this process (a query every 100 ms; the same counters nvidia-smi prints, without a
@@ -227,20 +268,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            import pynvml as nv
-            nv.nvmlInit()
-            # NVML orders devices by PCI bus id, CUDA_VISIBLE_DEVICES may renumber: match by UUID
-            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
-            handle = None
-            for i in range(nv.nvmlDeviceGetCount()):
-                h = nv.nvmlDeviceGetHandleByIndex(i)
-                u = nv.nvmlDeviceGetUUID(h)
-                u = u.decode() if isinstance(u, bytes) else u
-                if uuid in u:
-                    handle = h
-                    break
-            if handle is None:
-                handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            nv, handle = nvml_handle(self.index)
             self.smax = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
             self.source = "nvml"
             self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
@@ -678,6 +706,8 @@ def main():
     ap.add_argument("--path", default="auto", choices=["auto", "simt", "tcgen05", "fused_bwd"])
     ap.add_argument("--cpu-sample-T", type=int, default=8192)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-host-binding", action="store_true",
+                    help="with several ranks: leave the ranks' host threads and pinned buffers where the OS puts them")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-twin", action="store_true", help="skip the sequence-only twin (depth-KV overhead) leg")
     ap.add_argument("--no-other-workloads", action="store_true", help="skip the secondary workloads (configs 2, 3, 5, published shape)")
@@ -706,6 +736,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists)")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    # several ranks on one node: each keeps its host side (threads, pinned buffers) beside its GPU
+    host_binding = bind_host_near_gpu(local_rank) if world > 1 and not args.no_host_binding else None
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
@@ -1002,6 +1034,7 @@ def main():
                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": n_e2e,
                    "ms_per_step": ems / n_e2e,
                    "h2d_gbs_per_rank": h2d / sec / 1e9, "d2h_gbs_per_rank": d2h / sec / 1e9,
+                   "host_binding": host_binding,
                    "note": "per-rank bytes; pinned host buffers; one (batch, KV-head) unit per operator call, "
                            "copies of neighbouring units (of this and the next step) on their own streams under the kernels"}
             # the pipelined results are the whole-tensor results, unit by unit
