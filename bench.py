@@ -66,18 +66,18 @@ PUBLISHED_A100_MS = {"published_causal_T65536_d64": 1883.026}   # reference READ
 DEFAULT_WORKLOAD = "config4_chunk_visible_T65536"
 CHUNK_ROWS = 64
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel on the default workload,
-# SCALED from the ncu captures summarised under profiles/: the tcgen05 kernels were captured on
-# the T=8192 case (the full size exceeds the capture size rule); their DRAM traffic there is
-# 0.96-1.01 x the algorithmic bytes (inputs read once from HBM, tiles re-read from L2), and
-# traffic grows with the units processed, so the full-size figure is the algorithmic bytes of the
-# launch times that ratio.  Algorithmic bytes at config 4: forward q, k, v, depth K/V in, o + lse
-# out = 9.93 GB; dq the same inputs + o, dO in, dq out = 10.5 GB; dk/dv (sequence keys only) q, dO,
-# k, v in, dk, dv out = 1.62 GB; depth gradients depth K/V, q, dO in, d_depth_k/v out = 18.3 GB.
-NCU_TRAFFIC_BYTES = {"tc_fwd": 0.99 * 9.93e9, "tc_dq": 0.98 * 10.5e9, "tc_dkv": 0.96 * 1.62e9,
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of a kernel on the default workload, from
+# the ncu captures summarised under profiles/.  Forward, dq and dk/dv: a one-pass capture of the
+# two counters at the full size (nothing is saved or restored with one pass).  Against the
+# algorithmic bytes at config 4 - forward q, k, v, depth K/V in, o + lse out = 9.93 GB; dq the same
+# inputs + o, dO in, dq out = 10.5 GB; dk/dv (sequence keys only) q, dO, k, v in, dk, dv out =
+# 1.62 GB - that is 1.11 x, 1.15 x and 1.6 x (the sequence K/V of a head, 33.5 MB, are re-read from
+# L2 by every block and now and then from HBM; dk/dv also re-reads q and dO per key tile).  The
+# depth-gradient kernel (18.3 GB algorithmic) is scaled from its T=8192 capture (1.01 x).
+NCU_TRAFFIC_BYTES = {"tc_fwd": 10.259e9 + 0.744e9, "tc_dq": 11.558e9 + 0.533e9, "tc_dkv": 2.305e9 + 0.263e9,
                      "tc_depth_grad": 1.01 * 18.3e9, "fda_fwd": 17.72e9, "fda_bwd": 35.43e9}
-NCU_TRAFFIC_SOURCE = {"tc_fwd": "scaled from the T=8192 ncu capture", "tc_dq": "scaled from the T=8192 ncu capture",
-                      "tc_dkv": "scaled from the T=8192 ncu capture", "tc_depth_grad": "scaled from the T=8192 ncu capture",
+NCU_TRAFFIC_SOURCE = {"tc_fwd": "one-pass ncu capture of this workload", "tc_dq": "one-pass ncu capture of this workload",
+                      "tc_dkv": "one-pass ncu capture of this workload", "tc_depth_grad": "scaled from the T=8192 ncu capture",
                       "fda_fwd": "ncu capture of this workload", "fda_bwd": "ncu capture of this workload"}
 
 # Algorithmic matmuls (of 2*D*pairs FLOP each) a kernel OWNS - the outputs it alone produces.  The

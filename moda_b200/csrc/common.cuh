@@ -48,6 +48,22 @@ __host__ __device__ __forceinline__ int64_t dep_mem_row(const Params& p, int64_t
   return (p.Ls == p.L) ? c : (c / p.L) * p.Ls + (c % p.L);
 }
 
+// Order in which a grid (tiles, H, B) is worked through.  Thread blocks are handed out x-fastest,
+// so by default a wave of them works on the tiles of ONE (batch, head), whose K/V then stay in L2.
+// When the sequence K/V of all heads together are small against L2 that locality comes for free
+// and the causal imbalance between tiles is what matters: `rank` then runs over the tiles of
+// every head alike, so that the heaviest tiles of ALL heads start first and the light ones fill
+// the tail of a short launch.  (Depth rows are read once, by one block: they do not count.)
+struct BlockId { int rank, h, b; };
+__device__ __forceinline__ BlockId block_order(const Params& p, int head_dim) {
+  const int64_t seq_kv_bytes = (int64_t)p.B * p.H * p.T_kv * head_dim * 4;     // K and V, 16-bit
+  if (seq_kv_bytes > ((int64_t)48 << 20)) return {(int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z};
+  const int hb = (int)(gridDim.y * gridDim.z);
+  const int lin = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+  const int r = lin / hb, w = lin - r * hb;
+  return {r, w % (int)gridDim.y, w / (int)gridDim.y};
+}
+
 // ---------------------------------------------------------------------------
 // Visibility.  A query row r (base position t = r / G) sees
 //   sequence key j     iff  seq_lo <= j < seq_hi

@@ -195,8 +195,9 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
 
   const int n_qt = (p.T_q + kBM - 1) / kBM;
-  const int qt = n_qt - 1 - (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const BlockId bid = block_order(p, D);
+  const int qt = n_qt - 1 - bid.rank;
+  const int h = bid.h, b = bid.b;
   const int r0 = qt * kBM;
   int n_seq, n_dep, dep_c0, seq_full_hi;   // key walk in steps of 64
   {
@@ -523,9 +524,10 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
 
-  const int h = blockIdx.y, b = blockIdx.z;
-  const bool is_dep = (int)blockIdx.x >= n_seq_key_tiles;
-  const int c0 = (is_dep ? (int)blockIdx.x - n_seq_key_tiles : (int)blockIdx.x) * kBN;
+  const BlockId bid = block_order(p, D);
+  const int h = bid.h, b = bid.b;
+  const bool is_dep = bid.rank >= n_seq_key_tiles;
+  const int c0 = (is_dep ? bid.rank - n_seq_key_tiles : bid.rank) * kBN;
   const int n_keys = is_dep ? p.T_kv * p.L : p.T_kv;
   const int c_last = min(c0 + kBN, n_keys) - 1;
 

@@ -16,7 +16,10 @@
 // alone), then the depth key tiles of the two query tiles, interleaved (their depth windows are
 // different rows, so a depth step belongs to one query tile).
 //
-//   warp 9 (TMA)   Q_0, Q_1 once; ring of two {K tile, V tile} slots.
+//   warp 9 (TMA)   Q_0, Q_1 once; a ring of K tiles and a ring of V tiles with barriers of their own:
+//                  a K slot is free again once the scores that read it have run, a softmax earlier
+//                  than the V slot of the same step, so the next K tile is on its way that much
+//                  sooner (depth tiles come from HBM, not from L2, and are needed right away).
 //   warp 8 (MMA)   S_a = Q_a K^T (SS, M128 N128), O_a += P_a V (TS, N = D: P_a packed over S_a in TMEM).
 //   warps 0-3 / 4-7  softmax of query tile 0 / 1, lazy O rescale, epilogue.
 //
@@ -40,10 +43,16 @@ static_assert(2 * 128 * kF3SoftmaxRegs + 128 * kF3IssueRegs <= 384 * 168, "regis
 constexpr int kF3Parts = 2;
 __device__ constexpr int kF3Bound[5] = {0, 32, 64, 64, 64};
 static_assert(kF3Parts >= 1 && kF3Parts <= 4, "one to four parts");
-// barriers: q, full[2], empty[2], s[2], done, p[part][2] (part of P stored)
-struct F3Bars { static constexpr int q = 0, full0 = 1, empty0 = 3, s0 = 5, done = 7, p0 = 8, count = 8 + 2 * kF3Parts; };
+constexpr int kF3KSlots = 2;      // K tiles in flight or in use (three fit and measured the same); V tiles: two
+static_assert(kF3KSlots == 2 || kF3KSlots == 3, "two or three K slots");
+// barriers: q, fullk[3], fullv[2], emptyk[3], emptyv[2], s[2], done, p[part][2] (part of P stored)
+struct F3Bars {
+  static constexpr int q = 0, fullk0 = 1, fullv0 = 4, emptyk0 = 6, emptyv0 = 9, s0 = 11, done = 13, p0 = 14, count = 14 + 2 * kF3Parts;
+};
 static_assert(F3Bars::count <= kMaxBars, "control block too small");
-template <int D> __host__ __device__ constexpr uint32_t f3_smem() { return 6 * tile_bytes<D>() + kCtlBytes; }   // Q_0, Q_1, two {K, V} slots
+// Q_0, Q_1, the K slots, two V slots
+template <int D> __host__ __device__ constexpr uint32_t f3_smem() { return (4 + kF3KSlots) * tile_bytes<D>() + kCtlBytes; }
+static_assert(f3_smem<128>() <= 232448, "shared memory of the CTA exceeded");
 
 struct Fwd3Maps { CUtensorMap q, k, v, kd, vd; };        // 128-row boxes
 
@@ -120,8 +129,10 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
     return;
   }
   const uint32_t sQ = base;                              // Q_a at sQ + a * kTile
-  const uint32_t sRing = base + 2 * kTile;               // slot: {K tile, V tile}
-  const uint32_t ctl_off = 6 * kTile;
+  constexpr int KS = kF3KSlots;
+  const uint32_t sK = base + 2 * kTile;                  // K slot i at sK + i * kTile
+  const uint32_t sV = sK + KS * kTile;                   // V slot i at sV + i * kTile
+  const uint32_t ctl_off = (4 + KS) * kTile;
   const uint32_t bars = base + ctl_off;
   unsigned char* gctl = smem_raw + ctl_off;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gctl + 8 * kMaxBars);
@@ -132,8 +143,9 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;
 
   const int n_pairs = (p.T_q + 2 * kBM - 1) / (2 * kBM);
-  const int pq = n_pairs - 1 - (int)blockIdx.x;     // heaviest causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const BlockId bid = block_order(p, D);
+  const int pq = n_pairs - 1 - bid.rank;            // heaviest causal tiles first
+  const int h = bid.h, b = bid.b;
   const int r0 = pq * 2 * kBM;
   const F3Plan pl = f3_plan(p, r0);
   const bool two = r0 + kBM < p.T_q;                // the second query tile exists
@@ -142,9 +154,13 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
   if (tid == 0) {
     mbar_init(bars + 8 * B_::q, 1);
     mbar_init(bars + 8 * B_::done, 1);
+    for (int i = 0; i < KS; ++i) {
+      mbar_init(bars + 8 * (B_::fullk0 + i), 1);
+      mbar_init(bars + 8 * (B_::emptyk0 + i), 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bars + 8 * (B_::full0 + i), 1);
-      mbar_init(bars + 8 * (B_::empty0 + i), 1);
+      mbar_init(bars + 8 * (B_::fullv0 + i), 1);
+      mbar_init(bars + 8 * (B_::emptyv0 + i), 1);
       mbar_init(bars + 8 * (B_::s0 + i), 1);
       for (int j = 0; j < kF3Parts; ++j) mbar_init(bars + 8 * (B_::p0 + 2 * j + i), 4);   // one arrival per softmax warp
     }
@@ -176,33 +192,40 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         if (two) tma_load_tile<D>(sQ + kTile, &maps.q, bars + 8 * B_::q, kHalfBytes, h, r0 + kBM, b);
       }
       __syncwarp();
+      // K tiles run kLead steps ahead of the V tiles: K(s + kLead) waits for the scores of step
+      // s + kLead - KS, V(s) for the P V of step s - 2, which finish in that order.
+      constexpr int kLead = KS - 2;
       bool ok = true;
-      int issued = 0;
-      for (int s = 0; ok && s < pl.n; ++s) {
-        const uint32_t slot = s & 1;
-        if (s >= 2 && !(ok = mbar_wait(bars + 8 * (B_::empty0 + slot), ((s >> 1) - 1) & 1, abort_flag, B_::empty0 + slot))) break;
+      int issued_k = 0, issued_v = 0;
+      auto load = [&](int s, bool is_k) -> bool {
+        const uint32_t slot = is_k ? s % KS : s & 1;
+        const int e_bar = (is_k ? B_::emptyk0 : B_::emptyv0) + slot, f_bar = (is_k ? B_::fullk0 : B_::fullv0) + slot;
+        const int use = is_k ? s / KS : s >> 1;           // how often the slot has been filled before
+        if (use >= 1 && !mbar_wait(bars + 8 * e_bar, (use - 1) & 1, abort_flag, e_bar)) return false;
         int part, row; bool dep;
         f3_step(pl, s, part, dep, row);
-        const uint32_t dst = sRing + slot * 2 * kTile, bar = bars + 8 * (B_::full0 + slot);
-        const CUtensorMap* mk = dep ? &maps.kd : &maps.k;
-        const CUtensorMap* mv = dep ? &maps.vd : &maps.v;
+        const uint32_t dst = is_k ? sK + slot * kTile : sV + slot * kTile, bar = bars + 8 * f_bar;
+        const CUtensorMap* m = dep ? (is_k ? &maps.kd : &maps.vd) : (is_k ? &maps.k : &maps.v);
         if (elect_one()) {
-          mbar_expect_tx(bar, 2 * kTile);
-          if (dep) {
-            tma_load_dep_tile<D>(dst, mk, bar, kHalfBytes, h, row, b, dep5);
-            tma_load_dep_tile<D>(dst + kTile, mv, bar, kHalfBytes, h, row, b, dep5);
-          } else {
-            tma_load_tile<D>(dst, mk, bar, kHalfBytes, h, row, b);
-            tma_load_tile<D>(dst + kTile, mv, bar, kHalfBytes, h, row, b);
-          }
+          mbar_expect_tx(bar, kTile);
+          if (dep) tma_load_dep_tile<D>(dst, m, bar, kHalfBytes, h, row, b, dep5);
+          else tma_load_tile<D>(dst, m, bar, kHalfBytes, h, row, b);
         }
         __syncwarp();
-        issued = s + 1;
+        (is_k ? issued_k : issued_v) = s + 1;
+        return true;
+      };
+      for (int s = 0; ok && s < kLead && s < pl.n; ++s) ok = load(s, true);
+      for (int s = 0; ok && s < pl.n; ++s) {
+        if (s + kLead < pl.n) ok = load(s + kLead, true);
+        if (ok) ok = load(s, false);
       }
       if (!ok) {   // let loads in flight land before the CTA's shared memory is released
         mbar_wait(bars + 8 * B_::q, 0, drain_flag, B_::q);
-        for (int s = max(0, issued - 2); s < issued; ++s)
-          mbar_wait(bars + 8 * (B_::full0 + (s & 1)), (s >> 1) & 1, drain_flag, B_::full0 + (s & 1));
+        for (int s = max(0, issued_k - KS); s < issued_k; ++s)
+          mbar_wait(bars + 8 * (B_::fullk0 + s % KS), (s / KS) & 1, drain_flag, B_::fullk0 + s % KS);
+        for (int s = max(0, issued_v - 2); s < issued_v; ++s)
+          mbar_wait(bars + 8 * (B_::fullv0 + (s & 1)), (s >> 1) & 1, drain_flag, B_::fullv0 + (s & 1));
       }
     }
   } else if (warp == 8) {
@@ -213,12 +236,14 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       constexpr uint32_t idesc_pv = instr_desc(fmt, D, true);
       int qk_cnt[2] = {0, 0}, pv_cnt[2] = {0, 0};     // steps tile a has taken part in so far
       bool ok = mbar_wait(bars + 8 * B_::q, 0, abort_flag, B_::q);
-      // S_a = Q_a K(s)^T
+      int qk_left = 0;                                // tiles that have yet to read the K tile being read
+      // S_a = Q_a K(s)^T; the last tile to read K(s) hands the slot back
       auto qk = [&](int a, int s) -> bool {
-        const uint32_t slot = s & 1;
-        if (!mbar_wait(bars + 8 * (B_::full0 + slot), (s >> 1) & 1, abort_flag, B_::full0 + slot)) return false;
+        const uint32_t slot = s % KS;
+        if (!mbar_wait(bars + 8 * (B_::fullk0 + slot), (s / KS) & 1, abort_flag, B_::fullk0 + slot)) return false;
         tc_fence_after();
-        const uint64_t dK = desc_kmajor(sRing + slot * 2 * kTile), dQa = desc_kmajor(sQ + a * kTile);
+        const uint64_t dK = desc_kmajor(sK + slot * kTile), dQa = desc_kmajor(sQ + a * kTile);
+        --qk_left;
         const uint32_t tS = tmem + a * 128;
         if (elect_one()) {
 #pragma unroll
@@ -227,6 +252,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
             mma_ss(tS, desc_add(dQa, off), desc_add(dK, off), idesc_qk, kk > 0);
           }
           tc_commit(bars + 8 * (B_::s0 + a));
+          if (qk_left == 0) tc_commit(bars + 8 * (B_::emptyk0 + slot));
         }
         __syncwarp();
         ++qk_cnt[a];
@@ -236,7 +262,8 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       // matmuls over a part of P go out while the softmax still computes the next one.
       auto pv = [&](int a, int s, bool last) -> bool {
         const uint32_t slot = s & 1;
-        const uint64_t dV = desc_mnmajor(sRing + slot * 2 * kTile + kTile, kHalfBytes);
+        if (!mbar_wait(bars + 8 * (B_::fullv0 + slot), (s >> 1) & 1, abort_flag, B_::fullv0 + slot)) return false;
+        const uint64_t dV = desc_mnmajor(sV + slot * kTile, kHalfBytes);
         const uint32_t tS = tmem + a * 128, tO = tmem + 256 + a * 128;
 #pragma unroll
         for (int part = 0; part < kF3Parts; ++part) {
@@ -246,7 +273,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
 #pragma unroll
             for (int kk = kF3Bound[part] / 8; kk < kF3Bound[part + 1] / 8; ++kk)
               mma_ts(tO, tS + kk * 8, desc_add(dV, kk * 2048), idesc_pv, (pv_cnt[a] > 0 || kk > 0) ? 1u : 0u);
-            if (last && part == kF3Parts - 1) tc_commit(bars + 8 * (B_::empty0 + slot));
+            if (last && part == kF3Parts - 1) tc_commit(bars + 8 * (B_::emptyv0 + slot));
           }
           __syncwarp();
         }
@@ -256,6 +283,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       int part, row, part_next = 0; bool dep;
       if (ok) {
         f3_step(pl, 0, part, dep, row);
+        qk_left = __popc(part);
         for (int a = 0; ok && a < 2; ++a)
           if (part & (1 << a)) ok = qk(a, 0);
       }
@@ -267,10 +295,13 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
       const int n_both = min(pl.w[0].n_seq, pl.w[1].n_seq);
       if (ok && n_both > 1) {
         const uint64_t dQ[2] = {desc_kmajor(sQ), desc_kmajor(sQ + kTile)};
+        uint32_t kn_slot = 1 % KS, kn_par = 0;            // slot of K(s+1) and the parity of its filling
         for (; ok && s + 1 < n_both; ++s) {
           const uint32_t slot = s & 1, par = s & 1;       // both tiles have taken part in s steps so far
-          const uint64_t dV = desc_mnmajor(sRing + slot * 2 * kTile + kTile, kHalfBytes);
-          const uint64_t dKn = desc_kmajor(sRing + (slot ^ 1) * 2 * kTile);
+          // V(s) landed long ago: the check costs nothing while the warp waits for P_0 anyway
+          if (!(ok = mbar_wait(bars + 8 * (B_::fullv0 + slot), (s >> 1) & 1, abort_flag, B_::fullv0 + slot))) break;
+          const uint64_t dV = desc_mnmajor(sV + slot * kTile, kHalfBytes);
+          const uint64_t dKn = desc_kmajor(sK + kn_slot * kTile);
           const uint32_t acc = s > 0 ? 1u : 0u;
 #pragma unroll
           for (int a = 0; a < 2; ++a) {
@@ -283,13 +314,13 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
 #pragma unroll
                 for (int kk = kF3Bound[part_i] / 8; kk < kF3Bound[part_i + 1] / 8; ++kk)
                   mma_ts(tO, tS + kk * 8, desc_add(dV, kk * 2048), idesc_pv, kk > 0 ? 1u : acc);
-                if (a == 1 && part_i == kF3Parts - 1) tc_commit(bars + 8 * (B_::empty0 + slot));
+                if (a == 1 && part_i == kF3Parts - 1) tc_commit(bars + 8 * (B_::emptyv0 + slot));
               }
               __syncwarp();
             }
             if (!ok) break;
             // K(s+1): one wait serves both tiles
-            if (a == 0 && !(ok = mbar_wait(bars + 8 * (B_::full0 + (slot ^ 1)), ((s + 1) >> 1) & 1, abort_flag, B_::full0 + (slot ^ 1)))) break;
+            if (a == 0 && !(ok = mbar_wait(bars + 8 * (B_::fullk0 + kn_slot), kn_par, abort_flag, B_::fullk0 + kn_slot))) break;
             tc_fence_after();
             if (elect_one()) {
 #pragma unroll
@@ -298,9 +329,11 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
                 mma_ss(tS, desc_add(dQ[a], off), desc_add(dKn, off), idesc_qk, kk > 0);
               }
               tc_commit(bars + 8 * (B_::s0 + a));
+              if (a == 1) tc_commit(bars + 8 * (B_::emptyk0 + kn_slot));
             }
             __syncwarp();
           }
+          if (++kn_slot == KS) { kn_slot = 0; kn_par ^= 1; }
         }
         qk_cnt[0] = qk_cnt[1] = s + 1;
         pv_cnt[0] = pv_cnt[1] = s;
@@ -309,6 +342,7 @@ fwd3_kernel(const __grid_constant__ Params p, const __grid_constant__ Fwd3Maps m
         f3_step(pl, s, part, dep, row);
         part_next = 0;
         if (s + 1 < pl.n) f3_step(pl, s + 1, part_next, dep, row);
+        qk_left = __popc(part_next);
         // a tile that joins at s+1 without taking part in s (alternating depth steps) has a free
         // score block: its scores go ahead of this step's PVs and run under the other tile's softmax
 #pragma unroll

@@ -397,8 +397,9 @@ fwd_kernel(const __grid_constant__ Params p, const __grid_constant__ FwdMaps map
   if (*reinterpret_cast<volatile int*>(&g_tc_status) != 0) return;   // an earlier CTA failed: do nothing
 
   const int n_qt = (p.T_q + kBM - 1) / kBM;
-  const int qt = n_qt - 1 - (int)blockIdx.x;     // heaviest causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const BlockId bid = block_order(p, D);
+  const int qt = n_qt - 1 - bid.rank;            // heaviest causal tiles first
+  const int h = bid.h, b = bid.b;
   const int r0 = qt * kBM;
   const Walk walk = make_walk(p, r0);
   const int n_tiles = walk.n_seq + walk.n_dep;

@@ -24,7 +24,7 @@ from tests.helpers import TOL_LSE_MAX_ABS, TOL_O_MAX_ABS, max_abs
 pytestmark = pytest.mark.gpu
 
 BAR_P = {"one_tile": 4,     # tc::BarId::kBarP of the one-tile forward
-         "two_tiles": 8}    # tc::F3Bars::p0 (first part of P, query tile 0) of the two-tile forward
+         "two_tiles": 14}   # tc::F3Bars::p0 (first part of P, query tile 0) of the two-tile forward
 
 
 @pytest.mark.parametrize("fwd", ["one_tile", "two_tiles"])
@@ -54,8 +54,8 @@ def test_expired_wait_is_reported_and_context_survives(built_library, fwd):
     torch.cuda.synchronize()                         # returns: the kernel ended by itself
     assert wt.moda_b200_device_status(ctypes.byref(st)) == 0
     # (the softmax warps' own bounded wait for the end of the matmuls starts a few microseconds
-    # later and may, in principle, run out first: barrier 7 of the two-tile forward)
-    expected = {(1 << 8) | BAR_P[fwd]} | ({(1 << 8) | 7} if fwd == "two_tiles" else set())
+    # later and may, in principle, run out first: barrier 13 of the two-tile forward)
+    expected = {(1 << 8) | BAR_P[fwd]} | ({(1 << 8) | 13} if fwd == "two_tiles" else set())
     assert st.value in expected, hex(st.value)
     assert wt.moda_b200_device_status(ctypes.byref(st)) == 0 and st.value == 0      # reading reset it
     assert float(o.abs().max()) == 0.0               # the abandoned launch wrote no output
