@@ -141,6 +141,26 @@ def mma_mix(kernel, D):
     return None
 
 
+SMEM_PORT_BYTES_PER_CLOCK = 128     # shared-memory bandwidth of one SM; the SS matmul rates of the probe (8 KB in 67.7 clocks) sit just under it
+
+
+def smem_bytes(kernel, D):
+    """Bytes that cross the SM's shared-memory port per 128x128 block: matmul operands read from shared
+    memory (A of an SS instruction 128 x 16 x 2 B, B of any instruction N x 16 x 2 B), the tiles TMA
+    writes into it, and what the softmax warps store there (dS; P^T and dS^T)."""
+    a_op, kd = 128 * 16 * 2, D // 16
+    b_op = lambda n: n * 16 * 2
+    if kernel == "tc_fwd":       # scores SS N=128, P V TS N=D; K and V tiles (128 x D) serve two query tiles
+        return {"mma_operands": kd * (a_op + b_op(128)) + 8 * b_op(D), "tma_fill": 2 * 128 * D * 2 // 2, "softmax_stores": 0}
+    if kernel == "tc_dq":        # per 64-key step: S, dP TS N=64; dQ += dS K SS N=D (K = 64); dS tile; K, V step tiles
+        return {"mma_operands": 2 * (2 * kd * b_op(64) + 4 * (a_op + b_op(D))), "tma_fill": 2 * 2 * 64 * D * 2,
+                "softmax_stores": 2 * 128 * 64 * 2}
+    if kernel == "tc_dkv":       # per 64-row step: S^T, dP^T TS N=64; dV, dK SS N=D; P^T and dS^T tiles; Q, dO step tiles + lse, delta
+        return {"mma_operands": 2 * (2 * kd * b_op(64) + 8 * (a_op + b_op(D))), "tma_fill": 2 * (2 * 64 * D * 2 + 512),
+                "softmax_stores": 2 * 2 * 128 * 64 * 2}
+    return None
+
+
 def tensor_pipe_model(M, device, prof, mode, B, T, Hkv, G, D, L, shard_frac, sm_mhz):
     """Tensor-pipe time each attention kernel's instruction mix needs per block, from instruction
     rates measured on this GPU (moda_b200.tensor_pipe_rates), beside the clocks per block the
@@ -160,7 +180,9 @@ def tensor_pipe_model(M, device, prof, mode, B, T, Hkv, G, D, L, shard_frac, sm_
                    "measured clocks per instruction (one issuing warp; two warps overlap a little better, so dq and "
                    "dk/dv can read slightly above 1); measured_clocks_per_block = launch time x median SM clock x SMs "
                    "/ blocks; pipe_busy = their ratio.  nominal_frac = what the same mix would reach of the nominal "
-                   "8192 flop/clock/SM if the pipe were never idle: the ceiling the instruction shapes allow."}
+                   "8192 flop/clock/SM if the pipe were never idle: the ceiling the instruction shapes allow.  "
+                   "smem_port_busy = bytes through the SM's shared-memory port per block (matmul operands, TMA fills, "
+                   "softmax stores) / 128 B per clock / measured clocks: the backward kernels sit near this limit."}
     for k_ in ("tc_fwd", "tc_dq", "tc_dkv"):
         if k_ not in prof or prof[k_][1] <= 0:
             continue
@@ -170,9 +192,13 @@ def tensor_pipe_model(M, device, prof, mode, B, T, Hkv, G, D, L, shard_frac, sm_
         pipe = sum(n * rates[sh] for sh, n in mix.items())
         nominal = sum(n * int(sh.split("_n")[1]) / 2 for sh, n in mix.items())
         meas = tot_ms / cnt * 1e-3 * sm_mhz * 1e6 * n_sm / blocks
+        sb = smem_bytes(k_, D)
+        port = sum(sb.values()) / SMEM_PORT_BYTES_PER_CLOCK
         out["kernels"][k_] = {"mma_per_block": mix, "pipe_clocks_per_block": round(pipe, 1),
                               "measured_clocks_per_block": round(meas, 1), "pipe_busy": round(pipe / meas, 3),
-                              "nominal_frac_of_mix": round(nominal / pipe, 3)}
+                              "nominal_frac_of_mix": round(nominal / pipe, 3),
+                              "smem_bytes_per_block": sb, "smem_port_clocks_per_block": round(port, 1),
+                              "smem_port_busy": round(port / meas, 3)}
     return out
 
 

@@ -101,3 +101,9 @@ def test_tensor_pipe_model_counts():
     assert b.mma_mix("tc_dkv", 128) == {"ts_n64": 32, "ss_n128": 16}
     assert b.mma_mix("tc_fwd", 64) == {"ss_n128": 4, "ts_n64": 8}
     assert b.mma_mix("fda_fwd", 128) is None
+    # bytes through the shared-memory port per 128 x 128 block
+    assert sum(b.smem_bytes("tc_fwd", 128).values()) == 131072
+    assert sum(b.smem_bytes("tc_dq", 128).values()) == 229376
+    assert sum(b.smem_bytes("tc_dkv", 128).values()) == 328704
+    assert sum(b.smem_bytes("tc_fwd", 64).values()) == 65536
+    assert b.smem_bytes("fda_fwd", 128) is None
