@@ -164,7 +164,9 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t d, uint32_t byte_off) { re
 // Shared memory: ring of dq_ring<D>() x {K step tile, V step tile} ([64 x D] each), then two
 // [128 x 64] dS tiles (K-major, 128-byte swizzle).  A softmax warpgroup releases its TMEM stage
 // as soon as it has the scores in registers, so the next-but-one score MMAs overlap its math;
-// dS reaches the update MMA through shared memory.
+// dS reaches the update MMA through shared memory - at D = 64 through TMEM instead: the 64-column
+// accumulator leaves [320, 384) free for the two dS tiles as 16-bit A operands (32 columns each).
+constexpr uint32_t kDqDsCol0 = 320;
 template <typename T, int D>
 __global__ void __launch_bounds__(kDqThreads, 1)
 dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps, const float* delta_t,
@@ -332,10 +334,13 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         const uint32_t slot = j % R;
         const uint64_t da = desc_kmajor(sDS + (j & 1) * kScoreTile);
         const uint64_t dk = desc_mnmajor(sRing + slot * 2 * kStepTile, kStepHalf);
+        const uint32_t tds = tmem + kDqDsCol0 + (j & 1) * 32;      // D = 64: dS in TMEM
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {
+            if constexpr (D == 64) mma_ts(tmem_dQ, tds + kk * 8, desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            else mma_ss(tmem_dQ, desc_add(da, kk * 32), desc_add(dk, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+          }
           tc_commit(bars + 8 * (B_.empty0 + slot));      // slot j may be refilled
           tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // dS tile j&1 may be rewritten
           if (j == n - 1) tc_commit(bars + 8 * B_.done);
@@ -426,13 +431,19 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
         if (!ok) break;
       }
-      {   // row of the K-major, 128B-swizzled [128 x 64] tile: 16-byte chunk c lives at chunk c ^ (row & 7)
+      if constexpr (D == 64) {
+        // the 64-column accumulator leaves TMEM columns free at D = 64: dS goes there as the A operand
+        // of the update matmul (packed pairs of key columns), not through shared memory
+        tmem_st32<0>(tmem + kDqDsCol0 + (i & 1) * 32 + lane_addr, pk);
+        tmem_wait_st();
+        tc_fence_before();
+      } else {   // row of the K-major, 128B-swizzled [128 x 64] tile: 16-byte chunk c lives at chunk c ^ (row & 7)
         unsigned char* prow = smem_raw + ds_off + (i & 1) * kScoreTile + row * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch)
           *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #ifndef MODA_WAIT_TEST
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
 #endif
@@ -488,13 +499,17 @@ dq_kernel(const __grid_constant__ Params p, const __grid_constant__ DqMaps maps,
 // =========================================================================== dk / dv
 // grid (n_seq_key_tiles + n_dep_key_tiles, H, B), 384 threads; key tiles of 128.
 // TMEM (512 columns): [0, 64) S^T and [64, 128) dP^T (one fp32 score stage);
-//   [128, 128+D) dV; [256, 256+D) dK; [384, 384+D/2) K and [448, 448+D/2) V rows as 16-bit A operands.
+//   [128, 128+D) dV; [256, 256+D) dK; [384, 384+D/2) K and [448, 448+D/2) V rows as 16-bit A operands;
+//   at D = 64 also [192, 256) and [320, 384): the two {P^T, dS^T} pairs as 16-bit A operands.
 // Shared memory: ring of dkv_ring<D>() x {Q step tile, dO step tile}; two {P^T, dS^T} tile pairs
 // ([128 keys x 64 rows], K-major, 128-byte swizzle), one per softmax warpgroup; the ring of
 // {64 lse, 64 delta}.  A warpgroup releases the score stage as soon as the scores are in its
 // registers, so the next step's score MMAs overlap its math; P^T and dS^T reach the update
 // MMAs through shared memory.
 constexpr uint32_t kDkvPairBytes = 2 * kScoreTile;   // P^T tile + dS^T tile
+// D = 64: the two {P^T, dS^T} pairs live in TMEM columns the 64-column accumulators leave free
+// ([192, 256) and [320, 384): P^T in the first 32 columns of a pair, dS^T in the next 32)
+constexpr uint32_t kDkvPairCol0 = 192, kDkvPairColStride = 128;
 
 template <typename T, int D>
 __global__ void __launch_bounds__(kDkvThreads, 1)
@@ -645,11 +660,17 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         const uint32_t slot = j % R, sQ = sRing + slot * 2 * kStepTile;
         const uint64_t dq = desc_mnmajor(sQ, kStepHalf), ddo = desc_mnmajor(sQ + kStepTile, kStepHalf);
         const uint64_t dpt = desc_kmajor(sPT + (j & 1) * kDkvPairBytes), dst = desc_kmajor(sPT + (j & 1) * kDkvPairBytes + kScoreTile);
+        const uint32_t tpair = tmem + kDkvPairCol0 + (j & 1) * kDkvPairColStride;   // D = 64: P^T, dS^T in TMEM
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            mma_ss(tmem_dV, desc_add(dpt, kk * 32), desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
-            mma_ss(tmem_dK, desc_add(dst, kk * 32), desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            if constexpr (D == 64) {
+              mma_ts(tmem_dV, tpair + kk * 8, desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+              mma_ts(tmem_dK, tpair + 32 + kk * 8, desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            } else {
+              mma_ss(tmem_dV, desc_add(dpt, kk * 32), desc_add(ddo, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+              mma_ss(tmem_dK, desc_add(dst, kk * 32), desc_add(dq, kk * 2048), idesc_t, (j > 0 || kk > 0) ? 1u : 0u);
+            }
           }
           tc_commit(bars + 8 * (B_.empty0 + slot));      // ring slot j may be refilled
           tc_commit(bars + 8 * (B_.t0 + (j & 1)));       // tile pair j&1 may be rewritten
@@ -752,7 +773,15 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (B_.t0 + (i & 1)), ((i - 2) >> 1) & 1, abort_flag, B_.t0 + (i & 1)));
         if (!ok) break;
       }
-      {   // rows of the K-major, 128B-swizzled [128 x 64] tiles: 16-byte chunk c lives at chunk c ^ (row & 7)
+      if constexpr (D == 64) {
+        // the accumulators leave TMEM columns free at D = 64: P^T and dS^T go there as the A operands
+        // of the update matmuls (packed pairs of query columns, 32 columns each), not through shared memory
+        const uint32_t tpair = tmem + kDkvPairCol0 + (i & 1) * kDkvPairColStride + lane_addr;
+        tmem_st32<0>(tpair, pp);
+        tmem_st32<0>(tpair + 32, pd);
+        tmem_wait_st();
+        tc_fence_before();
+      } else {   // rows of the K-major, 128B-swizzled [128 x 64] tiles: 16-byte chunk c lives at chunk c ^ (row & 7)
         unsigned char* prow = smem_raw + pt_off + (i & 1) * kDkvPairBytes + row * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
@@ -760,8 +789,8 @@ dkv_kernel(const __grid_constant__ Params p, const __grid_constant__ DkvMaps map
           *reinterpret_cast<uint4*>(prow + o) = make_uint4(pp[4 * ch], pp[4 * ch + 1], pp[4 * ch + 2], pp[4 * ch + 3]);
           *reinterpret_cast<uint4*>(prow + kScoreTile + o) = make_uint4(pd[4 * ch], pd[4 * ch + 1], pd[4 * ch + 2], pd[4 * ch + 3]);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 #ifndef MODA_WAIT_TEST
       mbar_arrive(bars + 8 * (B_.p0 + (i & 1)));
 #endif
