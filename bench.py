@@ -131,14 +131,25 @@ def executed_blocks(mode, B, T, Hkv, G, L):
 # kernels step by 64 (keys in dq, query rows in dk/dv): scores TS N = 64 from operands resident in
 # TMEM, updates SS N = D over 64 rows of dS / P^T / dS^T in shared memory.
 def mma_mix(kernel, D):
-    kd, upd = D // 16, "ss_n%d" % D
+    kd = D // 16
+    upd = "ts_n64" if D == 64 else "ss_n%d" % D     # at D = 64 the backward's update operands (dS; P^T, dS^T) sit in TMEM
+    mix = {}
+
+    def add(shape, n):
+        mix[shape] = mix.get(shape, 0) + n
+
     if kernel == "tc_fwd":
-        return {"ss_n128": kd, "ts_n%d" % D: 8}
-    if kernel == "tc_dq":
-        return {"ts_n64": 2 * 2 * kd, upd: 2 * 4}
-    if kernel == "tc_dkv":
-        return {"ts_n64": 2 * 2 * kd, upd: 2 * 2 * 4}
-    return None
+        add("ss_n128", kd)
+        add("ts_n%d" % D, 8)
+    elif kernel == "tc_dq":
+        add("ts_n64", 2 * 2 * kd)
+        add(upd, 2 * 4)
+    elif kernel == "tc_dkv":
+        add("ts_n64", 2 * 2 * kd)
+        add(upd, 2 * 2 * 4)
+    else:
+        return None
+    return mix
 
 
 SMEM_PORT_BYTES_PER_CLOCK = 128     # shared-memory bandwidth of one SM; the SS matmul rates of the probe (8 KB in 67.7 clocks) sit just under it
@@ -152,12 +163,13 @@ def smem_bytes(kernel, D):
     b_op = lambda n: n * 16 * 2
     if kernel == "tc_fwd":       # scores SS N=128, P V TS N=D; K and V tiles (128 x D) serve two query tiles
         return {"mma_operands": kd * (a_op + b_op(128)) + 8 * b_op(D), "tma_fill": 2 * 128 * D * 2 // 2, "softmax_stores": 0}
-    if kernel == "tc_dq":        # per 64-key step: S, dP TS N=64; dQ += dS K SS N=D (K = 64); dS tile; K, V step tiles
-        return {"mma_operands": 2 * (2 * kd * b_op(64) + 4 * (a_op + b_op(D))), "tma_fill": 2 * 2 * 64 * D * 2,
-                "softmax_stores": 2 * 128 * 64 * 2}
-    if kernel == "tc_dkv":       # per 64-row step: S^T, dP^T TS N=64; dV, dK SS N=D; P^T and dS^T tiles; Q, dO step tiles + lse, delta
-        return {"mma_operands": 2 * (2 * kd * b_op(64) + 8 * (a_op + b_op(D))), "tma_fill": 2 * (2 * 64 * D * 2 + 512),
-                "softmax_stores": 2 * 2 * 128 * 64 * 2}
+    upd_a = 0 if D == 64 else a_op      # D = 64: the update's A operand (dS; P^T, dS^T) is in TMEM, nothing is stored
+    if kernel == "tc_dq":        # per 64-key step: S, dP TS N=64; dQ += dS K N=D (K = 64); dS tile; K, V step tiles
+        return {"mma_operands": 2 * (2 * kd * b_op(64) + 4 * (upd_a + b_op(D))), "tma_fill": 2 * 2 * 64 * D * 2,
+                "softmax_stores": 0 if D == 64 else 2 * 128 * 64 * 2}
+    if kernel == "tc_dkv":       # per 64-row step: S^T, dP^T TS N=64; dV, dK N=D; P^T and dS^T tiles; Q, dO step tiles + lse, delta
+        return {"mma_operands": 2 * (2 * kd * b_op(64) + 8 * (upd_a + b_op(D))), "tma_fill": 2 * (2 * 64 * D * 2 + 512),
+                "softmax_stores": 0 if D == 64 else 2 * 2 * 128 * 64 * 2}
     return None
 
 

@@ -106,4 +106,6 @@ def test_tensor_pipe_model_counts():
     assert sum(b.smem_bytes("tc_dq", 128).values()) == 229376
     assert sum(b.smem_bytes("tc_dkv", 128).values()) == 328704
     assert sum(b.smem_bytes("tc_fwd", 64).values()) == 65536
+    assert b.mma_mix("tc_dkv", 64) == {"ts_n64": 32} and b.mma_mix("tc_dq", 64) == {"ts_n64": 24}
+    assert b.smem_bytes("tc_dq", 64) == {"mma_operands": 49152, "tma_fill": 32768, "softmax_stores": 0}
     assert b.smem_bytes("fda_fwd", 128) is None
