@@ -2,8 +2,10 @@
 
     python -m moda_b200.build [--force] [--verbose]
 
-The library is a plain C-ABI shared object (no torch, no pybind); it is rebuilt when
-any file under ``moda_b200/csrc`` or ``include/`` is newer than the ``.so``.
+The library is a plain C-ABI shared object (no torch, no pybind); it is rebuilt when the hash
+of the files under ``moda_b200/csrc`` and ``include/`` (and of the compiler flags) differs from the
+one in the stamp file beside the ``.so``.  Builds are serialised by a lock file and the library is
+moved into place in one piece, so the ranks of a multi-GPU launch can all call ``build()``.
 
 ``build_wait_test()`` compiles the same sources with ``-DMODA_WAIT_TEST`` into
 ``libmoda_b200_waittest.so``: a test-only build in which the tcgen05 forwards and the dq /
@@ -13,7 +15,9 @@ product never loads that file.
 """
 from __future__ import annotations
 
+import fcntl
 import glob
+import hashlib
 import os
 import shutil
 import subprocess
@@ -36,24 +40,55 @@ def sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
-def _stale(out: str = OUT) -> bool:
-    if not os.path.exists(out):
+def _digest(extra) -> str:
+    """Hash of everything the library is built from: sources, headers, compiler flags."""
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS + list(extra)).encode())
+    deps = sorted(glob.glob(os.path.join(CSRC, "*")) + glob.glob(os.path.join(ROOT, "include", "*.h")))
+    for d in deps:
+        if os.path.isfile(d):
+            h.update(os.path.basename(d).encode())
+            with open(d, "rb") as f:
+                h.update(f.read())
+    return h.hexdigest()
+
+
+def _stale(out: str = OUT, extra=()) -> bool:
+    """The library is current when the stamp beside it holds the hash of the present sources.
+    File times play no part: a checkout or a copy of the tree changes them without changing a byte."""
+    stamp = out + ".stamp"
+    if not (os.path.exists(out) and os.path.exists(stamp)):
         return True
-    t = os.path.getmtime(out)
-    deps = glob.glob(os.path.join(CSRC, "*")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
-    return any(os.path.getmtime(d) > t for d in deps)
+    with open(stamp) as f:
+        return f.read().strip() != _digest(extra)
 
 
 def _compile(out: str, extra, force: bool, verbose: bool) -> str:
-    if not force and not _stale(out):
+    if not force and not _stale(out, extra):
         return out
-    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc] + NVCC_FLAGS + list(extra) + (["-Xptxas", "-v"] if verbose else []) + ["-o", out] + sources()
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed building " + os.path.basename(out))
+    # One builder at a time, and the file appears in one piece: the ranks of a multi-GPU launch all
+    # come here, and a library that another process is still writing must never be loaded.
+    with open(out + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale(out, extra):      # built by another process in the meantime
+                return out
+            nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+            tmp = f"{out}.tmp.{os.getpid()}"
+            cmd = [nvcc] + NVCC_FLAGS + list(extra) + (["-Xptxas", "-v"] if verbose else []) + ["-o", tmp] + sources()
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if verbose or res.returncode != 0:
+                sys.stderr.write(res.stdout + res.stderr)
+            if res.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise RuntimeError("nvcc failed building " + os.path.basename(out))
+            os.replace(tmp, out)
+            with open(out + ".stamp.tmp", "w") as f:
+                f.write(_digest(extra) + "\n")
+            os.replace(out + ".stamp.tmp", out + ".stamp")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return out
 
 

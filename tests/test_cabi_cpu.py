@@ -191,3 +191,37 @@ def test_product_package_does_not_import_the_oracle():
                 text = open(os.path.join(dirpath, fn)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), fn
                 assert "moda_oracle" not in text, fn
+
+
+def test_build_is_keyed_by_content_not_by_file_times(built_library):
+    """A checkout or a copy of the tree changes file times without changing a byte: the library must
+    not be taken for stale then (the ranks of a multi-GPU launch would all start rebuilding it)."""
+    import glob
+    import time
+    from moda_b200 import build
+    assert not build._stale(build.OUT)
+    src = sorted(glob.glob(os.path.join(build.CSRC, "*.cuh")))[0]
+    st = os.stat(src)
+    try:
+        os.utime(src, (time.time() + 100, time.time() + 100))      # "newer" than the library
+        assert not build._stale(build.OUT)
+        assert build.build() == build.OUT                           # returns without compiling
+    finally:
+        os.utime(src, (st.st_atime, st.st_mtime))
+    assert build._digest(()) != build._digest(("-DMODA_WAIT_TEST",))   # the flags are part of the key
+
+
+def test_concurrent_build_calls_leave_one_whole_library(built_library):
+    """Every rank of a multi-GPU launch calls build(): with an up-to-date stamp none of them writes,
+    and all of them can load the library."""
+    import subprocess
+    import sys
+    from moda_b200 import build
+    before = os.stat(build.OUT).st_mtime_ns
+    code = ("import ctypes; from moda_b200 import build; p = build.build(); "
+            "ctypes.CDLL(p); print('ok')")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = [subprocess.Popen([sys.executable, "-c", code], cwd=root, stdout=subprocess.PIPE, text=True) for _ in range(6)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs) and all("ok" in o for o in outs)
+    assert os.stat(build.OUT).st_mtime_ns == before
